@@ -1,0 +1,182 @@
+// Memory-bound fp16 GEMV for 1..8 right-hand sides (non tensor core).
+//
+//   Y[i, r] = sum_k W[r, k] * X[i, k]        W: rows x K (row-major, the HBM stream)
+//                                              X: m x K, m <= 8 (stays in L1/L2)
+// fp32 accumulate, one rounding to half at the end.  Counterpart of the reference's
+// mySGemvKernel_Stage4 (src_template/Ampere_FP16/gemv.cu:151-216) and its split-K twin
+// (gemv_splitK.cu:153-221); unlike those it accumulates in fp32, takes any row count and any
+// K that is a multiple of 8, and reduces split-K partials deterministically.
+//
+// Mapping: one warp owns RPW consecutive rows; lane l reads the 16-byte chunk l of each
+// 512-byte row segment, UNROLL segments in flight per row, so a thread keeps RPW*UNROLL
+// independent 128-bit streaming loads outstanding.  Lanes are reduced with a shuffle tree.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace helix {
+
+template <int MRHS, int RPW, int UNROLL>
+__global__ void __launch_bounds__(256)
+gemv_f16_kernel(const __half* __restrict__ W, int64_t ldw, const __half* __restrict__ X, int64_t ldx,
+                __half* __restrict__ Y, int64_t ldy, int64_t ldy_inner, float* __restrict__ partial,
+                int rows, int K, int m, int split_k, int k_per_split) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int warps_per_block = blockDim.x >> 5;
+  const int row_groups = (rows + RPW - 1) / RPW;
+  const int ks = blockIdx.y;
+  const int k_begin = ks * k_per_split;
+  const int k_end = min(K, k_begin + k_per_split);
+
+  for (int g = blockIdx.x * warps_per_block + warp; g < row_groups; g += gridDim.x * warps_per_block) {
+    const int r0 = g * RPW;
+    float acc[RPW][MRHS];
+#pragma unroll
+    for (int r = 0; r < RPW; ++r)
+#pragma unroll
+      for (int i = 0; i < MRHS; ++i) acc[r][i] = 0.0f;
+
+    const __half* wrow[RPW];
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) wrow[r] = W + (int64_t)min(r0 + r, rows - 1) * ldw;
+
+    for (int k0 = k_begin + lane * 8; k0 < k_end; k0 += 256 * UNROLL) {
+      uint4 wv[UNROLL][RPW];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int k = k0 + u * 256;
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+          if (k < k_end) wv[u][r] = ldg_stream_16(wrow[r] + k);
+          else wv[u][r] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int k = k0 + u * 256;
+        if (k < k_end) {
+#pragma unroll
+          for (int i = 0; i < MRHS; ++i) {
+            if (i < m) {
+              const uint4 xv = __ldg(reinterpret_cast<const uint4*>(X + (int64_t)i * ldx + k));
+              const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+#pragma unroll
+              for (int r = 0; r < RPW; ++r) {
+                const __half2* wh = reinterpret_cast<const __half2*>(&wv[u][r]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 wf = __half22float2(wh[j]);
+                  const float2 xf = __half22float2(xh[j]);
+                  acc[r][i] = fmaf(wf.x, xf.x, acc[r][i]);
+                  acc[r][i] = fmaf(wf.y, xf.y, acc[r][i]);
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < RPW; ++r)
+#pragma unroll
+      for (int i = 0; i < MRHS; ++i) {
+        float v = acc[r][i];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        acc[r][i] = v;
+      }
+    if (lane == 0) {
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) {
+        if (r0 + r < rows) {
+#pragma unroll
+          for (int i = 0; i < MRHS; ++i) {
+            if (i < m) {
+              if (split_k == 1) Y[(int64_t)i * ldy + (int64_t)(r0 + r) * ldy_inner] = __float2half_rn(acc[r][i]);
+              else partial[((int64_t)ks * m + i) * rows + r0 + r] = acc[r][i];
+            }
+          }
+        }
+      }
+    }
+  }
+}
+
+// Sums the split-K partials in slice order (deterministic) and rounds once.
+__global__ void gemv_splitk_reduce_kernel(const float* __restrict__ partial, __half* __restrict__ Y, int64_t ldy,
+                                          int64_t ldy_inner, int rows, int m, int split_k) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * m) return;
+  const int i = idx / rows, r = idx - i * rows;
+  float s = 0.0f;
+  for (int ks = 0; ks < split_k; ++ks) s += partial[((int64_t)ks * m + i) * rows + r];
+  Y[(int64_t)i * ldy + (int64_t)r * ldy_inner] = __float2half_rn(s);
+}
+
+size_t gemv_f16_workspace_bytes(int rows, int m, int split_k) {
+  return split_k > 1 ? (size_t)split_k * m * rows * sizeof(float) : 0;
+}
+
+int gemv_f16_default_split(int rows, int K, int sm_count) {
+  // Enough row groups to give every SM a few warps of work; otherwise cut K.
+  const int groups = (rows + 1) / 2;
+  int split = 1;
+  while (split < 16 && (int64_t)groups * split < (int64_t)sm_count * 16 && K / (split * 2) >= 2048) split *= 2;
+  return split;
+}
+
+template <int MRHS>
+static int launch_gemv(const __half* W, int64_t ldw, const __half* X, int64_t ldx, __half* Y, int64_t ldy,
+                       int64_t ldy_inner, float* partial, int rows, int K, int m, int split_k, int sm_count,
+                       cudaStream_t stream, int64_t* launches) {
+  constexpr int RPW = (MRHS <= 2) ? 2 : 1;
+  constexpr int UNROLL = (MRHS <= 4) ? 4 : 2;
+  const int row_groups = (rows + RPW - 1) / RPW;
+  const int warps = 8;
+  int blocks = (row_groups + warps - 1) / warps;
+  const int max_blocks = sm_count * 8;
+  if (blocks > max_blocks) blocks = max_blocks;
+  int k_per_split = (K + split_k - 1) / split_k;
+  k_per_split = (k_per_split + 255) / 256 * 256;
+  dim3 grid(blocks, split_k);
+  gemv_f16_kernel<MRHS, RPW, UNROLL><<<grid, warps * 32, 0, stream>>>(W, ldw, X, ldx, Y, ldy, ldy_inner, partial,
+                                                                      rows, K, m, split_k, k_per_split);
+  ++*launches;
+  if (split_k > 1) {
+    const int n = rows * m;
+    gemv_splitk_reduce_kernel<<<(n + 255) / 256, 256, 0, stream>>>(partial, Y, ldy, ldy_inner, rows, m, split_k);
+    ++*launches;
+  }
+  return cudaGetLastError() == cudaSuccess ? HELIX_OK : HELIX_ERR_CUDA;
+}
+
+int gemv_f16_launch(const helix_cfg_t* cfg, const void* W, int64_t ldw, const void* X, int64_t ldx, void* Y,
+                    int64_t ldy, int64_t ldy_inner, int rows, int K, int m, void* ws, size_t ws_bytes,
+                    int sm_count, cudaStream_t stream, int64_t* launches) {
+  if (!W || !X || !Y || rows <= 0 || K <= 0 || m <= 0 || m > 8) return HELIX_ERR_INVALID;
+  if (ldw == 0) ldw = K;
+  if (ldx == 0) ldx = K;
+  if (ldy == 0) ldy = rows;
+  if (ldy_inner == 0) ldy_inner = 1;
+  if ((K & 7) || (ldw & 7) || (ldx & 7) || (reinterpret_cast<uintptr_t>(W) & 15) ||
+      (reinterpret_cast<uintptr_t>(X) & 15))
+    return HELIX_ERR_ALIGN;
+  int split_k = (cfg && cfg->tile_m != 0 && cfg->split_k > 0) ? cfg->split_k
+                                                              : gemv_f16_default_split(rows, K, sm_count);
+  if (split_k > 1 && (K + split_k - 1) / split_k < 256) split_k = 1;
+  const size_t need = gemv_f16_workspace_bytes(rows, m, split_k);
+  if (need > 0 && (!ws || ws_bytes < need)) {
+    if (cfg && cfg->tile_m != 0 && cfg->split_k > 1) return HELIX_ERR_WORKSPACE;
+    split_k = 1;  // automatic choice falls back to the workspace-free variant
+  }
+  const __half* w = static_cast<const __half*>(W);
+  const __half* x = static_cast<const __half*>(X);
+  __half* y = static_cast<__half*>(Y);
+  float* part = static_cast<float*>(ws);
+  if (m == 1) return launch_gemv<1>(w, ldw, x, ldx, y, ldy, ldy_inner, part, rows, K, m, split_k, sm_count, stream, launches);
+  if (m == 2) return launch_gemv<2>(w, ldw, x, ldx, y, ldy, ldy_inner, part, rows, K, m, split_k, sm_count, stream, launches);
+  if (m <= 4) return launch_gemv<4>(w, ldw, x, ldx, y, ldy, ldy_inner, part, rows, K, m, split_k, sm_count, stream, launches);
+  return launch_gemv<8>(w, ldw, x, ldx, y, ldy, ldy_inner, part, rows, K, m, split_k, sm_count, stream, launches);
+}
+
+}  // namespace helix

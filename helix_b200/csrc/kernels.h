@@ -1,0 +1,40 @@
+// Internal launch interfaces between the kernel translation units and the C ABI layer.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/helix_b200.h"
+
+namespace helix {
+
+// ---- gemv_f16.cu
+size_t gemv_f16_workspace_bytes(int rows, int m, int split_k);
+int gemv_f16_default_split(int rows, int K, int sm_count);
+int gemv_f16_launch(const helix_cfg_t* cfg, const void* W, int64_t ldw, const void* X, int64_t ldx, void* Y,
+                    int64_t ldy, int64_t ldy_inner, int rows, int K, int m, void* ws, size_t ws_bytes,
+                    int sm_count, cudaStream_t stream, int64_t* launches);
+
+// ---- sgemm_f32.cu
+int sgemm_f32_num_configs();
+void sgemm_f32_get_config(int idx, helix_cfg_t* out);
+void sgemm_f32_default_config(int M, int N, int sm_count, helix_cfg_t* out);
+int sgemm_f32_launch(const helix_cfg_t* cfg, const float* A, int64_t lda, int trans_a, const float* B, int64_t ldb,
+                     float* C, int64_t ldc, int M, int N, int K, int sm_count, cudaStream_t stream,
+                     int64_t* launches);
+
+// ---- gemm_f16_tc.cu (tcgen05 GEMM and implicit-GEMM convolution)
+struct ConvGeom {
+  int NB, H, W, C, KO, R, S, stride, pad, Ho, Wo;
+};
+int gemm_f16_num_configs();
+void gemm_f16_get_config(int idx, helix_cfg_t* out);
+// Fills *out with the library's default choice for the problem.
+void gemm_f16_default_config(int M, int N, int K, int batch, int sm_count, bool conv, helix_cfg_t* out);
+size_t gemm_f16_workspace_bytes(const helix_cfg_t* cfg, int M, int N, int K, int batch);
+int gemm_f16_launch(const helix_cfg_t* cfg, const void* A, int64_t lda, const void* B, int64_t ldb, void* C,
+                    int64_t ldc, int M, int N, int K, int batch, int64_t sa, int64_t sb, int64_t sc, void* ws,
+                    size_t ws_bytes, int* status_dev, int sm_count, cudaStream_t stream, int64_t* launches);
+int conv_f16_launch(const helix_cfg_t* cfg, const void* x, const void* w, void* y, const ConvGeom& g, void* ws,
+                    size_t ws_bytes, int* status_dev, int sm_count, cudaStream_t stream, int64_t* launches);
+
+}  // namespace helix

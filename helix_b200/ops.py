@@ -1,0 +1,245 @@
+"""Operator front-end over the C ABI.  torch supplies device memory and streams only.
+
+These calls replace what the reference does by spawning a per-configuration
+executable and parsing its stdout (scripts/Ampere_FP16/Ampere_FP16_gemm.py
+:432-441, scripts/Ampere_FP16/Ampere_FP16_conv.py:431-446,
+scripts/Ampere_FP32/Ampere_FP32_gemm.py:101-107).  Layouts follow the reference
+kernels: fp16 GEMM takes A[M,K] and B stored [N,K]; fp32 GEMM takes A[M,K] (or
+K x M with ``trans_a``) and B[K,N].
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import Cfg, DevInfo, Launch, OP_CONV_F16, OP_GEMM_F16, OP_GEMM_F32, OP_GEMV_F16, check
+
+_status_words = {}
+_workspaces = {}
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if not t.is_cuda:
+            raise ValueError("helix_b200 operators take CUDA tensors only (there is no CPU path)")
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def status_word(device=None):
+    """Per-device int32 the kernels write HELIX_ERR_TIMEOUT into when a bounded wait runs out."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    if dev not in _status_words:
+        _status_words[dev] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{dev}")
+    return _status_words[dev]
+
+
+def check_status(device=None):
+    """Synchronising read of the status word; raises HelixError if a kernel reported a failure."""
+    w = status_word(device)
+    v = int(w.item())
+    if v != 0:
+        w.zero_()
+        raise _lib.HelixError(v, "device status word")
+
+
+def workspace(nbytes, device=None):
+    """Grow-only scratch buffer per device, reused across calls on the same stream."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    cur = _workspaces.get(dev)
+    if cur is None or cur.numel() < nbytes:
+        cur = torch.empty(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=f"cuda:{dev}")
+        _workspaces[dev] = cur
+    return cur
+
+
+def device_info(dev=-1):
+    info = DevInfo()
+    check(_lib.load().helix_device_info(dev, ctypes.byref(info)), "helix_device_info")
+    return info
+
+
+def configs(op):
+    lib = _lib.load()
+    out = []
+    for i in range(lib.helix_num_configs(op)):
+        c = Cfg()
+        if lib.helix_get_config(op, i, ctypes.byref(c)) == 0:
+            out.append(c)
+    return out
+
+
+def make_cfg(op, tile_m=128, tile_n=128, tile_k=64, stages=0, cta_group=1, split_k=1, swap_ab=0, raster=8,
+             thread_m=0, thread_n=0):
+    c = Cfg()
+    c.op, c.tile_m, c.tile_n, c.tile_k, c.stages = op, tile_m, tile_n, tile_k, stages
+    c.cta_group, c.split_k, c.swap_ab, c.raster, c.thread_m, c.thread_n = cta_group, split_k, swap_ab, raster, thread_m, thread_n
+    return c
+
+
+# ----------------------------------------------------------------------------- launch builders
+def _finish(launch, cfg, ws):
+    lib = _lib.load()
+    if cfg is not None:
+        launch.cfg = cfg
+    need = lib.helix_workspace_bytes(ctypes.byref(launch))
+    if need:
+        buf = ws if ws is not None else workspace(need)
+        if buf.numel() * buf.element_size() < need:
+            raise ValueError(f"workspace too small: need {need} bytes")
+        launch.ws = buf.data_ptr()
+        launch.ws_bytes = buf.numel() * buf.element_size()
+        launch._ws_ref = buf
+    return launch
+
+
+def launch_gemm_f16(a, b_nk, out, cfg=None, ws=None):
+    """A[M,K] (or [B,M,K]) x B[N,K] (or [B,N,K]) -> out[M,N] (or [B,M,N]), fp16."""
+    _require_cuda(a, b_nk, out)
+    assert a.dtype == b_nk.dtype == out.dtype == torch.float16
+    l = Launch()
+    l.op = OP_GEMM_F16
+    if a.dim() == 3:
+        assert a.stride(2) == 1 and b_nk.stride(2) == 1 and out.stride(2) == 1
+        l.batch, l.M, l.K = a.shape
+        l.N = b_nk.shape[1]
+        l.lda, l.ldb, l.ldc = a.stride(1), b_nk.stride(1), out.stride(1)
+        l.stride_a, l.stride_b, l.stride_c = a.stride(0), b_nk.stride(0), out.stride(0)
+    else:
+        assert a.stride(1) == 1 and b_nk.stride(1) == 1 and out.stride(1) == 1
+        l.batch = 1
+        l.M, l.K = a.shape
+        l.N = b_nk.shape[0]
+        l.lda, l.ldb, l.ldc = a.stride(0), b_nk.stride(0), out.stride(0)
+    assert b_nk.shape[-1] == l.K and tuple(out.shape[-2:]) == (l.M, l.N)
+    l.a, l.b, l.c = a.data_ptr(), b_nk.data_ptr(), out.data_ptr()
+    l._refs = (a, b_nk, out)
+    return _finish(l, cfg, ws)
+
+
+def launch_gemv_f16(w, x, out, cfg=None, ws=None, out_transposed=False):
+    """W[rows,K], X[m,K] (m <= 8) -> out[m,rows]; or out[rows,m] when ``out_transposed``."""
+    _require_cuda(w, x, out)
+    assert w.dtype == x.dtype == out.dtype == torch.float16
+    assert w.stride(1) == 1 and x.stride(1) == 1
+    l = Launch()
+    l.op = OP_GEMV_F16
+    l.N, l.K = w.shape
+    l.M = x.shape[0]
+    assert x.shape[1] == l.K
+    l.lda, l.ldb = w.stride(0), x.stride(0)
+    if out_transposed:
+        assert tuple(out.shape) == (l.N, l.M)
+        l.ldc, l.ldc_inner = out.stride(1), out.stride(0)
+    else:
+        assert tuple(out.shape) == (l.M, l.N)
+        l.ldc, l.ldc_inner = out.stride(0), out.stride(1)
+    l.a, l.b, l.c = w.data_ptr(), x.data_ptr(), out.data_ptr()
+    l._refs = (w, x, out)
+    return _finish(l, cfg, ws)
+
+
+def conv_out_hw(H, W, R, S, stride, pad):
+    return (H + 2 * pad - R) // stride + 1, (W + 2 * pad - S) // stride + 1
+
+
+def launch_conv2d_f16(x, w, out, stride, pad, cfg=None, ws=None):
+    """x[N,H,W,C], w[KO,R,S,C] -> out[N,Ho,Wo,KO], all contiguous fp16."""
+    _require_cuda(x, w, out)
+    assert x.dtype == w.dtype == out.dtype == torch.float16
+    assert x.is_contiguous() and w.is_contiguous() and out.is_contiguous()
+    N, H, W, C = x.shape
+    KO, R, S, C2 = w.shape
+    assert C == C2
+    Ho, Wo = conv_out_hw(H, W, R, S, stride, pad)
+    assert tuple(out.shape) == (N, Ho, Wo, KO)
+    l = Launch()
+    l.op = OP_CONV_F16
+    l.a, l.b, l.c = x.data_ptr(), w.data_ptr(), out.data_ptr()
+    for i, v in enumerate((N, H, W, C, KO, R, S, stride, pad)):
+        l.conv[i] = v
+    l._refs = (x, w, out)
+    return _finish(l, cfg, ws)
+
+
+def launch_gemm_f32(a, b, out, trans_a=False, cfg=None):
+    """A[M,K] (or [K,M] with trans_a) x B[K,N] -> out[M,N], fp32 FFMA."""
+    _require_cuda(a, b, out)
+    assert a.dtype == b.dtype == out.dtype == torch.float32
+    assert a.stride(1) == 1 and b.stride(1) == 1 and out.stride(1) == 1
+    l = Launch()
+    l.op = OP_GEMM_F32
+    if trans_a:
+        l.K, l.M = a.shape
+    else:
+        l.M, l.K = a.shape
+    assert b.shape[0] == l.K
+    l.N = b.shape[1]
+    assert tuple(out.shape) == (l.M, l.N)
+    l.lda, l.ldb, l.ldc = a.stride(0), b.stride(0), out.stride(0)
+    l.trans_a = int(trans_a)
+    l.a, l.b, l.c = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    l._refs = (a, b, out)
+    return _finish(l, cfg, None)
+
+
+def run(launch):
+    """Queue a prepared launch on torch's current stream."""
+    check(_lib.load().helix_launch(ctypes.byref(launch), ctypes.c_void_p(status_word().data_ptr()), _stream()),
+          "helix_launch")
+
+
+# ----------------------------------------------------------------------------- eager operators
+def gemm_f16(a, b_nk, out=None, cfg=None):
+    shape = (*a.shape[:-1], b_nk.shape[-2])
+    if out is None:
+        out = torch.empty(shape, dtype=torch.float16, device=a.device)
+    run(launch_gemm_f16(a, b_nk, out, cfg))
+    return out
+
+
+def gemv_f16(w, x, out=None, cfg=None):
+    if out is None:
+        out = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float16, device=w.device)
+    run(launch_gemv_f16(w, x, out, cfg))
+    return out
+
+
+def conv2d_f16_nhwc(x, w, stride=1, pad=0, out=None, cfg=None):
+    if out is None:
+        Ho, Wo = conv_out_hw(x.shape[1], x.shape[2], w.shape[1], w.shape[2], stride, pad)
+        out = torch.empty((x.shape[0], Ho, Wo, w.shape[0]), dtype=torch.float16, device=x.device)
+    run(launch_conv2d_f16(x, w, out, stride, pad, cfg))
+    return out
+
+
+def gemm_f32(a, b, trans_a=False, out=None, cfg=None):
+    M = a.shape[1] if trans_a else a.shape[0]
+    if out is None:
+        out = torch.empty((M, b.shape[1]), dtype=torch.float32, device=a.device)
+    run(launch_gemm_f32(a, b, out, trans_a, cfg))
+    return out
+
+
+# ----------------------------------------------------------------------------- timing
+def time_launches(launches, warmup=3, iters=20, use_graph=False):
+    """Seconds per launch (average), plus (min, max) seconds per round over the list.
+
+    The list is walked round-robin, so passing launches over distinct operand
+    buffers whose total footprint exceeds the L2 gives HBM-resident timings.
+    """
+    arr = (Launch * len(launches))()
+    for i, l in enumerate(launches):
+        ctypes.memmove(ctypes.byref(arr[i]), ctypes.byref(l), ctypes.sizeof(Launch))
+    avg, mn, mx = ctypes.c_double(), ctypes.c_double(), ctypes.c_double()
+    torch.cuda.synchronize()
+    check(_lib.load().helix_time_launches(arr, len(launches), warmup, iters, int(use_graph),
+                                          ctypes.byref(avg), ctypes.byref(mn), ctypes.byref(mx)),
+          "helix_time_launches")
+    return avg.value, mn.value, mx.value
+
+
+def launch_count():
+    return int(_lib.load().helix_launch_count())

@@ -1,0 +1,184 @@
+/*
+ * helix_b200.h -- C ABI of libhelix_b200.so.
+ *
+ * The Helix reference has no FFI: its host<->kernel boundary is "spawn an nvcc
+ * built executable with `M N K` on argv and parse one stdout line"
+ * (scripts/Ampere_FP16/Ampere_FP16_gemm.py:432-441, src_template/Ampere_FP16/
+ * gemm.cu:661-692).  Each entry point below replaces one of those executables
+ * (or the Python loop around it) with an in-process call; the comment above
+ * every declaration names the reference interface it stands in for.
+ *
+ * Conventions
+ *   - every function returns HELIX_OK (0) or a negative helix_status_t; nothing
+ *     throws, exits or traps the GPU;
+ *   - the caller owns every buffer (inputs, outputs, workspace and the optional
+ *     4-byte device status word); pointers are device pointers unless the name
+ *     says host;
+ *   - work is queued on the current CUDA device and on the stream passed as
+ *     `stream` (a cudaStream_t cast to void*; NULL = default stream), and is
+ *     asynchronous except for the helix_time_* and helix_*_host functions;
+ *   - `status_dev`, when not NULL, points to a zero-initialised int in device
+ *     memory; a kernel whose bounded wait ran out stores HELIX_ERR_TIMEOUT
+ *     there and returns instead of spinning for ever.
+ */
+#ifndef HELIX_B200_H_
+#define HELIX_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum helix_status {
+  HELIX_OK = 0,
+  HELIX_ERR_INVALID = -1,     /* bad argument (negative extent, NULL pointer, unknown op) */
+  HELIX_ERR_ALIGN = -2,       /* pointer or leading dimension violates the 16-byte rule   */
+  HELIX_ERR_WORKSPACE = -3,   /* workspace missing or smaller than helix_workspace_bytes  */
+  HELIX_ERR_CUDA = -4,        /* a CUDA runtime / driver call failed                      */
+  HELIX_ERR_TIMEOUT = -5,     /* a bounded device-side wait ran out (status word only)    */
+  HELIX_ERR_UNSUPPORTED = -6, /* configuration not built into the library                 */
+  HELIX_ERR_NODEVICE = -7     /* no sm_100 device is current                              */
+} helix_status_t;
+
+typedef enum helix_op {
+  HELIX_OP_GEMM_F16 = 0, /* tcgen05 tensor-core GEMM, fp16 in, fp32 accumulate, fp16 out  */
+  HELIX_OP_GEMV_F16 = 1, /* memory-bound SIMT GEMV for 1..8 right-hand sides              */
+  HELIX_OP_CONV_F16 = 2, /* implicit-GEMM NHWC convolution on the same tensor-core path   */
+  HELIX_OP_GEMM_F32 = 3  /* SIMT FFMA GEMM, true fp32                                     */
+} helix_op_t;
+
+/* Replaces the queried-nowhere literal `108` (A100 SM count) of the reference's
+ * cost models (scripts/Ampere_FP16/Ampere_FP16_gemm.py:425 and 11 more sites). */
+typedef struct helix_devinfo {
+  int sm_count;
+  int cc_major, cc_minor;
+  int clock_khz, mem_clock_khz;
+  int64_t l2_bytes;
+  int64_t smem_per_sm;
+  int64_t smem_per_block_optin;
+  int64_t total_mem;
+  char name[64];
+} helix_devinfo_t;
+
+/* One point of the search space.  Stands in for the `-D` macro tuple that names a
+ * reference executable: (K_STAGE, BLOCK_ROWS, BLOCK_COLS, WARP_ROWS, WARP_COLS,
+ * splitK) for fp16 (scripts/Ampere_FP16/build_Ampere_FP16.py:41-62) and
+ * (BM, BN, BK, TM, TN, ...) for fp32 (scripts/Ampere_FP32/build_Ampere_FP32.py:37-63).
+ * A zeroed struct (tile_m == 0) asks the library to choose. */
+typedef struct helix_cfg {
+  int op;        /* helix_op_t                                                       */
+  int tile_m;    /* CTA tile rows   (GEMM_F16/CONV: 128; GEMM_F32: 32..128)          */
+  int tile_n;    /* CTA tile cols   (GEMM_F16/CONV: 16..256, multiple of 16)         */
+  int tile_k;    /* K slab per stage (GEMM_F16/CONV: 64; GEMM_F32: 8 or 16)          */
+  int stages;    /* shared-memory ring depth (0 = as many as fit)                    */
+  int cta_group; /* 1 = one CTA per tile, 2 = CTA pair sharing one 256-row tile      */
+  int split_k;   /* >= 1; > 1 needs a workspace                                      */
+  int swap_ab;   /* 1 = put N on the 128-row UMMA axis (skinny M)                    */
+  int raster;    /* M-blocks per rasterisation group (L2 reuse), 0 = default         */
+  int thread_m;  /* GEMM_F32: per-thread register block rows                         */
+  int thread_n;  /* GEMM_F32: per-thread register block cols                         */
+  int reserved[5];
+} helix_cfg_t;
+
+/* A fully described launch; the tagged union the timing entry point iterates. */
+typedef struct helix_launch {
+  int op;            /* helix_op_t */
+  helix_cfg_t cfg;   /* cfg.tile_m == 0: library default */
+  const void* a;     /* GEMM: A[M,K]   GEMV: W[rows=N,K]   CONV: x[N,H,W,C]   */
+  const void* b;     /* GEMM: B[N,K] (f16) / B[K,N] (f32)  GEMV: X[m=M,K]  CONV: w[KO,R,S,C] */
+  void* c;           /* GEMM: C[M,N]   GEMV: Y             CONV: y[N,Ho,Wo,KO] */
+  int64_t lda, ldb, ldc; /* leading dimensions in elements (0 = packed)        */
+  int M, N, K;
+  int batch;             /* strided-batch count (GEMM_F16), >= 1               */
+  int64_t stride_a, stride_b, stride_c; /* batch strides in elements           */
+  int conv[9];           /* CONV: N, H, W, C, KO, R, S, stride, pad            */
+  int trans_a;           /* GEMM_F32: 1 = A is handed over as K x M            */
+  int64_t ldc_inner;     /* GEMV: element stride between rows of W in Y (0 = 1) */
+  void* ws;              /* workspace or NULL                                   */
+  size_t ws_bytes;
+} helix_launch_t;
+
+/* Library version (major*100 + minor). */
+int helix_version(void);
+/* Human-readable text of a status code. */
+const char* helix_status_string(int status);
+
+/* Device facts for the cost model; replaces the literal 108 (see helix_devinfo_t). */
+int helix_device_info(int dev, helix_devinfo_t* out);
+
+/* Enumerate the configurations compiled into the library.  Replaces listing
+ * build/bin_fp16/gemm_<K_STAGE>_<BR>_<BC>_<WR>_<WC> and build/bin_fp32/sgemm_*
+ * (scripts/Ampere_FP16/build_Ampere_FP16.py:41-70, scripts/Ampere_FP32/
+ * build_Ampere_FP32.py:37-63). */
+int helix_num_configs(int op);
+int helix_get_config(int op, int idx, helix_cfg_t* out);
+
+/* The configuration the library would pick for `launch` when launch->cfg is zeroed: the built-in
+ * analytic stand-in for cost_model() (scripts/Ampere_FP16/Ampere_FP16_gemm.py:420-430), used when
+ * no profiled dictionary is at hand. */
+int helix_default_config(const helix_launch_t* launch, helix_cfg_t* out);
+
+/* Bytes of workspace a launch needs (0 when none). */
+size_t helix_workspace_bytes(const helix_launch_t* launch);
+
+/* Queue one launch.  Generic form of the four typed entry points below. */
+int helix_launch(const helix_launch_t* launch, void* status_dev, void* stream);
+
+/* C[M,N] (fp16) = A[M,K] (fp16, row-major) * B[N,K]^T (fp16, row-major = column-major KxN),
+ * fp32 accumulate.  Replaces build/bin_fp16/gemm_* and gemm_splitK_*
+ * (src_template/Ampere_FP16/gemm.cu:120-558, gemm_splitK.cu:120-531) as invoked by
+ * get_Ampere_FP16_gemm_Helix_result (scripts/Ampere_FP16/Ampere_FP16_gemm.py:432-441).
+ * No host-side padding of M and N is needed.  lda/ldb multiples of 8, 16-byte aligned bases. */
+int helix_gemm_f16(const helix_cfg_t* cfg, const void* A, int64_t lda, const void* B, int64_t ldb,
+                   void* C, int64_t ldc, int M, int N, int K,
+                   int batch, int64_t stride_a, int64_t stride_b, int64_t stride_c,
+                   void* ws, size_t ws_bytes, void* status_dev, void* stream);
+
+/* Y[i,r] (fp16) = sum_k W[r,k] * X[i,k], i < m <= 8, fp32 accumulate; element (i,r) is
+ * stored at Y[i*ldy + r*ldy_inner].  Replaces build/bin_fp16/gemv and gemv_splitK
+ * (src_template/Ampere_FP16/gemv.cu:151-252, gemv_splitK.cu:153-260). */
+int helix_gemv_f16(const helix_cfg_t* cfg, const void* W, int64_t ldw, const void* X, int64_t ldx,
+                   void* Y, int64_t ldy, int64_t ldy_inner, int rows, int K, int m,
+                   void* ws, size_t ws_bytes, void* status_dev, void* stream);
+
+/* y[N,Ho,Wo,KO] = conv2d(x[N,H,W,C], w[KO,R,S,C]), zero padding, fp32 accumulate, fp16 in/out,
+ * as one implicit GEMM with M = N*Ho*Wo, N = KO, K = R*S*C.  Replaces the im2col executable plus
+ * GEMM executable pair of get_Ampere_FP16_conv_Helix_result (scripts/Ampere_FP16/
+ * Ampere_FP16_conv.py:431-446, src_template/Ampere_FP16/im2col.cu:37-97).  C multiple of 8. */
+int helix_conv2d_f16_nhwc(const helix_cfg_t* cfg, const void* x, const void* w, void* y,
+                          int N, int H, int W, int C, int KO, int R, int S, int stride, int pad,
+                          void* ws, size_t ws_bytes, void* status_dev, void* stream);
+
+/* C[M,N] = A * B in true fp32 (FFMA only, k ascending, no TF32).  B is K x N row-major; A is
+ * M x K row-major (trans_a = 0, the x86 template's layout, scripts/x86_CPU/profile_x86_CPU.py:27-29)
+ * or K x M (trans_a = 1, what src_template/Ampere_FP32/sgemm.cu:138 is handed).  Replaces
+ * build/bin_fp32/sgemm_* (sgemm.cu:97-350; scripts/Ampere_FP32/Ampere_FP32_gemm.py:101-107). */
+int helix_gemm_f32(const helix_cfg_t* cfg, const float* A, int64_t lda, int trans_a,
+                   const float* B, int64_t ldb, float* C, int64_t ldc, int M, int N, int K,
+                   void* status_dev, void* stream);
+
+/* Time `count` launches round-robin: `warmup` untimed rounds, then `iters` timed rounds between
+ * two CUDA events on a private stream; *avg_s is seconds per launch.  Distinct buffers per
+ * entry give the rotating-operand protocol for memory-bound shapes.  Replaces the cudaEvent
+ * loops of the reference harnesses (gemm.cu:622-660: 10 warm-up + 10 timed launches).
+ * use_graph != 0 captures one round into a CUDA graph first (for kernels of a few microseconds). */
+int helix_time_launches(const helix_launch_t* list, int count, int warmup, int iters, int use_graph,
+                        double* avg_s, double* min_round_s, double* max_round_s);
+
+/* Host-buffer convenience wrappers (synchronous: H2D copy, launch, D2H copy).  They are what the
+ * end-to-end benchmark leg times and what a caller without device memory of its own would bind. */
+int helix_gemm_f16_host(const void* A, const void* B, void* C, int M, int N, int K);
+int helix_gemv_f16_host(const void* W, const void* X, void* Y, int rows, int K, int m);
+int helix_gemm_f32_host(const float* A, const float* B, float* C, int M, int N, int K);
+int helix_conv2d_f16_nhwc_host(const void* x, const void* w, void* y, int N, int H, int W, int C,
+                               int KO, int R, int S, int stride, int pad);
+
+/* Number of kernel launches this process has queued through the library (all ops). */
+int64_t helix_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HELIX_B200_H_ */

@@ -1,0 +1,166 @@
+"""GPU parity: tcgen05 fp16 GEMM (fp32 accumulate) through the C ABI vs the CPU oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helix_b200 import datagen, ops
+from helix_b200._lib import OP_GEMM_F16
+from tests import util
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _run(a, b_nk, cfg=None):
+    ad, bd = torch.from_numpy(a).cuda(), torch.from_numpy(b_nk).cuda()
+    shape = (*a.shape[:-1], b_nk.shape[-2])
+    out = torch.full(shape, float("nan"), dtype=torch.float16, device="cuda")
+    ops.run(ops.launch_gemm_f16(ad, bd, out, cfg))
+    torch.cuda.synchronize()
+    ops.check_status()
+    return out.cpu().numpy()
+
+
+def _cfg(bn, split_k=1, swap=0, stages=0):
+    return ops.make_cfg(OP_GEMM_F16, tile_m=128, tile_n=bn, tile_k=64, stages=stages, split_k=split_k, swap_ab=swap)
+
+
+def test_single_tile_identity_known_answer():
+    """One 128x128x64 tile with B = I: the output must reproduce A exactly (checks descriptors,
+    swizzle, TMEM lane mapping and the epilogue addressing without any rounding)."""
+    rng = np.random.default_rng(0)
+    a = rng.standard_normal((128, 64)).astype(np.float16)
+    b = np.zeros((128, 64), np.float16)
+    b[np.arange(64), np.arange(64)] = 1
+    got = _run(a, b, _cfg(128))
+    assert np.array_equal(got[:, :64], a)
+    assert np.all(got[:, 64:] == 0)
+
+
+def test_one_hot_rows_and_k_steps():
+    """Each row of A selects one k: exercises all four K=16 steps of a slab and several slabs."""
+    K = 256
+    a = np.zeros((128, K), np.float16)
+    a[np.arange(128), (np.arange(128) * 37) % K] = 1
+    rng = np.random.default_rng(1)
+    b = rng.standard_normal((256, K)).astype(np.float16)
+    got = _run(a, b, _cfg(256))
+    want = b[:, (np.arange(128) * 37) % K].T
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("bn", [16, 32, 64, 128, 256])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 512), (200, 136, 72), (1, 8, 8), (300, 1000, 264)])
+def test_gemm_tiles_and_edges(oracle, shape, bn):
+    M, N, K = shape
+    a, b = datagen.c3_gemm(M, N, K, seed=2)
+    got = _run(a, b, _cfg(bn))
+    _, ref32 = oracle.hgemm_naive(a, b)
+    util.assert_f16_close(got, ref32, f"gemm {shape} bn={bn}")
+
+
+@pytest.mark.parametrize("bn,shape", [(16, (16, 1100, 512)), (32, (24, 300, 136)), (128, (128, 512, 1024)), (64, (5, 129, 64))])
+def test_gemm_swap_ab(oracle, bn, shape):
+    M, N, K = shape
+    a, b = datagen.c3_gemm(M, N, K, seed=3)
+    got = _run(a, b, _cfg(bn, swap=1))
+    _, ref32 = oracle.hgemm_naive(a, b)
+    util.assert_f16_close(got, ref32, f"swap gemm {shape} bn={bn}")
+
+
+@pytest.mark.parametrize("split,swap", [(2, 0), (4, 0), (3, 1), (8, 1)])
+def test_gemm_split_k(oracle, split, swap):
+    M, N, K = (48, 400, 2048)
+    a, b = datagen.c3_gemm(M, N, K, seed=4)
+    cfg = _cfg(64 if swap else 128, split_k=split, swap=swap)
+    got = _run(a, b, cfg)
+    again = _run(a, b, cfg)
+    assert np.array_equal(got.view(np.uint16), again.view(np.uint16)), "split-K reduction must be deterministic"
+    _, ref32 = oracle.hgemm_naive(a, b)
+    util.assert_f16_close(got, ref32, f"split_k={split} swap={swap}")
+
+
+def test_gemm_many_tiles_persistent_and_stage_wrap(oracle):
+    """More tiles than SMs and more K slabs than stages: several accumulator and ring phases."""
+    M, N, K = 2048, 2304, 1024
+    a, b = datagen.c3_gemm(M, N, K, seed=5)
+    _, ref32 = oracle.hgemm_fast(a, b)
+    for bn, stages in [(128, 0), (256, 2), (64, 3)]:
+        got = _run(a, b, _cfg(bn, stages=stages))
+        util.assert_f16_close(got, ref32, f"persistent bn={bn} stages={stages}")
+
+
+def test_gemm_strided_batch(oracle):
+    """Batched QK^T-like shape: 6 x (160, 96, 64)."""
+    a, b = datagen.c3_gemm(160, 96, 64, seed=6, batch=6)
+    got = _run(a, b)
+    for i in range(6):
+        _, ref32 = oracle.hgemm_naive(a[i], b[i])
+        util.assert_f16_close(got[i], ref32, f"batch {i}")
+
+
+def test_gemm_default_config_on_sweep_shapes_reduced(oracle):
+    """The library's own choice (incl. swap / split-K) on scaled-down versions of the sweep shapes."""
+    for (M, N, K) in [(512, 512, 512), (16, 1376, 512), (128, 512, 1376), (256, 1792, 512)]:
+        a, b = datagen.c3_gemm(M, N, K, seed=2)
+        got = _run(a, b)
+        _, ref32 = oracle.hgemm_fast(a, b)
+        util.assert_f16_close(got, ref32, f"default {M}x{N}x{K}")
+
+
+def test_gemm_golden_vectors_from_reference_loop():
+    g = np.load(os.path.join(GOLD, "hgemm_ref.npz"))
+    for n in sorted({k.split("_a")[0] for k in g.files if k.endswith("_a")}):
+        a, b_kn = g[n + "_a"], g[n + "_b_kn"]
+        if a.shape[1] % 8:
+            continue  # leading dimension rule (16 bytes); odd K goes through the padded host entry point
+        got = _run(a, np.ascontiguousarray(b_kn.T))
+        util.assert_f16_close(got, g[n + "_c"].astype(np.float32), n)
+
+
+def test_gemm_host_entry_point_pads_odd_k(oracle, lib):
+    import ctypes
+    g = np.load(os.path.join(GOLD, "hgemm_ref.npz"))
+    a, b_kn = g["h1_a"], g["h1_b_kn"]           # K = 129
+    b_nk = np.ascontiguousarray(b_kn.T)
+    c = np.empty((a.shape[0], b_nk.shape[0]), np.float16)
+    rc = lib.helix_gemm_f16_host(a.ctypes.data_as(ctypes.c_void_p), b_nk.ctypes.data_as(ctypes.c_void_p),
+                                 c.ctypes.data_as(ctypes.c_void_p), a.shape[0], b_nk.shape[0], a.shape[1])
+    assert rc == 0
+    util.assert_f16_close(c, g["h1_c"].astype(np.float32), "host entry, K=129")
+
+
+def test_gemm_rejects_misaligned_leading_dimension():
+    a = torch.zeros((16, 20), dtype=torch.float16, device="cuda")
+    b = torch.zeros((16, 20), dtype=torch.float16, device="cuda")
+    with pytest.raises(Exception) as e:
+        ops.gemm_f16(a, b)
+    assert "-2" in str(e.value)
+
+
+@pytest.mark.parametrize("shape", datagen.C3_SHAPES)
+def test_gemm_full_size_linearity_property(shape):
+    """At the benchmark's full sizes the oracle is too slow; use size-independent properties:
+    rows of A that are one-hot must reproduce columns of B exactly, and scaling A by 2 (exact in
+    fp16) must scale C by exactly 2."""
+    M, N, K = shape
+    a, b = datagen.c3_gemm(M, N, K, seed=2)
+    sel = (np.arange(M) * 7919) % K
+    a[::5] = 0
+    a[np.arange(0, M, 5), sel[::5]] = 1
+    ad, bd = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    c1 = ops.gemm_f16(ad, bd)
+    c2 = ops.gemm_f16(ad * 2, bd)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(c1[::5], bd[:, torch.from_numpy(sel[::5]).cuda()].t().contiguous())
+    assert torch.equal(c2, c1 * 2)
+    # spot-check random rows against an fp64 host dot product
+    rng = np.random.default_rng(0)
+    rows = rng.integers(0, M, 4)
+    cols = rng.integers(0, N, 64)
+    want = a[rows].astype(np.float64) @ b[cols].astype(np.float64).T
+    got = c1[torch.from_numpy(rows).cuda()][:, torch.from_numpy(cols).cuda()].cpu().numpy()
+    util.assert_f16_close(got, want, f"full-size spot check {shape}")
