@@ -36,12 +36,13 @@ class Cfg(ctypes.Structure):
     _fields_ = [("op", ctypes.c_int), ("tile_m", ctypes.c_int), ("tile_n", ctypes.c_int),
                 ("tile_k", ctypes.c_int), ("stages", ctypes.c_int), ("cta_group", ctypes.c_int),
                 ("split_k", ctypes.c_int), ("swap_ab", ctypes.c_int), ("raster", ctypes.c_int),
-                ("thread_m", ctypes.c_int), ("thread_n", ctypes.c_int), ("reserved", ctypes.c_int * 5)]
+                ("thread_m", ctypes.c_int), ("thread_n", ctypes.c_int), ("load_group", ctypes.c_int),
+                ("reserved", ctypes.c_int * 4)]
 
     def key(self):
         """Hashable identity used as the prof_dict key."""
         return (self.op, self.tile_m, self.tile_n, self.tile_k, self.stages, self.cta_group,
-                self.split_k, self.swap_ab)
+                self.split_k, self.swap_ab, self.load_group)
 
     def copy(self):
         c = Cfg()

@@ -17,8 +17,9 @@
 //     (or store fp32 partials for split-K, reduced in slice order by a second kernel);
 //   * swap_ab puts the large N extent on the 128-row UMMA axis when M is skinny.
 // For convolution the A-side tile is gathered by 128 producer threads with 16-byte zero-filling
-// cp.async (one output pixel per thread, K axis ordered (r, s, c)), written in the same swizzled
-// layout the TMA would produce, and published to the tensor core after fence.proxy.async.
+// cp.async (8 lanes per output pixel, K axis ordered (r, s, c)), written in the same swizzled
+// layout the TMA would produce; each thread's arrival on the stage barrier fires when its copies
+// land, and the MMA thread issues fence.proxy.async before the tensor core reads the tile.
 //
 // Every mbarrier wait is bounded (see mbar_wait); there is no cluster launch and no multicast.
 #include <cuda.h>
@@ -35,7 +36,6 @@ constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kATileBytes = kBM * kBK * 2;  // 16 KiB
 constexpr int kConvTableEntries = 4096;     // 8-channel chunks of the K axis (K <= 32768)
-constexpr int kCpAsyncLag = 2;              // cp.async groups in flight per producer thread
 
 struct GemmParams {
   __half* C;
@@ -48,6 +48,7 @@ struct GemmParams {
   int total_tiles;
   int raster;
   int stages;
+  int load_group;  // K slabs the TMA producer requests back to back (DRAM page locality)
   int* status;
   // convolution only
   const __half* x;
@@ -158,41 +159,64 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           const TileCoord tc = decode_tile(p, t);
           const int kb0 = tc.ks * p.kb_per_split;
           const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
-          for (int kb = kb0; kb < kb1; ++kb) {
-            ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status);
+          for (int kb = kb0; kb < kb1 && ok; kb += p.load_group) {
+            // Wait for a whole group of free stages first, then request the group's slabs back to
+            // back: every row then has load_group * 128 contiguous bytes in flight at once.
+            const int gcount = min(p.load_group, kb1 - kb);
+            int s2 = stage;
+            uint32_t ph2 = phase;
+            for (int g = 0; g < gcount && ok; ++g) {
+              ok = mbar_wait(&empty_bar[s2], ph2 ^ 1, abort_flag, p.status);
+              if (++s2 == stages) { s2 = 0; ph2 ^= 1; }
+            }
             if (!ok) break;
-            mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
-            tma_load_3d(sA + (size_t)stage * kATileBytes, &tmap_a, &full_bar[stage], kb * kBK, tc.m_blk * kBM, tc.b);
-            tma_load_3d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, &full_bar[stage], kb * kBK, tc.n_blk * BN,
-                        tc.b);
-            if (++stage == stages) { stage = 0; phase ^= 1; }
+            for (int g = 0; g < gcount; ++g) {
+              mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
+              tma_load_3d(sA + (size_t)stage * kATileBytes, &tmap_a, &full_bar[stage], (kb + g) * kBK,
+                          tc.m_blk * kBM, tc.b);
+              tma_load_3d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, &full_bar[stage], (kb + g) * kBK,
+                          tc.n_blk * BN, tc.b);
+              if (++stage == stages) { stage = 0; phase ^= 1; }
+            }
           }
         }
       }
     } else {
-      const int row = threadIdx.x;  // 0..127: one output pixel of the tile per thread
+      // Lane mapping: 8 consecutive lanes fetch the 8 16-byte chunks of one pixel's 128-byte K
+      // slab, so one warp instruction touches 4 pixel rows = 4 cache lines (coalesced), and
+      // writes 4 full 128-byte rows of the swizzled tile (bank-conflict free).  Warp w owns
+      // rows [32w, 32w+32) of the tile in 8 passes; a thread keeps one chunk column (j) and
+      // the window origin of its 8 pixels in registers.
+      const int pw = threadIdx.x >> 5;       // producer warp 0..3
+      const int j = lane & 7;                // 16-byte chunk of the 128-byte slab
+      const int sub = lane >> 3;             // row within a pass, 0..3
       const int HoWo = p.g.Ho * p.g.Wo;
       const int chunks = p.K >> 3;
+      constexpr int kInvalid = -(1 << 20);   // window origin that fails every bounds check
       int stage = 0;
       uint32_t phase = 0;
-      int issued = 0;       // k-blocks whose copies this thread has committed
-      int published = 0;    // k-blocks this thread has arrived for
-      int pub_stage = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
         const TileCoord tc = decode_tile(p, t);
-        const int m = tc.m_blk * kBM + row;
-        const bool valid_m = m < p.PM;
-        int n_img = 0, hi0 = 0, wi0 = 0;
-        if (valid_m) {
-          n_img = m / HoWo;
-          const int rem = m - n_img * HoWo;
-          const int ho = rem / p.g.Wo;
-          const int wo = rem - ho * p.g.Wo;
-          hi0 = ho * p.g.stride - p.g.pad;
-          wi0 = wo * p.g.stride - p.g.pad;
+        int hi0[8], wi0[8];
+        int64_t img_off[8];
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int m = tc.m_blk * kBM + pw * 32 + it * 4 + sub;
+          if (m < p.PM) {
+            const int n_img = m / HoWo;
+            const int rem = m - n_img * HoWo;
+            const int ho = rem / p.g.Wo;
+            const int wo = rem - ho * p.g.Wo;
+            hi0[it] = ho * p.g.stride - p.g.pad;
+            wi0[it] = wo * p.g.stride - p.g.pad;
+            img_off[it] = (int64_t)n_img * p.g.H * p.g.W * p.g.C;
+          } else {
+            hi0[it] = kInvalid;
+            wi0[it] = kInvalid;
+            img_off[it] = 0;
+          }
         }
-        const __half* xb = p.x + (int64_t)n_img * p.g.H * p.g.W * p.g.C;
         const int kb0 = tc.ks * p.kb_per_split;
         const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -202,40 +226,27 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             mbar_arrive_expect_tx(&full_bar[stage], L::kBTileBytes);
             tma_load_3d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, &full_bar[stage], kb * kBK, tc.n_blk * BN, 0);
           }
-          const uint32_t dst_row = smem_u32(sA + (size_t)stage * kATileBytes) + row * 128;
+          const int kc = kb * 8 + j;
+          const bool k_ok = kc < chunks;
+          const uint32_t e = k_ok ? conv_tab[kc] : 0u;
+          const int dr = (int)(e >> 24), ds = (int)((e >> 16) & 0xFF), c0 = (int)(e & 0xFFFF);
+          const uint32_t tile_base = smem_u32(sA + (size_t)stage * kATileBytes);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int kc = kb * 8 + j;
-            bool valid = valid_m && kc < chunks;
-            const __half* src = p.x;
-            if (valid) {
-              const uint32_t e = conv_tab[kc];
-              const int hi = hi0 + (int)(e >> 24);
-              const int wi = wi0 + (int)((e >> 16) & 0xFF);
-              valid = hi >= 0 && hi < p.g.H && wi >= 0 && wi < p.g.W;
-              if (valid) src = xb + ((int64_t)hi * p.g.W + wi) * p.g.C + (e & 0xFFFF);
-            }
-            cp_async_16_zfill(dst_row + ((j ^ (row & 7)) << 4), src, valid);
+          for (int it = 0; it < 8; ++it) {
+            const int row = pw * 32 + it * 4 + sub;
+            const int hi = hi0[it] + dr;
+            const int wi = wi0[it] + ds;
+            const bool valid = k_ok && hi >= 0 && hi < p.g.H && wi >= 0 && wi < p.g.W;
+            const __half* src = valid ? p.x + img_off[it] + ((int64_t)hi * p.g.W + wi) * p.g.C + c0 : p.x;
+            cp_async_16_zfill(tile_base + row * 128 + ((j ^ (row & 7)) << 4), src, valid);
           }
-          cp_async_commit();
-          ++issued;
-          if (issued - published > kCpAsyncLag) {
-            cp_async_wait<kCpAsyncLag>();
-            fence_proxy_async_smem();
-            mbar_arrive(&full_bar[pub_stage]);
-            ++published;
-            if (++pub_stage == stages) pub_stage = 0;
-          }
+          // The barrier receives this thread's arrival when the copies above have landed; the
+          // thread itself never blocks on them, so all stages of the ring stay in flight.
+          cp_async_mbar_arrive_noinc(&full_bar[stage]);
           if (++stage == stages) { stage = 0; phase ^= 1; }
         }
       }
-      cp_async_wait<0>();
-      fence_proxy_async_smem();
-      while (published < issued) {
-        mbar_arrive(&full_bar[pub_stage]);
-        ++published;
-        if (++pub_stage == stages) pub_stage = 0;
-      }
+      cp_async_wait<0>();  // nothing of this thread's is in flight when the CTA tears down
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
@@ -257,6 +268,9 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status);
           if (!ok) break;
+          // The gathered A tile was written through the generic proxy (cp.async); order those
+          // writes, now visible through the barrier, before the tensor core's async-proxy reads.
+          if (CONV) fence_proxy_async_smem();
           tc_fence_after_sync();
           const uint64_t da = umma_desc_sw128(smem_u32(sA + (size_t)stage * kATileBytes));
           const uint64_t db = umma_desc_sw128(smem_u32(sB + (size_t)stage * L::kBTileBytes));
@@ -524,7 +538,8 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
   p.raster = cfg.raster > 0 ? cfg.raster : 8;
   const int smax = max_stages(bn, conv);
   p.stages = cfg.stages > 0 ? std::min(cfg.stages, smax) : smax;
-  if (p.stages < (conv ? kCpAsyncLag + 2 : 2)) return HELIX_ERR_UNSUPPORTED;
+  if (p.stages < (conv ? 3 : 2)) return HELIX_ERR_UNSUPPORTED;
+  p.load_group = std::max(1, std::min(cfg.load_group > 0 ? cfg.load_group : 1, p.stages / 2));
   const bool partial = p.split_k > 1;
   if (partial) {
     const size_t need = (size_t)p.split_k * p.batch * (size_t)p.PM * p.PN * sizeof(float);

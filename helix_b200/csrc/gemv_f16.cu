@@ -125,12 +125,10 @@ int gemv_f16_default_split(int rows, int K, int sm_count) {
   return split;
 }
 
-template <int MRHS>
+template <int MRHS, int RPW, int UNROLL>
 static int launch_gemv(const __half* W, int64_t ldw, const __half* X, int64_t ldx, __half* Y, int64_t ldy,
                        int64_t ldy_inner, float* partial, int rows, int K, int m, int split_k, int sm_count,
                        cudaStream_t stream, int64_t* launches) {
-  constexpr int RPW = (MRHS <= 2) ? 2 : 1;
-  constexpr int UNROLL = (MRHS <= 4) ? 4 : 2;
   const int row_groups = (rows + RPW - 1) / RPW;
   const int warps = 8;
   int blocks = (row_groups + warps - 1) / warps;
@@ -148,6 +146,26 @@ static int launch_gemv(const __half* W, int64_t ldw, const __half* X, int64_t ld
     ++*launches;
   }
   return cudaGetLastError() == cudaSuccess ? HELIX_OK : HELIX_ERR_CUDA;
+}
+
+// (rows per warp, 16-byte loads in flight per row and thread) variants compiled in.
+template <int MRHS>
+static int launch_gemv_variant(int rpw, int unroll, const __half* W, int64_t ldw, const __half* X, int64_t ldx,
+                               __half* Y, int64_t ldy, int64_t ldy_inner, float* partial, int rows, int K, int m,
+                               int split_k, int sm_count, cudaStream_t stream, int64_t* launches) {
+#define HELIX_GEMV_CASE(R, U)                                                                                 \
+  if (rpw == R && unroll == U)                                                                                \
+    return launch_gemv<MRHS, R, U>(W, ldw, X, ldx, Y, ldy, ldy_inner, partial, rows, K, m, split_k, sm_count, \
+                                   stream, launches);
+  HELIX_GEMV_CASE(1, 2)
+  HELIX_GEMV_CASE(1, 4)
+  HELIX_GEMV_CASE(1, 8)
+  HELIX_GEMV_CASE(1, 16)
+  HELIX_GEMV_CASE(2, 2)
+  HELIX_GEMV_CASE(2, 4)
+  HELIX_GEMV_CASE(2, 8)
+#undef HELIX_GEMV_CASE
+  return HELIX_ERR_UNSUPPORTED;
 }
 
 int gemv_f16_launch(const helix_cfg_t* cfg, const void* W, int64_t ldw, const void* X, int64_t ldx, void* Y,
@@ -173,10 +191,14 @@ int gemv_f16_launch(const helix_cfg_t* cfg, const void* W, int64_t ldw, const vo
   const __half* x = static_cast<const __half*>(X);
   __half* y = static_cast<__half*>(Y);
   float* part = static_cast<float*>(ws);
-  if (m == 1) return launch_gemv<1>(w, ldw, x, ldx, y, ldy, ldy_inner, part, rows, K, m, split_k, sm_count, stream, launches);
-  if (m == 2) return launch_gemv<2>(w, ldw, x, ldx, y, ldy, ldy_inner, part, rows, K, m, split_k, sm_count, stream, launches);
-  if (m <= 4) return launch_gemv<4>(w, ldw, x, ldx, y, ldy, ldy_inner, part, rows, K, m, split_k, sm_count, stream, launches);
-  return launch_gemv<8>(w, ldw, x, ldx, y, ldy, ldy_inner, part, rows, K, m, split_k, sm_count, stream, launches);
+  // tile_n = rows per warp, load_group = loads in flight per row; defaults favour deep
+  // memory-level parallelism (one pass over K per warp where K allows)
+  int rpw = (cfg && cfg->tile_m != 0 && cfg->tile_n > 0) ? cfg->tile_n : (m <= 2 ? 2 : 1);
+  int unroll = (cfg && cfg->tile_m != 0 && cfg->load_group > 0) ? cfg->load_group : (m <= 4 ? 4 : 2);
+  if (m == 1) return launch_gemv_variant<1>(rpw, unroll, w, ldw, x, ldx, y, ldy, ldy_inner, part, rows, K, m, split_k, sm_count, stream, launches);
+  if (m == 2) return launch_gemv_variant<2>(rpw, unroll, w, ldw, x, ldx, y, ldy, ldy_inner, part, rows, K, m, split_k, sm_count, stream, launches);
+  if (m <= 4) return launch_gemv_variant<4>(rpw, unroll, w, ldw, x, ldx, y, ldy, ldy_inner, part, rows, K, m, split_k, sm_count, stream, launches);
+  return launch_gemv_variant<8>(rpw, unroll, w, ldw, x, ldx, y, ldy, ldy_inner, part, rows, K, m, split_k, sm_count, stream, launches);
 }
 
 }  // namespace helix

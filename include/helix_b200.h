@@ -79,7 +79,9 @@ typedef struct helix_cfg {
   int raster;    /* M-blocks per rasterisation group (L2 reuse), 0 = default         */
   int thread_m;  /* GEMM_F32: per-thread register block rows                         */
   int thread_n;  /* GEMM_F32: per-thread register block cols                         */
-  int reserved[5];
+  int load_group;/* GEMM_F16: K slabs requested back to back by the TMA producer (0 = 1);
+                    GEMV_F16: 16-byte loads in flight per thread and row (0 = default)  */
+  int reserved[4];
 } helix_cfg_t;
 
 /* A fully described launch; the tagged union the timing entry point iterates. */

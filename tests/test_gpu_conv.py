@@ -88,7 +88,9 @@ def test_conv_benchmark_layers_sampled(oracle, layer):
     y2 = ops.conv2d_f16_nhwc(xd * 2, wd, stride, pad)
     torch.cuda.synchronize()
     ops.check_status()
-    assert torch.equal(y2, y * 2)
+    normal = y.abs() > 2.0 ** -14           # subnormal outputs sit on an absolute grid
+    assert torch.equal(y2[normal], (y * 2)[normal])
+    assert (y2.float() - 2 * y.float()).abs().max().item() <= 2.0 ** -23
     for img in (0, B - 1):
         _, y32 = oracle.conv2d_nhwc_f16(x[img:img + 1], w, stride, pad)
         util.assert_f16_close(y[img:img + 1].cpu().numpy(), y32, f"layer {layer} image {img}")

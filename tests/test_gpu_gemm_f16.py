@@ -144,7 +144,8 @@ def test_gemm_rejects_misaligned_leading_dimension():
 def test_gemm_full_size_linearity_property(shape):
     """At the benchmark's full sizes the oracle is too slow; use size-independent properties:
     rows of A that are one-hot must reproduce columns of B exactly, and scaling A by 2 (exact in
-    fp16) must scale C by exactly 2."""
+    fp16) must scale C by exactly 2 wherever C is a normal fp16 number (subnormal outputs sit on
+    an absolute grid, so there 2*round(c) may differ from round(2c) by one grid step)."""
     M, N, K = shape
     a, b = datagen.c3_gemm(M, N, K, seed=2)
     sel = (np.arange(M) * 7919) % K
@@ -156,7 +157,9 @@ def test_gemm_full_size_linearity_property(shape):
     torch.cuda.synchronize()
     ops.check_status()
     assert torch.equal(c1[::5], bd[:, torch.from_numpy(sel[::5]).cuda()].t().contiguous())
-    assert torch.equal(c2, c1 * 2)
+    normal = c1.abs() > 2.0 ** -14
+    assert torch.equal(c2[normal], (c1 * 2)[normal])
+    assert (c2.float() - 2 * c1.float()).abs().max().item() <= 2.0 ** -23
     # spot-check random rows against an fp64 host dot product
     rng = np.random.default_rng(0)
     rows = rng.integers(0, M, 4)
