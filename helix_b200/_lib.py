@@ -37,12 +37,12 @@ class Cfg(ctypes.Structure):
                 ("tile_k", ctypes.c_int), ("stages", ctypes.c_int), ("cta_group", ctypes.c_int),
                 ("split_k", ctypes.c_int), ("swap_ab", ctypes.c_int), ("raster", ctypes.c_int),
                 ("thread_m", ctypes.c_int), ("thread_n", ctypes.c_int), ("load_group", ctypes.c_int),
-                ("reserved", ctypes.c_int * 4)]
+                ("stream_k", ctypes.c_int), ("reserved", ctypes.c_int * 3)]
 
     def key(self):
         """Hashable identity used as the prof_dict key."""
         return (self.op, self.tile_m, self.tile_n, self.tile_k, self.stages, self.cta_group,
-                self.split_k, self.swap_ab, self.load_group)
+                self.split_k, self.swap_ab, self.load_group, self.stream_k)
 
     def copy(self):
         c = Cfg()

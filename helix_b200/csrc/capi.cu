@@ -223,7 +223,7 @@ size_t helix_workspace_bytes(const helix_launch_t* l) {
     case HELIX_OP_GEMM_F16: {
       helix_cfg_t cfg = l->cfg;
       if (!have_cfg) helix::gemm_f16_default_config(l->M, l->N, l->K, l->batch > 0 ? l->batch : 1, sms, false, &cfg);
-      return helix::gemm_f16_workspace_bytes(&cfg, l->M, l->N, l->K, l->batch > 0 ? l->batch : 1);
+      return helix::gemm_f16_workspace_bytes(&cfg, l->M, l->N, l->K, l->batch > 0 ? l->batch : 1, sms);
     }
     case HELIX_OP_CONV_F16: {
       const helix::ConvGeom g = conv_geom(l->conv);
@@ -232,7 +232,7 @@ size_t helix_workspace_bytes(const helix_launch_t* l) {
       helix_cfg_t cfg = l->cfg;
       const bool as_gemm = g.R == 1 && g.S == 1 && g.stride == 1 && g.pad == 0;
       if (!have_cfg) helix::gemm_f16_default_config((int)M, g.KO, (int)K, 1, sms, !as_gemm, &cfg);
-      return helix::gemm_f16_workspace_bytes(&cfg, (int)M, g.KO, (int)K, 1);
+      return helix::gemm_f16_workspace_bytes(&cfg, (int)M, g.KO, (int)K, 1, sms);
     }
     case HELIX_OP_GEMV_F16: {
       const int split = have_cfg && l->cfg.split_k > 0 ? l->cfg.split_k : helix::gemv_f16_default_split(l->N, l->K, sms);

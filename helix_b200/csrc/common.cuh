@@ -113,6 +113,19 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// Wait until at most n (0..6) of this thread's cp.async groups are still in flight.
+__device__ __forceinline__ void cp_async_wait_dyn(int n) {
+  switch (n) {
+    case 0: cp_async_wait<0>(); break;
+    case 1: cp_async_wait<1>(); break;
+    case 2: cp_async_wait<2>(); break;
+    case 3: cp_async_wait<3>(); break;
+    case 4: cp_async_wait<4>(); break;
+    case 5: cp_async_wait<5>(); break;
+    default: cp_async_wait<6>(); break;
+  }
+}
+
 // Arrival on `bar` that fires when all cp.async copies this thread issued before it have
 // completed; does not raise the barrier's pending count, so it must be part of the init count.
 __device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t* bar) {

@@ -30,7 +30,7 @@ int gemm_f16_num_configs();
 void gemm_f16_get_config(int idx, helix_cfg_t* out);
 // Fills *out with the library's default choice for the problem.
 void gemm_f16_default_config(int M, int N, int K, int batch, int sm_count, bool conv, helix_cfg_t* out);
-size_t gemm_f16_workspace_bytes(const helix_cfg_t* cfg, int M, int N, int K, int batch);
+size_t gemm_f16_workspace_bytes(const helix_cfg_t* cfg, int M, int N, int K, int batch, int sm_count);
 int gemm_f16_launch(const helix_cfg_t* cfg, const void* A, int64_t lda, const void* B, int64_t ldb, void* C,
                     int64_t ldc, int M, int N, int K, int batch, int64_t sa, int64_t sb, int64_t sc, void* ws,
                     size_t ws_bytes, int* status_dev, int sm_count, cudaStream_t stream, int64_t* launches);

@@ -1,0 +1,145 @@
+"""Run a list of independent GEMM / convolution units on one GPU.
+
+This is the in-process form of the reference's sweep loops, which call one
+executable per shape (scripts/Ampere_FP16/benchmark_Ampere_FP16_gemm.py:9-17,
+benchmark_Ampere_FP16_model_level_LLM.py:9-27, ..._CNN.py:9-27): every unit gets
+its own operand buffers in HBM and one prepared launch; ``step()`` queues all of
+them on the current stream.  ``HostSweep`` is the host-buffer variant (pinned
+host operands copied in, results copied out, copies overlapped with compute).
+"""
+import math
+
+import torch
+
+from . import ops, workloads
+
+STEM_CHANNEL_PAD = 8  # NHWC activations need C % 8 == 0 (16-byte rule); C = 3 is stored as 8
+
+
+def _padded_channels(c):
+    return (c + STEM_CHANNEL_PAD - 1) // STEM_CHANNEL_PAD * STEM_CHANNEL_PAD
+
+
+def unit_operand_shapes(unit):
+    """Shapes (a, b, out) of a unit's device tensors in the layouts the kernels take."""
+    s = unit["shape"]
+    if unit["kind"] == "gemm":
+        M, N, K = s[:3]
+        if len(s) > 3:
+            return (s[3], M, K), (s[3], N, K), (s[3], M, N)
+        return (M, K), (N, K), (M, N)
+    B, IC, H, W, OC, kh, kw, stride, pad = s
+    C = _padded_channels(IC)
+    Ho, Wo = ops.conv_out_hw(H, W, kh, kw, stride, pad)
+    return (B, H, W, C), (OC, kh, kw, C), (B, Ho, Wo, OC)
+
+
+def _fill(shape, scale, gen, device, valid_channels=None):
+    t = torch.empty(shape, dtype=torch.float16, device=device)
+    t.normal_(0.0, 1.0, generator=gen)
+    t.mul_(scale)
+    if valid_channels is not None and valid_channels < shape[-1]:
+        t[..., valid_channels:] = 0
+    return t
+
+
+class Sweep:
+    """Device-resident sweep: distinct operand buffers per unit, one prepared launch each."""
+
+    def __init__(self, units, seed=4, device=None, cfg_for=None):
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.units = list(units)
+        self.tensors = []
+        self.launches = []
+        gen = torch.Generator(device=self.device)
+        for i, u in enumerate(self.units):
+            gen.manual_seed(int(seed) * 1000003 + i)
+            sa, sb, so = unit_operand_shapes(u)
+            if u["kind"] == "gemm":
+                K = u["shape"][2]
+                scale = 1.0 / math.sqrt(K)
+                a = _fill(sa, scale, gen, self.device)
+                b = _fill(sb, scale, gen, self.device)
+            else:
+                B, IC, H, W, OC, kh, kw, stride, pad = u["shape"]
+                scale = 1.0 / math.sqrt(IC * kh * kw)
+                a = _fill(sa, scale, gen, self.device, valid_channels=IC)
+                b = _fill(sb, scale, gen, self.device, valid_channels=IC)
+            out = torch.empty(so, dtype=torch.float16, device=self.device)
+            self.tensors.append((a, b, out))
+            cfg = cfg_for(u) if cfg_for is not None else None
+            self.launches.append(self._prepare(u, a, b, out, cfg))
+        self.flops = sum(workloads.unit_flops(u) for u in self.units)
+        self.bytes = sum(workloads.unit_bytes(u) for u in self.units)
+
+    @staticmethod
+    def _prepare(u, a, b, out, cfg):
+        if u["kind"] == "gemm":
+            return ops.launch_gemm_f16(a, b, out, cfg)
+        stride, pad = u["shape"][7], u["shape"][8]
+        return ops.launch_conv2d_f16(a, b, out, stride, pad, cfg)
+
+    def step(self):
+        """Queue every unit once on the current stream; returns the number of library launches."""
+        before = ops.launch_count()
+        for l in self.launches:
+            ops.run(l)
+        return ops.launch_count() - before
+
+
+class HostSweep:
+    """Host-buffer sweep: per step every operand travels host -> device and every result back.
+
+    Pinned host buffers are shared between units of identical shape (the twelve BERT layers
+    reuse one set), device buffers are the sweep's own.  Copies run on two side streams and
+    overlap the kernels; a unit's kernel waits for its operands, its download for the kernel.
+    """
+
+    def __init__(self, sweep):
+        self.sweep = sweep
+        self.host = {}
+        for u, (a, b, out) in zip(sweep.units, sweep.tensors):
+            key = (u["kind"], tuple(u["shape"]))
+            if key not in self.host:
+                ha = torch.empty(a.shape, dtype=a.dtype, pin_memory=True)
+                hb = torch.empty(b.shape, dtype=b.dtype, pin_memory=True)
+                ho = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
+                ha.copy_(a)
+                hb.copy_(b)
+                self.host[key] = (ha, hb, ho)
+        self.h2d = torch.cuda.Stream()
+        self.d2h = torch.cuda.Stream()
+        self.h2d_bytes = sum(a.numel() * 2 + b.numel() * 2 for a, b, _ in sweep.tensors)
+        self.d2h_bytes = sum(o.numel() * 2 for _, _, o in sweep.tensors)
+        self._done = [None] * len(sweep.units)
+        self._drained = [None] * len(sweep.units)
+
+    def step(self):
+        compute = torch.cuda.current_stream()
+        for i, (u, (a, b, out), l) in enumerate(zip(self.sweep.units, self.sweep.tensors, self.sweep.launches)):
+            ha, hb, ho = self.host[(u["kind"], tuple(u["shape"]))]
+            with torch.cuda.stream(self.h2d):
+                if self._done[i] is not None:
+                    self.h2d.wait_event(self._done[i])   # previous step's kernel still reads a, b
+                a.copy_(ha, non_blocking=True)
+                b.copy_(hb, non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(self.h2d)
+            compute.wait_event(ready)
+            if self._drained[i] is not None:
+                compute.wait_event(self._drained[i])     # previous step's download still reads out
+            ops.run(l)
+            done = torch.cuda.Event()
+            done.record(compute)
+            self._done[i] = done
+            with torch.cuda.stream(self.d2h):
+                self.d2h.wait_event(done)
+                ho.copy_(out, non_blocking=True)
+                drained = torch.cuda.Event()
+                drained.record(self.d2h)
+            self._drained[i] = drained
+
+    def finish(self):
+        self.h2d.synchronize()
+        self.d2h.synchronize()
+        torch.cuda.current_stream().synchronize()

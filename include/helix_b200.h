@@ -81,7 +81,10 @@ typedef struct helix_cfg {
   int thread_n;  /* GEMM_F32: per-thread register block cols                         */
   int load_group;/* GEMM_F16: K slabs requested back to back by the TMA producer (0 = 1);
                     GEMV_F16: 16-byte loads in flight per thread and row (0 = default)  */
-  int reserved[4];
+  int stream_k;  /* GEMM_F16/CONV: 1 = whole waves of tiles round-robin, the K slabs of the
+                    remaining tiles dealt evenly to all CTAs (needs a workspace); overrides
+                    split_k                                                              */
+  int reserved[3];
 } helix_cfg_t;
 
 /* A fully described launch; the tagged union the timing entry point iterates. */

@@ -86,7 +86,7 @@ def sgemm_template(a, b, m1, m2, n1, n2, k1, fma=False):
     return c
 
 
-def sgemm_parallel(a, b, tiling=(6, 1, 16, 16, 1, 8, 4), threads=0, fma=False, out=None):
+def sgemm_parallel(a, b, tiling=(8, 1, 32, 64, 1, 2, 6), threads=0, fma=False, out=None):
     """Parallel / packed op-level schedule (benchmark_x86_CPU_gemm.py:71-117).
 
     ``tiling`` = (m1, m2, m3, n1, n2, n3, k1) as returned by ``get_tiling``.

@@ -136,6 +136,33 @@ static void micro_kernel(const float* restrict a, size_t lda, int mrows, int kc_
                          const float* restrict bp, float* restrict cl, size_t ldcl,
                          int m1, int k1, int n1, int fma) {
   /* one (vm2, vn2) cell for one vk2 step: k1 x m1 x n1 */
+  if ((n1 & 15) == 0 && m1 <= 16 && k1 <= 16) {
+    /* Same sums in the same k order per output, with vk1 moved inside vm1/vn1 so the C row
+     * chunk stays in a vector register across the k1 steps (what unrolling vk1 and vm1 and
+     * vectorising vn1 gives the reference's generated code). */
+    typedef float v16 __attribute__((vector_size(64), aligned(4)));
+    float av[16][16];
+    for (int vm1 = 0; vm1 < m1; ++vm1)
+      for (int vk1 = 0; vk1 < k1; ++vk1)
+        av[vm1][vk1] = (vm1 < mrows && vk1 < kc_valid) ? a[(size_t)vm1 * lda + vk1] : 0.0f;
+    for (int c0 = 0; c0 < n1; c0 += 16) {
+      for (int vm1 = 0; vm1 < m1; ++vm1) {
+        float* crow = cl + (size_t)vm1 * ldcl + c0;
+        v16 acc = *(const v16*)crow;
+        for (int vk1 = 0; vk1 < k1; ++vk1) {
+          const v16 bv = *(const v16*)(bp + (size_t)vk1 * n1 + c0);
+          const float s = av[vm1][vk1];
+          if (fma) {
+            for (int i = 0; i < 16; ++i) acc[i] = fmaf(s, bv[i], acc[i]);
+          } else {
+            acc += s * bv;
+          }
+        }
+        *(v16*)crow = acc;
+      }
+    }
+    return;
+  }
   for (int vk1 = 0; vk1 < k1; ++vk1) {
     const float* brow = bp + (size_t)vk1 * n1;
     for (int vm1 = 0; vm1 < m1; ++vm1) {

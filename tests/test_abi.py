@@ -62,7 +62,13 @@ def test_default_config_and_workspace_are_consistent(lib):
         assert lib.helix_default_config(ctypes.byref(l), ctypes.byref(c)) == 0
         assert c.tile_m == 128 and c.tile_n in (16, 32, 64, 128, 256) and c.stages >= 2
         ws = lib.helix_workspace_bytes(ctypes.byref(l))
-        assert ws == (0 if c.split_k == 1 else c.split_k * b * M * N * 4)
+        if c.stream_k:
+            pm, pn = (N, M) if c.swap_ab else (M, N)
+            tiles = -(-pm // 128) * -(-pn // c.tile_n) * b
+            grid = min(tiles * -(-K // 64), 148)   # no device here: the library assumes 148 SMs
+            assert ws == (0 if tiles % grid == 0 else 2 * grid * 128 * c.tile_n * 4)
+        else:
+            assert ws == (0 if c.split_k == 1 else c.split_k * b * M * N * 4)
 
 
 def test_launch_without_device_reports_nodevice_or_runs(lib):

@@ -94,3 +94,18 @@ def test_conv_benchmark_layers_sampled(oracle, layer):
     for img in (0, B - 1):
         _, y32 = oracle.conv2d_nhwc_f16(x[img:img + 1], w, stride, pad)
         util.assert_f16_close(y[img:img + 1].cpu().numpy(), y32, f"layer {layer} image {img}")
+
+
+@pytest.mark.parametrize("geom,bn", [((2, 64, 14, 14, 128, 3, 3, 1, 1), 128), ((5, 32, 9, 9, 72, 3, 3, 2, 1), 64),
+                                     ((32, 128, 28, 28, 128, 3, 3, 1, 1), 128)])
+def test_conv_stream_k(oracle, geom, bn):
+    B, C, H, W, OC, kh, kw, stride, pad = geom
+    x, w = datagen.c4_conv(*geom, seed=13)
+    cfg = ops.make_cfg(OP_CONV_F16, tile_m=128, tile_n=bn, tile_k=64, stream_k=1)
+    got = _run(x, w, stride, pad, cfg)
+    sl = slice(0, min(B, 3))
+    _, y32 = oracle.conv2d_nhwc_f16(x[sl], w, stride, pad)
+    util.assert_f16_close(got[sl], y32, f"stream-K conv {geom}")
+    if B > 3:
+        _, y32 = oracle.conv2d_nhwc_f16(x[-1:], w, stride, pad)
+        util.assert_f16_close(got[-1:], y32, f"stream-K conv {geom} last image")

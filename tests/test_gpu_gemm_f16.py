@@ -167,3 +167,47 @@ def test_gemm_full_size_linearity_property(shape):
     want = a[rows].astype(np.float64) @ b[cols].astype(np.float64).T
     got = c1[torch.from_numpy(rows).cuda()][:, torch.from_numpy(cols).cuda()].cpu().numpy()
     util.assert_f16_close(got, want, f"full-size spot check {shape}")
+
+
+def _sk(bn, swap=0):
+    return ops.make_cfg(OP_GEMM_F16, tile_m=128, tile_n=bn, tile_k=64, swap_ab=swap, stream_k=1, load_group=2)
+
+
+@pytest.mark.parametrize("bn,swap,shape", [
+    (128, 0, (256, 384, 2048)),      # 6 tiles < SMs: every tile is shared by many CTAs
+    (64, 0, (1000, 520, 1096)),      # ragged edges, K tail
+    (16, 1, (16, 1100, 1024)),       # skinny M, swapped
+    (256, 0, (2560, 2304, 512)),     # 180 tiles: one whole wave + a dealt-out tail
+    (128, 0, (2048, 2304, 320)),     # 288 tiles, 5 slabs each: tail tiles touched by two CTAs
+    (32, 1, (24, 4000, 200)),
+    (128, 0, (128, 128, 64)),        # one tile, one slab
+])
+def test_gemm_stream_k(oracle, bn, swap, shape):
+    M, N, K = shape
+    a, b = datagen.c3_gemm(M, N, K, seed=11)
+    cfg = _sk(bn, swap)
+    got = _run(a, b, cfg)
+    again = _run(a, b, cfg)
+    assert np.array_equal(got.view(np.uint16), again.view(np.uint16)), "stream-K fix-up must be deterministic"
+    _, ref32 = oracle.hgemm_fast(a, b)
+    util.assert_f16_close(got, ref32, f"stream-K {shape} bn={bn} swap={swap}")
+
+
+def test_gemm_stream_k_batched(oracle):
+    a, b = datagen.c3_gemm(200, 136, 192, seed=12, batch=5)
+    got = _run(a, b, _sk(64))
+    for i in range(5):
+        _, ref32 = oracle.hgemm_naive(a[i], b[i])
+        util.assert_f16_close(got[i], ref32, f"stream-K batch {i}")
+
+
+def test_gemm_stream_k_needs_workspace():
+    a = torch.zeros((256, 256), dtype=torch.float16, device="cuda")
+    b = torch.zeros((384, 256), dtype=torch.float16, device="cuda")
+    out = torch.zeros((256, 384), dtype=torch.float16, device="cuda")
+    l = ops.launch_gemm_f16(a, b, out, _sk(128))
+    assert l.ws_bytes > 0
+    l.ws, l.ws_bytes = None, 0
+    with pytest.raises(Exception) as e:
+        ops.run(l)
+    assert "-3" in str(e.value)
