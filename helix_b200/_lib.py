@@ -15,6 +15,7 @@ STATUS_TEXT = {
     0: "ok", -1: "invalid argument", -2: "pointer or leading dimension not 16-byte aligned",
     -3: "workspace missing or too small", -4: "CUDA call failed", -5: "bounded device-side wait ran out",
     -6: "configuration not built into the library", -7: "no sm_100 device is current",
+    -8: "problem exceeds the capacity of a fixed built-in buffer",
 }
 
 
@@ -81,6 +82,7 @@ SIGNATURES = {
     "helix_gemv_f16_host": (_I, [_P, _P, _P, _I, _I, _I]),
     "helix_gemm_f32_host": (_I, [_P, _P, _P, _I, _I, _I]),
     "helix_conv2d_f16_nhwc_host": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I]),
+    "helix_gemv_f16_static": (_I, [_P, _L, _P, _L, _P, _L, _L, _I, _I, _I, _I, _P]),
     "helix_launch_count": (_L, []),
 }
 

@@ -135,6 +135,7 @@ const char* helix_status_string(int status) {
     case HELIX_ERR_TIMEOUT: return "bounded device-side wait ran out";
     case HELIX_ERR_UNSUPPORTED: return "configuration not built into the library";
     case HELIX_ERR_NODEVICE: return "no sm_100 device is current";
+    case HELIX_ERR_CAPACITY: return "problem exceeds the capacity of a fixed built-in buffer";
     default: return "unknown status";
   }
 }
@@ -477,6 +478,18 @@ int helix_conv2d_f16_nhwc_host(const void* x, const void* w, void* y, int N, int
   int rc = finish_host(dispatch(&l, dS.p, nullptr), static_cast<int*>(dS.p));
   if (rc != HELIX_OK) return rc;
   return cudaMemcpy(y, dy.p, yb, cudaMemcpyDeviceToHost) == cudaSuccess ? HELIX_OK : HELIX_ERR_CUDA;
+}
+
+int helix_gemv_f16_static(const void* W, int64_t ldw, const void* X, int64_t ldx, void* Y, int64_t ldy,
+                          int64_t ldy_inner, int rows, int K, int m, int split_k, void* stream) {
+  helix_devinfo_t info;
+  const int rc = current_device(&info, false);
+  if (rc != HELIX_OK) return rc;
+  int64_t n = 0;
+  const int st = helix::gemv_f16_static_launch(W, ldw, X, ldx, Y, ldy, ldy_inner, rows, K, m, split_k,
+                                               info.sm_count, static_cast<cudaStream_t>(stream), &n);
+  g_launches += n;
+  return st;
 }
 
 int64_t helix_launch_count(void) { return g_launches.load(); }

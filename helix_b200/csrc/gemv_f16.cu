@@ -10,6 +10,8 @@
 // Mapping: one warp owns RPW consecutive rows; lane l reads the 16-byte chunk l of each
 // 512-byte row segment, UNROLL segments in flight per row, so a thread keeps RPW*UNROLL
 // independent 128-bit streaming loads outstanding.  Lanes are reduced with a shuffle tree.
+#include <mutex>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -199,6 +201,69 @@ int gemv_f16_launch(const helix_cfg_t* cfg, const void* W, int64_t ldw, const vo
   if (m == 2) return launch_gemv_variant<2>(rpw, unroll, w, ldw, x, ldx, y, ldy, ldy_inner, part, rows, K, m, split_k, sm_count, stream, launches);
   if (m <= 4) return launch_gemv_variant<4>(rpw, unroll, w, ldw, x, ldx, y, ldy, ldy_inner, part, rows, K, m, split_k, sm_count, stream, launches);
   return launch_gemv_variant<8>(rpw, unroll, w, ldw, x, ldx, y, ldy, ldy_inner, part, rows, K, m, split_k, sm_count, stream, launches);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Split-K GEMV whose partial sums live in a buffer that is part of the library image.
+//
+// Some users of this library may not create device memory at the moment they need a GEMV: a
+// decode loop that has handed every byte of HBM to its own pool, or code that runs while a
+// stream is being recorded, cannot call cudaMalloc (it may fail, it synchronises the device, and
+// it is not allowed during recording).  For them the fp32 partials of the split-K variant are
+// kept in the fixed array below instead of a caller-supplied workspace.  Every GPU on which the
+// library is loaded carries these 4 MiB until the process exits.
+//
+// In host code the name `g_gemv_static_scratch` is only a handle for the symbol, not an address
+// the GPU understands; the device address is looked up once per device with
+// cudaGetSymbolAddress (that device being current) and that pointer is what the kernels get.
+constexpr size_t kGemvStaticFloats = size_t(1) << 20;  // 4 MiB of fp32 partials
+static __device__ __align__(256) float g_gemv_static_scratch[kGemvStaticFloats];
+
+size_t gemv_f16_static_capacity_floats() { return kGemvStaticFloats; }
+
+// The set-up (symbol lookup) happens in the first call made on each device, so that first call
+// should be issued outside any stream recording.  All calls share the one array: it still holds
+// the previous call's partials when a call starts, which is harmless because the kernel writes
+// every slot the reduction reads before it is read (nothing has to start at zero) -- but two
+// calls that may run on the GPU at the same time (different streams) would overwrite each
+// other's partials, so callers must order them.  Nothing here allocates or frees memory.
+int gemv_f16_static_launch(const void* W, int64_t ldw, const void* X, int64_t ldx, void* Y, int64_t ldy,
+                           int64_t ldy_inner, int rows, int K, int m, int split_k, int sm_count,
+                           cudaStream_t stream, int64_t* launches) {
+  if (!W || !X || !Y || rows <= 0 || K <= 0 || m <= 0 || m > 8 || split_k < 1) return HELIX_ERR_INVALID;
+  if (ldw == 0) ldw = K;
+  if (ldx == 0) ldx = K;
+  if (ldy == 0) ldy = rows;
+  if (ldy_inner == 0) ldy_inner = 1;
+  if ((K & 7) || (ldw & 7) || (ldx & 7) || (reinterpret_cast<uintptr_t>(W) & 15) ||
+      (reinterpret_cast<uintptr_t>(X) & 15))
+    return HELIX_ERR_ALIGN;
+  if (split_k > 1 && (K + split_k - 1) / split_k < 256) split_k = 1;
+  if ((size_t)split_k * (size_t)m * (size_t)rows > kGemvStaticFloats) return HELIX_ERR_CAPACITY;
+
+  static std::mutex mu;
+  static float* scratch_on_device[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return HELIX_ERR_NODEVICE;
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!scratch_on_device[dev]) {
+      void* p = nullptr;
+      if (cudaGetSymbolAddress(&p, g_gemv_static_scratch) != cudaSuccess || !p) return HELIX_ERR_CUDA;
+      scratch_on_device[dev] = static_cast<float*>(p);
+    }
+    scratch = scratch_on_device[dev];
+  }
+  const __half* w = static_cast<const __half*>(W);
+  const __half* x = static_cast<const __half*>(X);
+  __half* y = static_cast<__half*>(Y);
+  const int rpw = m <= 2 ? 2 : 1;
+  const int unroll = m <= 4 ? 4 : 2;
+  if (m == 1) return launch_gemv_variant<1>(rpw, unroll, w, ldw, x, ldx, y, ldy, ldy_inner, scratch, rows, K, m, split_k, sm_count, stream, launches);
+  if (m == 2) return launch_gemv_variant<2>(rpw, unroll, w, ldw, x, ldx, y, ldy, ldy_inner, scratch, rows, K, m, split_k, sm_count, stream, launches);
+  if (m <= 4) return launch_gemv_variant<4>(rpw, unroll, w, ldw, x, ldx, y, ldy, ldy_inner, scratch, rows, K, m, split_k, sm_count, stream, launches);
+  return launch_gemv_variant<8>(rpw, unroll, w, ldw, x, ldx, y, ldy, ldy_inner, scratch, rows, K, m, split_k, sm_count, stream, launches);
 }
 
 }  // namespace helix

@@ -14,6 +14,12 @@ int gemv_f16_launch(const helix_cfg_t* cfg, const void* W, int64_t ldw, const vo
                     int64_t ldy, int64_t ldy_inner, int rows, int K, int m, void* ws, size_t ws_bytes,
                     int sm_count, cudaStream_t stream, int64_t* launches);
 
+// Variant with the split-K partials in an array that is part of the library image.
+size_t gemv_f16_static_capacity_floats();
+int gemv_f16_static_launch(const void* W, int64_t ldw, const void* X, int64_t ldx, void* Y, int64_t ldy,
+                           int64_t ldy_inner, int rows, int K, int m, int split_k, int sm_count,
+                           cudaStream_t stream, int64_t* launches);
+
 // ---- sgemm_f32.cu
 int sgemm_f32_num_configs();
 void sgemm_f32_get_config(int idx, helix_cfg_t* out);

@@ -39,7 +39,8 @@ typedef enum helix_status {
   HELIX_ERR_CUDA = -4,        /* a CUDA runtime / driver call failed                      */
   HELIX_ERR_TIMEOUT = -5,     /* a bounded device-side wait ran out (status word only)    */
   HELIX_ERR_UNSUPPORTED = -6, /* configuration not built into the library                 */
-  HELIX_ERR_NODEVICE = -7     /* no sm_100 device is current                              */
+  HELIX_ERR_NODEVICE = -7,    /* no sm_100 device is current                              */
+  HELIX_ERR_CAPACITY = -8     /* problem larger than a fixed built-in buffer can hold     */
 } helix_status_t;
 
 typedef enum helix_op {
@@ -179,6 +180,20 @@ int helix_gemv_f16_host(const void* W, const void* X, void* Y, int rows, int K, 
 int helix_gemm_f32_host(const float* A, const float* B, float* C, int M, int N, int K);
 int helix_conv2d_f16_nhwc_host(const void* x, const void* w, void* y, int N, int H, int W, int C,
                                int KO, int R, int S, int stride, int pad);
+
+/* Split-K GEMV (same result as helix_gemv_f16 with cfg.split_k = split_k) that never touches the
+ * device allocator: the fp32 partial sums go to a 4 MiB array compiled into the library instead
+ * of a caller workspace, so split_k * m * rows may not exceed HELIX_GEMV_STATIC_FLOATS, else
+ * HELIX_ERR_CAPACITY.  It has no counterpart in the reference.  Meant for callers that cannot
+ * allocate when they need the product, e.g. a decode loop that has given all HBM to its own
+ * pool, or code running while a stream is being recorded.  The first call on each device looks
+ * up the array's device address, so make that call outside any stream recording.  The array is
+ * shared by all calls and keeps the last call's partials; a call overwrites every slot before
+ * reading it, so nothing needs clearing, but calls that can overlap on the GPU (different
+ * streams) corrupt each other and must be ordered by the caller. */
+#define HELIX_GEMV_STATIC_FLOATS (1u << 20)
+int helix_gemv_f16_static(const void* W, int64_t ldw, const void* X, int64_t ldx, void* Y, int64_t ldy,
+                          int64_t ldy_inner, int rows, int K, int m, int split_k, void* stream);
 
 /* Number of kernel launches this process has queued through the library (all ops). */
 int64_t helix_launch_count(void);
