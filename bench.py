@@ -228,7 +228,7 @@ def bench_helix(args, rank, world, local_rank):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    from helix_b200 import ops, sweep, workloads
+    from helix_b200 import dist_util, ops, sweep, workloads
     peaks = read_peaks()
 
     units = workloads.model_level_sweep()
@@ -275,10 +275,7 @@ def bench_helix(args, rank, world, local_rank):
     ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
     ops.check_status()
-    if dist is not None:
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ms = dist_util.max_over_ranks(ms, dist, "cuda")
     ms_per_step = ms / args.steps
     value = sw.flops * world / (ms_per_step * 1e-3) / 1e12
 
@@ -295,10 +292,7 @@ def bench_helix(args, rank, world, local_rank):
         hs.step()
     hs.finish()
     e2e_s = (time.perf_counter() - t0) / e2e_steps
-    if dist is not None:
-        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+    e2e_s = dist_util.max_over_ranks(e2e_s, dist, "cuda")
     e2e_value = sw.flops * world / e2e_s / 1e12
     ops.check_status()
 

@@ -1,0 +1,174 @@
+"""Search space, profiled dictionary and cost model for the sm_100a kernels.
+
+The reference profiles every tile configuration once on a one-CTA problem and
+predicts ``ceil(blocks / 108) * t_cfg`` with K ignored (scripts/Ampere_FP16/
+Ampere_FP16_gemm.py:420-430, profile_Ampere_FP16.py:17-62).  The same idea, re-derived
+for a persistent tcgen05 kernel:
+
+* a configuration is (stages, tile_m, tile_n, cta_group, swap_ab, mode) with mode 0 = whole
+  tiles round-robin, 1 = stream-K; GEMV configurations start with 0 like the reference's
+  (0, 1, 128, 0, 0, splitK) keys: (0, 1, rows_per_warp, loads_in_flight, 0, split_k);
+* each GEMM tile width is probed at two K values on a full-machine problem, which gives a
+  fixed cost per launch and a cost per 64-deep K slab (the reference's single number per
+  configuration cannot separate the two, so its model drops K);
+* the time of a shape is  t_fixed + slabs_per_CTA * t_slab,  slabs counted from the wave
+  structure on the queried SM count (not a literal 108), floored by the bytes that must come
+  from HBM at the measured streaming rate of the SMs that take part, plus the measured
+  overhead of the stream-K fix-up where used.
+
+The dictionary is one Python literal (``str(dict)``), written where the reference writes it:
+``build/prof_dict/<backend>_cost_model.dict``.
+"""
+import math
+
+TILE_M = 128
+TILE_K = 64
+GEMM_TILE_NS = (256, 128, 64, 32, 16)
+GEMV_VARIANTS = ((2, 4), (1, 4), (1, 8), (2, 2))   # (rows per warp, 16-byte loads in flight per row)
+GEMV_SPLITS = (1, 2, 4, 8)
+DEFAULT_SMS = 148
+
+# FP32 SIMT tiles: (BM, BN, BK, TM, TN), the analogue of the reference's
+# (BM, BN, BK, TM, TN, WARP_ROW_THREAD, COPY_A, COPY_B) keys (build_Ampere_FP32.py:37-63)
+SGEMM_TILES = ((128, 128, 16, 8, 8), (128, 64, 16, 8, 4), (64, 128, 16, 4, 8), (64, 64, 16, 4, 4), (32, 64, 16, 4, 4))
+
+
+def is_valid_config(tile_n, swap_ab, mode, stages):
+    """Analogue of is_valid_config (build_Ampere_FP16.py:30-39): what the library can launch."""
+    return tile_n in GEMM_TILE_NS and swap_ab in (0, 1) and mode in (0, 1) and 0 <= stages <= 8
+
+
+def max_stages(tile_n):
+    budget = 227 * 1024 - 1024 - 256
+    return min(8, budget // (TILE_M * TILE_K * 2 + tile_n * TILE_K * 2))
+
+
+def gemm_keys():
+    """Every GEMM configuration of the search space, as dictionary keys."""
+    keys = []
+    for bn in GEMM_TILE_NS:
+        for swap in (0, 1):
+            for mode in (0, 1):
+                keys.append((max_stages(bn), TILE_M, bn, 1, swap, mode))
+    return keys
+
+
+def gemv_keys():
+    return [(0, 1, rpw, unroll, 0, split) for (rpw, unroll) in GEMV_VARIANTS for split in GEMV_SPLITS]
+
+
+def sgemm_keys():
+    return [(bm, bn, bk, tm, tn, 0, 0, 0) for (bm, bn, bk, tm, tn) in SGEMM_TILES]
+
+
+# ----------------------------------------------------------------------------- prediction
+def _param(prof_dict, name, default):
+    return prof_dict.get((name,), default)
+
+
+def gemm_time(prof_dict, key, M, N, K, batch=1, conv=False):
+    """Predicted seconds of one GEMM launch with configuration `key` (inf if inapplicable)."""
+    stages, tm, bn, group, swap, mode = key
+    val = prof_dict.get(key) or prof_dict.get((stages, tm, bn, group, 0, 0))
+    if val is None:
+        return float("inf")
+    t_fixed, t_slab = val
+    if conv:
+        if swap:
+            return float("inf")
+        t_slab = max(t_slab, prof_dict.get(("conv_slab", bn), t_slab))
+    sms = _param(prof_dict, "sm_count", DEFAULT_SMS)
+    pm, pn = (N, M) if swap else (M, N)
+    tiles_m, tiles_n = -(-pm // tm), -(-pn // bn)
+    tiles = tiles_m * tiles_n * batch
+    nkb = -(-K // TILE_K)
+    rounds, tail = divmod(tiles, sms)
+    if mode == 0:
+        slabs = (rounds + (1 if tail else 0)) * nkb
+        active = min(tiles, sms)
+        extra = 0.0
+    else:
+        if tail == 0 or nkb < 2:
+            return float("inf")      # identical to mode 0: keep one entry
+        slabs = rounds * nkb + max(-(-tail * nkb // sms), min(4, nkb))
+        active = min(tiles * nkb, sms)
+        extra = prof_dict.get(("streamk_overhead", bn), 8e-6)
+    t = t_fixed + slabs * t_slab + extra
+    # HBM floor: operand bytes at the streaming rate of the SMs that take part
+    per_sm = _param(prof_dict, "dram_gbs_per_sm", 40.0) * 1e9
+    hbm = _param(prof_dict, "hbm_gbs", 6000.0) * 1e9
+    bytes_ = 2.0 * batch * (M * K + N * K + M * N)
+    t_mem = t_fixed + bytes_ / min(hbm, active * per_sm)
+    return max(t, t_mem)
+
+
+def gemv_time(prof_dict, key, rows, K, m):
+    val = prof_dict.get(key)
+    if val is None or m > 8:
+        return float("inf")
+    t_fixed, s_per_byte = val
+    split = key[5]
+    if split > 1 and K // split < 256:
+        return float("inf")
+    bytes_ = 2.0 * (rows * K + m * K + m * rows)
+    # m right-hand sides multiply the arithmetic per streamed byte; beyond ~2 the SIMT kernel is issue bound
+    return t_fixed + bytes_ * s_per_byte * max(1.0, m / 2.0)
+
+
+def cost_model(prof_dict, M, N, K, batch=1, conv=False):
+    """Best configuration key for C[M,N] = A[M,K] * B[N,K]^T; first element 0 means GEMV.
+
+    Same call shape as the reference's cost_model(prof_dict, M, N, K)
+    (Ampere_FP16_gemm.py:420-430), but K and the batch count enter the estimate.
+    """
+    best_key, best = None, float("inf")
+    for key in prof_dict:
+        if len(key) != 6:
+            continue
+        if key[0] == 0:
+            if conv or batch != 1 or min(M, N) > 8:
+                continue
+            rows, m = (N, M) if M <= N else (M, N)
+            t = gemv_time(prof_dict, key, rows, K, m)
+        else:
+            t = gemm_time(prof_dict, key, M, N, K, batch, conv)
+        if t < best:
+            best, best_key = t, key
+    return best_key
+
+
+def predicted_time(prof_dict, key, M, N, K, batch=1, conv=False):
+    if key[0] == 0:
+        rows, m = (N, M) if M <= N else (M, N)
+        return gemv_time(prof_dict, key, rows, K, m)
+    return gemm_time(prof_dict, key, M, N, K, batch, conv)
+
+
+def sgemm_cost_model(prof_dict, M, N, K):
+    """FP32: ceil(tiles / SMs) * K-slabs * profiled seconds per tile-slab (Ampere_FP32_gemm.py:89-99)."""
+    sms = _param(prof_dict, "sm_count", DEFAULT_SMS)
+    best_key, best = None, float("inf")
+    for key, v in prof_dict.items():
+        if len(key) != 8:
+            continue
+        bm, bn, bk = key[0], key[1], key[2]
+        tiles = -(-M // bm) * -(-N // bn)
+        t = math.ceil(tiles / sms) * -(-K // bk) * v
+        if t < best:
+            best, best_key = t, key
+    return best_key
+
+
+# ----------------------------------------------------------------------------- dictionary I/O
+def save(prof_dict, path):
+    import os
+    os.makedirs(os.path.dirname(path), exist_ok=True)
+    tmp = path + ".tmp"
+    with open(tmp, "w") as f:
+        f.write(str(prof_dict))
+    os.replace(tmp, path)          # a crash mid-profile never leaves a truncated dictionary
+
+
+def load(path):
+    with open(path) as f:
+        return eval(f.readlines()[0])   # the reference's own loading idiom (benchmark_Ampere_FP16_gemm.py:10-12)

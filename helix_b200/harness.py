@@ -1,0 +1,331 @@
+"""In-process replacements for the reference's per-configuration executables.
+
+The reference measures a configuration by spawning ``build/bin_fp16/gemm_<cfg> M N K`` and
+reading token [-8] of its stdout (scripts/Ampere_FP16/profile_Ampere_FP16.py:36-39,
+Ampere_FP16_gemm.py:438-441).  Here the same questions -- "how long does this configuration
+take on this shape", "fill the dictionary", "run the predicted-best configuration" -- are
+answered through the C ABI, with operands that are real seeded data and with rotating buffers
+for memory-bound shapes so that they really come from HBM.
+"""
+import math
+import os
+
+import torch
+
+from . import costmodel, ops
+from ._lib import OP_CONV_F16, OP_GEMM_F16, OP_GEMM_F32, OP_GEMV_F16
+
+ROTATE_BYTES = 300e6      # more than twice the 126 MB L2
+
+
+def root_path():
+    return os.getcwd()   # the reference resolves build/ against the working directory (build_Ampere_FP16.py:4)
+
+
+def dict_path(backend):
+    return os.path.join(root_path(), "build", "prof_dict", f"{backend}_cost_model.dict")
+
+
+def require_gpu():
+    if not torch.cuda.is_available():
+        raise RuntimeError("the Helix B200 backends need a CUDA device; there is no CPU fallback")
+
+
+def key_to_cfg(key, conv=False):
+    """Dictionary key -> library configuration."""
+    if key[0] == 0:
+        return ops.make_cfg(OP_GEMV_F16, tile_m=1, tile_n=key[2], tile_k=256, split_k=key[5], load_group=key[3])
+    stages, tm, bn, group, swap, mode = key
+    return ops.make_cfg(OP_CONV_F16 if conv else OP_GEMM_F16, tile_m=tm, tile_n=bn, tile_k=costmodel.TILE_K,
+                        stages=0, cta_group=group, swap_ab=swap, stream_k=mode, load_group=2)
+
+
+def _randn(shape, scale):
+    return torch.randn(shape, device="cuda", dtype=torch.float16) * scale
+
+
+def time_gemm_f16(M, N, K, cfg=None, batch=None, iters=20):
+    """Seconds per launch of the fp16 GEMM; operands rotate through > 2x L2 when the shape is memory-bound."""
+    b = batch or 1
+    bytes_ = 2.0 * b * (M * K + N * K + M * N)
+    flops = 2.0 * b * M * N * K
+    nbuf = 1 if flops / bytes_ > 300 else int(ROTATE_BYTES // bytes_) + 1
+    sa, sb, sc = ((M, K), (N, K), (M, N)) if batch is None else ((b, M, K), (b, N, K), (b, M, N))
+    s = 1.0 / math.sqrt(K)
+    bufs = [(_randn(sa, s), _randn(sb, s), torch.empty(sc, device="cuda", dtype=torch.float16)) for _ in range(nbuf)]
+    ls = [ops.launch_gemm_f16(a, bb, c, cfg) for a, bb, c in bufs]
+    reps = max(1, 4 // len(ls))
+    avg, _, _ = ops.time_launches(ls * reps, warmup=3, iters=iters, use_graph=True)
+    return avg
+
+
+def time_gemv_f16(rows, K, m, cfg=None, transposed=False, iters=30):
+    bytes_ = 2.0 * (rows * K + m * K + m * rows)
+    nbuf = int(ROTATE_BYTES // bytes_) + 1
+    x = _randn((m, K), 1.0)
+    ws = [_randn((rows, K), 0.02) for _ in range(nbuf)]
+    oshape = (rows, m) if transposed else (m, rows)
+    ys = [torch.empty(oshape, device="cuda", dtype=torch.float16) for _ in range(nbuf)]
+    ls = [ops.launch_gemv_f16(w, x, y, cfg, out_transposed=transposed) for w, y in zip(ws, ys)]
+    reps = max(1, 4 // len(ls))
+    avg, _, _ = ops.time_launches(ls * reps, warmup=3, iters=iters, use_graph=True)
+    return avg
+
+
+def time_conv_f16(batch, IC, H, W, OC, kH, kW, stride, pad, cfg=None, iters=20):
+    C = (IC + 7) // 8 * 8    # NHWC activations are stored with C padded to a multiple of 8
+    x = torch.rand((batch, H, W, C), device="cuda", dtype=torch.float16) * 2 - 1
+    w = _randn((OC, kH, kW, C), math.sqrt(2.0 / (IC * kH * kW)))
+    if C != IC:
+        x[..., IC:] = 0
+        w[..., IC:] = 0
+    Ho, Wo = ops.conv_out_hw(H, W, kH, kW, stride, pad)
+    y = torch.empty((batch, Ho, Wo, OC), device="cuda", dtype=torch.float16)
+    l = ops.launch_conv2d_f16(x, w, y, stride, pad, cfg)
+    avg, _, _ = ops.time_launches([l] * 4, warmup=3, iters=iters, use_graph=True)
+    return avg
+
+
+def time_gemm_f32(M, N, K, cfg=None, iters=10):
+    a = torch.rand((M, K), device="cuda") * 2 - 1
+    b = torch.rand((K, N), device="cuda") * 2 - 1
+    c = torch.empty((M, N), device="cuda")
+    avg, _, _ = ops.time_launches([ops.launch_gemm_f32(a, b, c, False, cfg)] * 2, warmup=2, iters=iters, use_graph=True)
+    return avg
+
+
+# ----------------------------------------------------------------------------- profiling
+def _two_point(t1, s1, t2, s2):
+    slab = max((t2 - t1) / (s2 - s1), 1e-9)
+    return max(t1 - s1 * slab, 0.0), slab
+
+
+def profile_fp16(fast=False, progress=None):
+    """Fill the fp16 dictionary.  fast=True is the 'changed_profile' mode: probe the widest and the
+    64-wide tile only and interpolate the rest (the reference's fast mode extrapolates
+    BLOCK > WARP tiles from BLOCK == WARP ones, changed_profile_Ampere_FP16.py:27-54)."""
+    require_gpu()
+    sms = ops.device_info().sm_count
+    d = {("sm_count",): sms}
+    tick = progress or (lambda: None)
+
+    def cfg(bn, swap=0, mode=0):
+        return ops.make_cfg(OP_GEMM_F16, 128, bn, 64, swap_ab=swap, stream_k=mode, load_group=2)
+
+    measured = {}
+    wide = (256, 64) if fast else (256, 128, 64)
+    for bn in wide:                                  # L2-friendly square problem, two K values
+        M = N = 4096
+        tiles = (M // 128) * (N // bn)
+        waves = -(-tiles // sms)
+        t1 = time_gemm_f16(M, N, 512, cfg(bn)); tick()
+        t2 = time_gemm_f16(M, N, 4096, cfg(bn)); tick()
+        measured[bn] = _two_point(t1, waves * 8, t2, waves * 64)
+    if fast:                                         # interpolate 128 between 64 and 256
+        f64, f256 = measured[64], measured[256]
+        measured[128] = tuple(a + (b - a) * (128 - 64) / (256 - 64) for a, b in zip(f64, f256))
+    skinny = {}
+    for bn in ((16,) if fast else (32, 16)):          # skinny M on the UMMA N axis: everything streams from DRAM
+        N = 128 * sms
+        t1 = time_gemm_f16(bn, N, 1024, cfg(bn, swap=1)); tick()
+        t2 = time_gemm_f16(bn, N, 8192, cfg(bn, swap=1)); tick()
+        skinny[bn] = _two_point(t1, 16, t2, 128)
+    if fast:
+        skinny[32] = skinny[16]
+    # per-SM DRAM streaming rate from the narrowest tile: each CTA pulls 128 rows x 64 halves per slab
+    d[("dram_gbs_per_sm",)] = (128 * 64 * 2 + 16 * 64 * 2) / skinny[16][1] / 1e9
+    for bn in costmodel.GEMM_TILE_NS:
+        val = measured.get(bn) or skinny.get(bn)
+        for swap in (0, 1):
+            for mode in (0, 1):
+                d[(costmodel.max_stages(bn), 128, bn, 1, swap, mode)] = tuple(float(v) for v in val)
+    # stream-K: measured excess over the slab model on a half-wave problem
+    for bn in wide:
+        M, N, K = 128 * (sms // 2), bn, 4096
+        t = time_gemm_f16(M, N, K, cfg(bn, mode=1)); tick()
+        tf, ts = measured[bn]
+        d[("streamk_overhead", bn)] = max(t - (tf + 32 * ts), 2e-6)
+    if fast:
+        d[("streamk_overhead", 128)] = 0.5 * (d[("streamk_overhead", 64)] + d[("streamk_overhead", 256)])
+    # convolution: slope per slab of the gathering producer (3x3, 28x28, batch 32: 196 tiles)
+    for bn in wide:
+        ccfg = ops.make_cfg(OP_CONV_F16, 128, bn, 64)
+        waves = -(-196 * max(1, 1) // sms)
+        t1 = time_conv_f16(32, 64, 28, 28, bn, 3, 3, 1, 1, ccfg); tick()
+        t2 = time_conv_f16(32, 256, 28, 28, bn, 3, 3, 1, 1, ccfg); tick()
+        d[("conv_slab", bn)] = _two_point(t1, waves * 9, t2, waves * 36)[1]
+    if fast:
+        d[("conv_slab", 128)] = 0.5 * (d[("conv_slab", 64)] + d[("conv_slab", 256)])
+    # GEMV: fixed cost and seconds per streamed byte for each variant
+    variants = costmodel.GEMV_VARIANTS[:1] if fast else costmodel.GEMV_VARIANTS
+    best_rate = 0.0
+    for (rpw, unroll) in variants:
+        for split in costmodel.GEMV_SPLITS:
+            c = ops.make_cfg(OP_GEMV_F16, tile_m=1, tile_n=rpw, tile_k=256, split_k=split, load_group=unroll)
+            t1 = time_gemv_f16(2048, 4096, 1, c); tick()
+            t2 = time_gemv_f16(16384, 8192, 1, c); tick()
+            b1, b2 = 2.0 * (2048 * 4096), 2.0 * (16384 * 8192)
+            fixed, per_byte = _two_point(t1, b1, t2, b2)
+            d[(0, 1, rpw, unroll, 0, split)] = (float(fixed), float(per_byte))
+            best_rate = max(best_rate, b2 / t2 / 1e9)
+    d[("hbm_gbs",)] = best_rate
+    return d
+
+
+def profile_fp32(fast=False, progress=None):
+    require_gpu()
+    sms = ops.device_info().sm_count
+    d = {("sm_count",): sms}
+    size = 1024 if fast else 2048
+    for key in costmodel.sgemm_keys():
+        bm, bn, bk, tm, tn = key[:5]
+        c = ops.make_cfg(OP_GEMM_F32, tile_m=bm, tile_n=bn, tile_k=bk, thread_m=tm, thread_n=tn)
+        try:
+            t = time_gemm_f32(size, size, size, c)
+            tiles = -(-size // bm) * -(-size // bn)
+            d[key] = float(t / (math.ceil(tiles / sms) * (size // bk)))
+        except Exception:
+            d[key] = float("inf")   # a configuration that fails to run never wins (profile_Ampere_FP32.py:41-45)
+        if progress:
+            progress()
+    return d
+
+
+# ----------------------------------------------------------------------------- "run the winner"
+def gemm_f16_result(prof_dict, M, N, K, batch=None):
+    """(cost_ms, tflops) of the predicted-best configuration, the contract of
+    get_Ampere_FP16_gemm_Helix_result (Ampere_FP16_gemm.py:432-441, cuda branch: milliseconds)."""
+    require_gpu()
+    key = costmodel.cost_model(prof_dict, M, N, K, batch or 1)
+    if key is None:
+        raise RuntimeError("empty cost-model dictionary: run profile_template.py first")
+    if key[0] == 0:
+        rows, m, transposed = (N, M, False) if M <= N else (M, N, True)
+        Kp = (K + 7) // 8 * 8
+        t = time_gemv_f16(rows, Kp, m, key_to_cfg(key), transposed)
+    else:
+        Kp = (K + 7) // 8 * 8      # leading dimensions follow the 16-byte rule; the padding columns are zero work
+        t = time_gemm_f16(M, N, Kp, key_to_cfg(key), batch)
+    cost_ms = t * 1e3
+    return cost_ms, 2.0 * M * N * K * (batch or 1) / 1e9 / cost_ms
+
+
+def conv_f16_result(prof_dict, batch, IC, H, W, OC, kH, kW, stride, pad):
+    """(cost_ms, tflops) of one NHWC convolution as a single implicit GEMM
+    (get_Ampere_FP16_conv_Helix_result, Ampere_FP16_conv.py:431-446: im2col time + GEMM time)."""
+    require_gpu()
+    Ho, Wo = ops.conv_out_hw(H, W, kH, kW, stride, pad)
+    M, N, K = batch * Ho * Wo, OC, IC * kH * kW
+    as_gemm = kH == 1 and kW == 1 and stride == 1 and pad == 0
+    key = costmodel.cost_model(prof_dict, M, N, (K + 7) // 8 * 8, 1, conv=not as_gemm)
+    if key is None or key[0] == 0:
+        key = (costmodel.max_stages(128), 128, 128, 1, 0, 0)
+    t = time_conv_f16(batch, IC, H, W, OC, kH, kW, stride, pad, key_to_cfg(key, conv=True))
+    cost_ms = t * 1e3
+    return cost_ms, 2.0 * M * N * K / 1e9 / cost_ms
+
+
+def gemm_f32_result(prof_dict, M, N, K):
+    require_gpu()
+    key = costmodel.sgemm_cost_model(prof_dict, M, N, K)
+    if key is None:
+        raise RuntimeError("empty cost-model dictionary: run profile_template.py -b Ampere_FP32 first")
+    bm, bn, bk, tm, tn = key[:5]
+    t = time_gemm_f32(M, N, K, ops.make_cfg(OP_GEMM_F32, tile_m=bm, tile_n=bn, tile_k=bk, thread_m=tm, thread_n=tn))
+    cost_ms = t * 1e3
+    return cost_ms, 2.0 * M * N * K / 1e9 / cost_ms
+
+
+def conv_f32_result(prof_dict, batch, IC, H, W, OC, kH, kW, stride, pad):
+    """FP32 convolution = the reference's mapping conv -> GEMM dims (Ampere_FP32_conv.py:101-113); the
+    GEMM is timed on the mapped shape (an explicit fp32 im2col is not part of the tensor-core path)."""
+    Ho, Wo = ops.conv_out_hw(H, W, kH, kW, stride, pad)
+    return gemm_f32_result(prof_dict, batch * Ho * Wo, OC, IC * kH * kW)
+
+
+# ----------------------------------------------------------------------------- sharded-sweep workers
+def _bind(device):
+    require_gpu()
+    torch.cuda.set_device(int(device))
+
+
+def worker_gemm_f16(device, unit, prof_dict):
+    _bind(device)
+    M, N, K = unit[:3]
+    cost, tflops = gemm_f16_result(prof_dict, M, N, K, unit[3] if len(unit) > 3 else None)
+    return {"shape": list(unit), "ms": cost, "tflops": tflops}
+
+
+def worker_conv_f16(device, unit, prof_dict):
+    _bind(device)
+    cost, tflops = conv_f16_result(prof_dict, *unit)
+    return {"shape": list(unit), "ms": cost, "tflops": tflops}
+
+
+def worker_gemm_f32(device, unit, prof_dict):
+    _bind(device)
+    cost, tflops = gemm_f32_result(prof_dict, *unit[:3])
+    return {"shape": list(unit), "ms": cost, "tflops": tflops}
+
+
+def worker_conv_f32(device, unit, prof_dict):
+    _bind(device)
+    cost, tflops = conv_f32_result(prof_dict, *unit)
+    return {"shape": list(unit), "ms": cost, "tflops": tflops}
+
+
+def run_shape_list(units, worker, prof_dict, gpus=1, predicted=None, journal=None):
+    """Rows (ordered like `units`) of a sweep over 1..N GPUs of this box."""
+    from . import shard
+    if gpus <= 1:
+        return [worker(torch.cuda.current_device() if torch.cuda.is_available() else 0, u, prof_dict) for u in units]
+    rows, stats = shard.run_sharded(units, worker, list(range(gpus)), costs=predicted, journal=journal,
+                                    fn_args=(prof_dict,))
+    if stats["unfinished"]:
+        raise RuntimeError(f"sweep incomplete: {stats}")
+    return [rows[i] for i in range(len(units))]
+
+
+# ----------------------------------------------------------------------------- vendor comparators (context only)
+def time_torch(fn, iters=20):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e-3 / iters
+
+
+def cublas_gemm_result(M, N, K, dtype=torch.float16):
+    """cuBLAS through torch.matmul: the comparator row of the reference's cublas_f16.cu / cublas_f32.cu."""
+    require_gpu()
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        a = torch.randn((M, K), device="cuda", dtype=dtype)
+        b = torch.randn((N, K), device="cuda", dtype=dtype)
+        t = time_torch(lambda: torch.matmul(a, b.t()))
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    cost_ms = t * 1e3
+    return cost_ms, 2.0 * M * N * K / 1e9 / cost_ms
+
+
+def cudnn_conv_result(batch, IC, H, W, OC, kH, kW, stride, pad, dtype=torch.float16):
+    """cuDNN through torch conv2d in channels-last: the comparator row of cudnn_fp16.cu / cudnn_fp32.cu."""
+    require_gpu()
+    prev = torch.backends.cudnn.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        x = torch.randn((batch, IC, H, W), device="cuda", dtype=dtype).contiguous(memory_format=torch.channels_last)
+        w = torch.randn((OC, IC, kH, kW), device="cuda", dtype=dtype).contiguous(memory_format=torch.channels_last)
+        t = time_torch(lambda: torch.nn.functional.conv2d(x, w, stride=stride, padding=pad))
+    finally:
+        torch.backends.cudnn.allow_tf32 = prev
+    Ho, Wo = ops.conv_out_hw(H, W, kH, kW, stride, pad)
+    cost_ms = t * 1e3
+    return cost_ms, 2.0 * batch * Ho * Wo * OC * IC * kH * kW / 1e9 / cost_ms

@@ -1,0 +1,68 @@
+"""Run one operator a few times on seeded data -- the target of `ncu` captures.
+
+  python -m helix_b200.profile_case gemm M N K [--batch B] [--bn 256] [--stream-k] [--swap] [--reps 3]
+  python -m helix_b200.profile_case conv B IC H W OC kH kW stride pad [--bn 128] [--reps 3]
+  python -m helix_b200.profile_case gemv ROWS K [--m 1] [--reps 3]
+  python -m helix_b200.profile_case sgemm M N K [--reps 3]
+
+Keeps device memory small and launches few kernels, so that a full-metric capture of one launch
+(`ncu --set full --clock-control none -k regex:<kernel> -s 1 -c 1 ...`) ends by itself quickly.
+"""
+import argparse
+import sys
+
+import torch
+
+from . import datagen, ops
+from ._lib import OP_CONV_F16, OP_GEMM_F16
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op", choices=["gemm", "conv", "gemv", "sgemm"])
+    ap.add_argument("dims", type=int, nargs="+")
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--stream-k", action="store_true")
+    ap.add_argument("--swap", action="store_true")
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--reps", type=int, default=3)
+    args = ap.parse_args(argv)
+    dev = "cuda"
+    if args.op == "gemm":
+        M, N, K = args.dims
+        a, b = datagen.c3_gemm(M, N, K, seed=2, batch=args.batch)
+        a, b = torch.from_numpy(a).to(dev), torch.from_numpy(b).to(dev)
+        cfg = None
+        if args.bn:
+            cfg = ops.make_cfg(OP_GEMM_F16, 128, args.bn, 64, stream_k=int(args.stream_k), swap_ab=int(args.swap),
+                               load_group=2)
+        for _ in range(args.reps):
+            out = ops.gemm_f16(a, b, cfg=cfg)
+    elif args.op == "conv":
+        geom = tuple(args.dims)
+        x, w = datagen.c4_conv(*geom, seed=3)
+        x, w = torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev)
+        cfg = ops.make_cfg(OP_CONV_F16, 128, args.bn, 64, stream_k=int(args.stream_k)) if args.bn else None
+        for _ in range(args.reps):
+            out = ops.conv2d_f16_nhwc(x, w, geom[7], geom[8], cfg=cfg)
+    elif args.op == "gemv":
+        rows, K = args.dims
+        w, x = datagen.c2_gemv(rows, K, args.m, seed=1)
+        w, x = torch.from_numpy(w).to(dev), torch.from_numpy(x).to(dev)
+        for _ in range(args.reps):
+            out = ops.gemv_f16(w, x)
+    else:
+        M, N, K = args.dims
+        a, b = datagen.c1_fp32_gemm(M, N, K, seed=0)
+        a, b = torch.from_numpy(a).to(dev), torch.from_numpy(b).to(dev)
+        for _ in range(args.reps):
+            out = ops.gemm_f32(a, b)
+    torch.cuda.synchronize()
+    ops.check_status()
+    print("ok", tuple(out.shape), float(out.float().abs().mean()))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

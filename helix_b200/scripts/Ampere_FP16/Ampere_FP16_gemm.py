@@ -1,0 +1,25 @@
+"""Selection + execution of one fp16 GEMM (reference: scripts/Ampere_FP16/Ampere_FP16_gemm.py:420-554)."""
+import os
+
+import _bootstrap  # noqa: F401
+
+root_path = os.getcwd()
+
+
+def cost_model(prof_dict, M, N, K):
+    from helix_b200 import costmodel
+    return costmodel.cost_model(prof_dict, M, N, K)
+
+
+def get_Ampere_FP16_gemm_Helix_result(prof_dict, M, N, K, backend="cuda"):
+    """(cost in ms, TFLOPS on the unpadded M, N, K).  Only the "cuda" backend exists: the reference's
+    "tvm" branch is its TVM code generator, which this build replaces rather than wraps."""
+    if backend != "cuda":
+        raise ValueError("only backend='cuda' is available (no TVM code generation in this build)")
+    from helix_b200 import harness
+    return harness.gemm_f16_result(prof_dict, M, N, K)
+
+
+def get_Ampere_FP16_gemm_cublas_result(M, N, K):
+    from helix_b200 import harness
+    return harness.cublas_gemm_result(M, N, K)

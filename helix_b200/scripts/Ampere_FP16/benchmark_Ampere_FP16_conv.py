@@ -1,0 +1,35 @@
+"""Op-level convolution sweep (reference: scripts/Ampere_FP16/benchmark_Ampere_FP16_conv.py:9-23)."""
+import os
+
+import _bootstrap  # noqa: F401
+from utils.get_benchmark_shape_list import get_conv_op_shape_list
+from Ampere_FP16.Ampere_FP16_conv import get_Ampere_FP16_conv_cudnn_result
+
+root_path = os.getcwd()
+
+
+def Ampere_FP16_Helix_op_level_Conv_benchmark(backend="cuda", gpus=1, limit=0):
+    from helix_b200 import costmodel, harness
+    prof_dict = costmodel.load(f'{root_path}/build/prof_dict/Ampere_FP16_cost_model.dict')
+
+    shape_list = get_conv_op_shape_list()
+    if limit:
+        shape_list = shape_list[:limit]
+    rows = harness.run_shape_list(shape_list, harness.worker_conv_f16, prof_dict, gpus)
+    for (batch, input_channel, H, W, output_channel, kH, kW, stride, pad), row in zip(shape_list, rows):
+        helix_tflops = row["tflops"]
+        print(f'{batch}x{input_channel}x{H}x{W}x{output_channel}x{kH}x{kW}x{stride}x{pad}: Helix: {helix_tflops:.2f} TFLOPS')
+    return rows
+
+
+def Ampere_FP16_cudnn_op_level_Conv_benchmark():
+    shape_list = get_conv_op_shape_list()
+    for batch, input_channel, H, W, output_channel, kH, kW, stride, pad in shape_list:
+        _, cudnn_tflops = get_Ampere_FP16_conv_cudnn_result(batch, input_channel, H, W, output_channel, kH, kW, stride, pad)
+        print(f'{batch}x{input_channel}x{H}x{W}x{output_channel}x{kH}x{kW}x{stride}x{pad}: cudnn: {cudnn_tflops:.2f} TFLOPS')
+
+
+if __name__ == "__main__":
+
+    Ampere_FP16_Helix_op_level_Conv_benchmark(backend="cuda")
+    Ampere_FP16_cudnn_op_level_Conv_benchmark()

@@ -1,0 +1,24 @@
+"""Selection + execution of one fp32 convolution (reference: scripts/Ampere_FP32/Ampere_FP32_conv.py:89-151)."""
+import os
+
+import _bootstrap  # noqa: F401
+
+root_path = os.getcwd()
+
+
+def cost_model(prof_dict, M, N, K):
+    from helix_b200 import costmodel
+    return costmodel.sgemm_cost_model(prof_dict, M, N, K)
+
+
+def get_Ampere_FP32_conv_Helix_result(prof_dict, batch, input_channel, H, W, output_channel, kH, kW, stride, pad, backend="cuda"):
+    if backend != "cuda":
+        raise ValueError("only backend='cuda' is available (no TVM code generation in this build)")
+    from helix_b200 import harness
+    return harness.conv_f32_result(prof_dict, batch, input_channel, H, W, output_channel, kH, kW, stride, pad)
+
+
+def get_Ampere_FP32_conv_cudnn_result(batch, input_channel, H, W, output_channel, kH, kW, stride, pad):
+    import torch
+    from helix_b200 import harness
+    return harness.cudnn_conv_result(batch, input_channel, H, W, output_channel, kH, kW, stride, pad, dtype=torch.float32)

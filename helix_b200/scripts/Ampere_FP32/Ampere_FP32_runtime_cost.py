@@ -1,0 +1,39 @@
+"""Selection overhead vs. op time, fp32 (reference: scripts/Ampere_FP32/Ampere_FP32_runtime_cost.py:7-39)."""
+import os
+import time
+
+import _bootstrap  # noqa: F401
+
+root_path = os.getcwd()
+
+
+def cost_model(prof_dict, M, N, K):
+    from helix_b200 import costmodel
+    return costmodel.sgemm_cost_model(prof_dict, M, N, K)
+
+
+def get_Helix_runtime_cost(prof_dict, M, N, K):
+    from helix_b200 import harness, ops
+    from helix_b200._lib import OP_GEMM_F32
+    T1 = time.perf_counter()
+    for i in range(100):
+        best_config = cost_model(prof_dict, M, N, K)
+    T2 = time.perf_counter()
+    bm, bn, bk, tm, tn = best_config[:5]
+    cost = harness.time_gemm_f32(M, N, K, ops.make_cfg(OP_GEMM_F32, tile_m=bm, tile_n=bn, tile_k=bk, thread_m=tm, thread_n=tn))
+    return (T2 - T1) / 100 / 1000, cost
+
+
+def Ampere_FP32_runtime_cost():
+    from helix_b200 import costmodel
+    prof_dict = costmodel.load(f'{root_path}/build/prof_dict/Ampere_FP32_cost_model.dict')
+
+    MNKList = [(64, 64, 64), (128, 128, 128), (256, 256, 256), (512, 512, 512), (1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096)]
+    for M, N, K in MNKList:
+        runtime_cost, op_cost = get_Helix_runtime_cost(prof_dict, M, N, K)
+        print(f'The runtime cost of {M}x{N}x{K} is {runtime_cost} ms, and the op cost is {op_cost} ms.')
+
+
+if __name__ == '__main__':
+
+    Ampere_FP32_runtime_cost()

@@ -1,0 +1,34 @@
+"""Op-level fp32 GEMM sweep (reference: scripts/Ampere_FP32/benchmark_Ampere_FP32_gemm.py:9-23)."""
+import os
+
+import _bootstrap  # noqa: F401
+from utils.get_benchmark_shape_list import get_gemm_op_MNKList
+from Ampere_FP32.Ampere_FP32_gemm import get_Ampere_FP32_gemm_cublas_result
+
+root_path = os.getcwd()
+
+
+def Ampere_FP32_Helix_op_level_GEMM_benchmark(backend="cuda", gpus=1, limit=0):
+    from helix_b200 import costmodel, harness
+    prof_dict = costmodel.load(f'{root_path}/build/prof_dict/Ampere_FP32_cost_model.dict')
+
+    MNKList = get_gemm_op_MNKList()
+    if limit:
+        MNKList = MNKList[:limit]
+    rows = harness.run_shape_list(MNKList, harness.worker_gemm_f32, prof_dict, gpus)
+    for (M, N, K), row in zip(MNKList, rows):
+        helix_tflops = row["tflops"]
+        print(f'{M}x{N}x{K}: Helix: {helix_tflops:.2f} TFLOPS')
+    return rows
+
+
+def Ampere_FP32_cublas_op_level_GEMM_benchmark():
+    for M, N, K in get_gemm_op_MNKList():
+        _, cublas_tflops = get_Ampere_FP32_gemm_cublas_result(M, N, K)
+        print(f'{M}x{N}x{K}: cublas: {cublas_tflops:.2f} TFLOPS')
+
+
+if __name__ == "__main__":
+
+    Ampere_FP32_Helix_op_level_GEMM_benchmark(backend="cuda")
+    Ampere_FP32_cublas_op_level_GEMM_benchmark()

@@ -1,0 +1,24 @@
+"""CLI of the profiling step (reference: scripts/profile_template.py:9-24)."""
+import argparse
+import time
+
+import _bootstrap  # noqa: F401
+
+CPU_NOTE = "{} is the reference's TVM-generated CPU backend; this build covers the GPU backends only"
+
+if __name__ == "__main__":
+    parser = argparse.ArgumentParser(description="Get runtime cost of an operation")
+    parser.add_argument("-b", "--backend", type=str, choices=['Ampere_FP16', 'Ampere_FP32', 'x86_CPU', 'ARM_CPU'], default='Ampere_FP16', help="backend")
+    args = parser.parse_args()
+
+    T1 = time.perf_counter()
+    if args.backend == 'Ampere_FP16':
+        from Ampere_FP16.profile_Ampere_FP16 import profile_Helix_Ampere_FP16_gemm_kernel
+        profile_Helix_Ampere_FP16_gemm_kernel()
+    elif args.backend == 'Ampere_FP32':
+        from Ampere_FP32.profile_Ampere_FP32 import profile_Helix_Ampere_FP32_gemm_kernel
+        profile_Helix_Ampere_FP32_gemm_kernel()
+    else:
+        print(CPU_NOTE.format(args.backend))
+    T2 = time.perf_counter()
+    print(f'Profiling time: {T2-T1} seconds')

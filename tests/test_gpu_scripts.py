@@ -1,0 +1,72 @@
+"""GPU: the drop-in scripts end to end (build -> fast profile -> cost model -> sweeps) in a scratch working
+directory, the way the reference is driven from its repository root."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SCRIPTS = os.path.join(ROOT, "helix_b200", "scripts")
+
+
+def _run(cwd, script, *args):
+    env = dict(os.environ, PYTHONPATH=SCRIPTS)
+    out = subprocess.run([sys.executable, os.path.join(SCRIPTS, script), *args], capture_output=True, text=True,
+                         env=env, cwd=cwd, timeout=900)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    return out.stdout
+
+
+@pytest.fixture(scope="module")
+def workdir(tmp_path_factory):
+    d = tmp_path_factory.mktemp("helix_run")
+    _run(d, "build_template.py", "-b", "Ampere_FP16")
+    _run(d, "changed_profile.py", "-b", "Ampere_FP16")
+    return d
+
+
+def test_build_and_profile_leave_the_reference_artefacts(workdir):
+    assert (workdir / "build" / "bin_fp16" / "MANIFEST").exists()
+    text = (workdir / "build" / "prof_dict" / "Ampere_FP16_cost_model.dict").read_text()
+    d = eval(text.splitlines()[0])
+    assert any(len(k) == 6 and k[0] == 0 for k in d) and any(len(k) == 6 and k[0] != 0 for k in d)
+    assert 20.0 < d[("dram_gbs_per_sm",)] < 200.0 and 2000.0 < d[("hbm_gbs",)] < 9000.0
+
+
+def test_op_level_sweep_prints_the_reference_lines(workdir):
+    out = _run(workdir, "benchmark_op_level_eval.py", "-o", "GEMM", "-b", "Ampere_FP16", "-s", "Helix", "--limit", "4")
+    lines = [l for l in out.splitlines() if "Helix:" in l]
+    assert len(lines) == 4 and lines[0].startswith("2x1024x1024: Helix: ") and lines[0].endswith(" TFLOPS")
+    out = _run(workdir, "benchmark_op_level_eval.py", "-o", "Conv", "-b", "Ampere_FP16", "-s", "Helix", "--limit", "2")
+    assert sum("Helix:" in l for l in out.splitlines()) == 2
+
+
+def test_runtime_cost_prints_the_reference_line(workdir):
+    out = _run(workdir, "runtime_cost.py", "-b", "Ampere_FP16")
+    lines = [l for l in out.splitlines() if l.startswith("The runtime cost of ")]
+    assert len(lines) == 7 and "4096x4096x4096" in lines[-1] and "and the op cost is" in lines[-1]
+
+
+def test_cost_model_prediction_tracks_measurement(workdir):
+    """The model's choice must be close to the exhaustive best ("Oracle" vs "Default" in the reference's
+    benchmark_Ampere_FP16_performance_comparison.py:44-93) and its time estimate within a factor of two."""
+    sys.path.insert(0, ROOT)
+    from helix_b200 import costmodel, harness
+    d = costmodel.load(str(workdir / "build" / "prof_dict" / "Ampere_FP16_cost_model.dict"))
+    for (M, N, K) in [(4096, 4096, 4096), (8192, 768, 3072), (16, 11008, 4096), (2048, 2304, 768)]:
+        key = costmodel.cost_model(d, M, N, K)
+        t_default = harness.time_gemm_f16(M, N, K, harness.key_to_cfg(key))
+        pred = costmodel.predicted_time(d, key, M, N, K)
+        assert 0.5 <= pred / t_default <= 2.0, (M, N, K, key, pred, t_default)
+        best = min(harness.time_gemm_f16(M, N, K, harness.key_to_cfg(k)) for k in costmodel.gemm_keys()
+                   if k[5] == 0 or costmodel.gemm_time(d, k, M, N, K) < float("inf"))
+        assert t_default <= 1.3 * best, (M, N, K, key, t_default, best)
+
+
+def test_fp32_backend_profile_and_sweep(workdir):
+    _run(workdir, "build_template.py", "-b", "Ampere_FP32")
+    _run(workdir, "changed_profile.py", "-b", "Ampere_FP32")
+    out = _run(workdir, "benchmark_op_level_eval.py", "-o", "GEMM", "-b", "Ampere_FP32", "-s", "Helix", "--limit", "2")
+    assert sum("Helix:" in l for l in out.splitlines()) == 2

@@ -1,0 +1,221 @@
+"""CPU-only tests of the host side: cost model, shape suites, drop-in scripts, sharding, rank aggregation."""
+import importlib
+import json
+import os
+import subprocess
+import sys
+import time
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SCRIPTS = os.path.join(ROOT, "helix_b200", "scripts")
+
+from helix_b200 import costmodel, shard, workloads  # noqa: E402
+
+
+def synthetic_dict():
+    d = {("sm_count",): 148, ("dram_gbs_per_sm",): 40.0, ("hbm_gbs",): 6000.0}
+    slab = {256: 0.45e-6, 128: 0.31e-6, 64: 0.27e-6, 32: 0.26e-6, 16: 0.25e-6}
+    for key in costmodel.gemm_keys():
+        d[key] = (4e-6, slab[key[2]])
+    for bn in (256, 128, 64):
+        d[("streamk_overhead", bn)] = 8e-6 + bn * 4e-8
+        d[("conv_slab", bn)] = 0.6e-6
+    for key in costmodel.gemv_keys():
+        d[key] = (3e-6 + 2e-6 * (key[5] > 1), 1.0 / 5.5e12)
+    return d
+
+
+def test_dictionary_round_trip_is_a_python_literal(tmp_path):
+    d = synthetic_dict()
+    p = tmp_path / "build" / "prof_dict" / "Ampere_FP16_cost_model.dict"
+    costmodel.save(d, str(p))
+    text = p.read_text()
+    assert "\n" not in text.strip()
+    assert eval(text) == d            # the reference loads the file with eval(lines[0])
+    assert costmodel.load(str(p)) == d
+
+
+def test_cost_model_picks_sensible_configurations():
+    d = synthetic_dict()
+    big = costmodel.cost_model(d, 8192, 8192, 8192)
+    assert big[0] != 0 and big[2] == 256 and big[4] == 0
+    gemv = costmodel.cost_model(d, 1, 4096, 4096)
+    assert gemv[0] == 0                                   # first element 0 <=> GEMV, as in the reference's keys
+    tall = costmodel.cost_model(d, 7680, 2, 2560)         # N <= 8: GEMV with the matrix on M
+    assert tall[0] == 0
+    skinny = costmodel.cost_model(d, 16, 11008, 4096)
+    assert skinny[0] != 0 and skinny[4] == 1              # M = 16 goes on the UMMA N axis
+    conv = costmodel.cost_model(d, 25088, 128, 1152, conv=True)
+    assert conv[0] != 0 and conv[4] == 0                  # no swap for the gathering producer
+    # unlike the reference's model, K matters: a deep K amortises the stream-K fix-up on a ragged tile count
+    assert costmodel.cost_model(d, 2048, 14336, 256)[5] == 0
+    assert costmodel.cost_model(d, 128, 4096, 11008)[5] == 1
+
+
+def test_cost_model_wave_quantisation_uses_device_sm_count():
+    d = synthetic_dict()
+    key = (4, 128, 256, 1, 0, 0)
+    t148 = costmodel.gemm_time(d, key, 128 * 148, 256, 4096)
+    t149 = costmodel.gemm_time(d, key, 128 * 149, 256, 4096)      # one tile more than a wave
+    assert t149 > 1.8 * t148 - 4e-6
+    d[("sm_count",)] = 160
+    assert costmodel.gemm_time(d, key, 128 * 149, 256, 4096) == pytest.approx(t148, rel=0.05)
+
+
+def test_sgemm_cost_model():
+    d = {("sm_count",): 148}
+    for key in costmodel.sgemm_keys():
+        d[key] = 1e-7 * key[0] * key[1] / (64 * 64) * (1.2 if key[0] < 128 else 1.0)
+    assert costmodel.sgemm_cost_model(d, 4096, 4096, 4096)[:2] == (128, 128)
+    small = costmodel.sgemm_cost_model(d, 256, 256, 1024)
+    assert small[0] * small[1] < 128 * 128                       # few tiles: smaller tiles fill more SMs
+
+
+def test_workloads_match_the_published_totals():
+    units = workloads.model_level_sweep()
+    assert len(units) == 125 and sum(u["kind"] == "conv" for u in units) == 53
+    gemm = sum(workloads.unit_flops(u) for u in units if u["kind"] == "gemm")
+    conv = sum(workloads.unit_flops(u) for u in units if u["kind"] == "conv")
+    assert gemm == pytest.approx(1546.19e9, rel=1e-4) and conv == pytest.approx(261.58e9, rel=1e-4)
+    assert len({u["shape"] for u in units if u["kind"] == "conv"}) == 23
+    assert sum(workloads.unit_bytes(u) for u in units if u["kind"] == "conv") == pytest.approx(1440.6e6, rel=1e-3)
+
+
+def test_lpt_partition_balances_and_is_deterministic():
+    costs = [float(workloads.unit_flops(u)) for u in workloads.model_level_sweep()]
+    for parts in (1, 2, 4, 8):
+        p = workloads.lpt_partition(costs, parts)
+        assert sorted(i for lst in p for i in lst) == list(range(len(costs)))
+        loads = [sum(costs[i] for i in lst) for lst in p]
+        assert max(loads) <= sum(costs) / parts + max(costs)
+        assert p == workloads.lpt_partition(costs, parts)
+
+
+def test_shape_suites_have_the_reference_structure():
+    sys.path.insert(0, SCRIPTS)
+    try:
+        m = importlib.import_module("utils.get_benchmark_shape_list")
+    finally:
+        sys.path.remove(SCRIPTS)
+    gemm = m.get_gemm_op_MNKList()
+    assert len(gemm) == 60 * 16 + 8 * 10 and all(len(s) == 3 for s in gemm)
+    bert, llama2, gpt2 = m.get_llm_opset_MNKList()
+    assert (len(bert), len(llama2), len(gpt2)) == (4380, 240, 5760)     # same counts as the reference's lists
+    alex, res, goog = m.get_cnn_opset_shape_List()
+    assert (len(alex), len(res), len(goog)) == (85, 340, 952)
+    assert all(len(s) == 9 for s in m.get_conv_op_shape_list())
+
+
+@pytest.mark.parametrize("script,args,expect", [
+    ("benchmark_op_level_eval.py", ["-o", "GEMM", "-b", "x86_CPU", "-s", "Helix"], "GEMM x86_CPU Helix is not supported"),
+    ("benchmark_model_level_eval.py", ["-m", "CNN", "-b", "ARM_CPU", "-s", "acl"], "CNN ARM_CPU acl is not supported"),
+    ("runtime_cost.py", ["-b", "x86_CPU"], "covers the GPU backends only"),
+])
+def test_cli_flags_and_dispatch_without_a_gpu(script, args, expect):
+    env = dict(os.environ, PYTHONPATH=SCRIPTS)
+    out = subprocess.run([sys.executable, os.path.join(SCRIPTS, script)] + args, capture_output=True, text=True,
+                         env=env, cwd=ROOT, timeout=120)
+    assert out.returncode == 0, out.stderr
+    assert expect in out.stdout
+
+
+def test_backend_modules_import_lazily_and_expose_the_reference_names():
+    sys.path.insert(0, SCRIPTS)
+    try:
+        for mod, names in [
+            ("Ampere_FP16.build_Ampere_FP16", ["build_Helix_Ampere_FP16_gemm_kernel", "build_cublas_FP16_gemm_kernel",
+                                               "build_cudnn_FP16_conv_kernel", "is_valid_config", "compile_kernel"]),
+            ("Ampere_FP16.profile_Ampere_FP16", ["profile_Helix_Ampere_FP16_gemm_kernel"]),
+            ("Ampere_FP16.changed_profile_Ampere_FP16", ["profile_Helix_Ampere_FP16_gemm_kernel"]),
+            ("Ampere_FP16.Ampere_FP16_gemm", ["cost_model", "get_Ampere_FP16_gemm_Helix_result", "get_Ampere_FP16_gemm_cublas_result"]),
+            ("Ampere_FP16.Ampere_FP16_conv", ["cost_model", "get_Ampere_FP16_conv_Helix_result", "get_Ampere_FP16_conv_cudnn_result"]),
+            ("Ampere_FP16.Ampere_FP16_runtime_cost", ["Ampere_FP16_runtime_cost", "get_Helix_runtime_cost"]),
+            ("Ampere_FP16.benchmark_Ampere_FP16_gemm", ["Ampere_FP16_Helix_op_level_GEMM_benchmark"]),
+            ("Ampere_FP16.benchmark_Ampere_FP16_conv", ["Ampere_FP16_Helix_op_level_Conv_benchmark"]),
+            ("Ampere_FP16.benchmark_Ampere_FP16_model_level_LLM", ["Ampere_FP16_Helix_model_level_LLM_benchmark"]),
+            ("Ampere_FP16.benchmark_Ampere_FP16_model_level_CNN", ["Ampere_FP16_Helix_model_level_CNN_benchmark"]),
+            ("Ampere_FP32.build_Ampere_FP32", ["build_Helix_Ampere_FP32_gemm_kernel", "build_cublas_FP32_gemm_kernel",
+                                               "build_cudnn_FP32_conv_kernel", "get_copy_value"]),
+            ("Ampere_FP32.profile_Ampere_FP32", ["profile_Helix_Ampere_FP32_gemm_kernel"]),
+            ("Ampere_FP32.Ampere_FP32_gemm", ["cost_model", "get_Ampere_FP32_gemm_Helix_result"]),
+            ("Ampere_FP32.Ampere_FP32_conv", ["cost_model", "get_Ampere_FP32_conv_Helix_result"]),
+            ("Ampere_FP32.Ampere_FP32_runtime_cost", ["Ampere_FP32_runtime_cost"]),
+            ("Ampere_FP32.benchmark_Ampere_FP32_model_level_CNN", ["Ampere_FP32_Helix_model_level_CNN_benchmark"]),
+        ]:
+            m = importlib.import_module(mod)
+            for n in names:
+                assert callable(getattr(m, n)), (mod, n)
+        cm = importlib.import_module("Ampere_FP16.Ampere_FP16_gemm").cost_model
+        assert cm(synthetic_dict(), 4096, 4096, 4096)[2] == 256
+    finally:
+        sys.path.remove(SCRIPTS)
+
+
+# ----------------------------------------------------------------------------- sharded sweep with a fake device
+def fake_device(device, unit, scale):
+    time.sleep(unit["cost"] * scale)
+    return {"shape": unit["name"], "ms": unit["cost"] * 1e3}
+
+
+_seen = {"n": 0}
+
+
+def dying_device(device, unit, scale):
+    _seen["n"] += 1                        # per worker process (forked), so this counts its own units
+    if device == 1 and _seen["n"] == 3:
+        os._exit(17)                       # a worker that exits mid-sweep, between units
+    return fake_device(device, unit, scale)
+
+
+def test_sharded_sweep_two_workers_resume_and_requeue(tmp_path):
+    units = [{"name": f"u{i}", "cost": 0.01 * (1 + i % 4)} for i in range(12)]
+    costs = [u["cost"] for u in units]
+    journal = str(tmp_path / "sweep.jsonl")
+    rows, stats = shard.run_sharded(units, fake_device, [0, 1], costs, journal, fn_args=(1.0,), start_method="fork")
+    assert sorted(rows) == list(range(12)) and stats["unfinished"] == 0 and not stats["failed_workers"]
+    assert {r["device"] for r in rows.values()} == {0, 1}
+    assert len(open(journal).read().splitlines()) == 12
+    # resume: nothing left to do, no worker work repeated
+    rows2, stats2 = shard.run_sharded(units, fake_device, [0, 1], costs, journal, fn_args=(1.0,), start_method="fork")
+    assert stats2["resumed"] == 12 and stats2["rounds"] == 0 and sorted(rows2) == list(range(12))
+    # a worker dies on the host between units: the survivor finishes its share
+    journal2 = str(tmp_path / "sweep2.jsonl")
+    rows3, stats3 = shard.run_sharded(units, dying_device, [0, 1], costs, journal2, fn_args=(0.1,), start_method="fork")
+    assert sorted(rows3) == list(range(12)) and stats3["failed_workers"] == [1] and stats3["rounds"] == 2
+    # a torn last line (killed mid-write) is ignored on resume
+    with open(journal2, "a") as f:
+        f.write('{"index": 99, "dev')
+    assert sorted(shard.read_journal(journal2)) == list(range(12))
+
+
+# ----------------------------------------------------------------------------- rank aggregation over gloo
+WORKER = r"""
+import os, sys
+sys.path.insert(0, {root!r})
+import torch.distributed as dist
+from helix_b200 import dist_util
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:{port}", rank=int(sys.argv[1]), world_size=2)
+rank = dist.get_rank()
+dist_util.barrier(dist)
+slowest = dist_util.max_over_ranks(1.0 + rank, dist)
+tput = dist_util.aggregate_throughput(10.0, 1.0 + rank, dist)
+print(f"{{rank}} {{slowest}} {{tput}}")
+dist.destroy_process_group()
+"""
+
+
+def test_max_over_ranks_and_aggregate_throughput_world_size_2(tmp_path):
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    script = tmp_path / "w.py"
+    script.write_text(WORKER.format(root=ROOT, port=port))
+    procs = [subprocess.Popen([sys.executable, str(script), str(r)], stdout=subprocess.PIPE, text=True) for r in (0, 1)]
+    outs = [p.communicate(timeout=120)[0].split() for p in procs]
+    assert all(p.returncode == 0 for p in procs)
+    for rank, (r, slowest, tput) in enumerate(outs):
+        assert int(r) == rank and float(slowest) == 2.0 and float(tput) == pytest.approx(10.0)   # 2 x 10 units / 2 s
