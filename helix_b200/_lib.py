@@ -58,7 +58,10 @@ class Launch(ctypes.Structure):
                 ("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("batch", ctypes.c_int),
                 ("stride_a", ctypes.c_int64), ("stride_b", ctypes.c_int64), ("stride_c", ctypes.c_int64),
                 ("conv", ctypes.c_int * 9), ("trans_a", ctypes.c_int), ("ldc_inner", ctypes.c_int64),
-                ("ws", ctypes.c_void_p), ("ws_bytes", ctypes.c_size_t)]
+                ("ws", ctypes.c_void_p), ("ws_bytes", ctypes.c_size_t), ("flags", ctypes.c_uint32)]
+
+
+LAUNCH_INDEPENDENT = 1
 
 
 # name -> (restype, argtypes); every symbol include/helix_b200.h declares

@@ -84,18 +84,20 @@ int dispatch(const helix_launch_t* l, void* status_dev, cudaStream_t stream) {
       if ((rc = current_device(&info, true)) != HELIX_OK) return rc;
       rc = helix::gemm_f16_launch(cfg, l->a, l->lda, l->b, l->ldb, l->c, l->ldc, l->M, l->N, l->K, l->batch,
                                   l->stride_a, l->stride_b, l->stride_c, l->ws, l->ws_bytes,
-                                  static_cast<int*>(status_dev), info.sm_count, stream, &n);
+                                  static_cast<int*>(status_dev), info.sm_count,
+                                  (l->flags & HELIX_LAUNCH_INDEPENDENT) != 0, stream, &n);
       break;
     case HELIX_OP_GEMV_F16:
       if ((rc = current_device(&info, false)) != HELIX_OK) return rc;
       rc = helix::gemv_f16_launch(cfg, l->a, l->lda, l->b, l->ldb, l->c, l->ldc, l->ldc_inner, l->N, l->K, l->M,
-                                  l->ws, l->ws_bytes, info.sm_count, stream, &n);
+                                  l->ws, l->ws_bytes, info.sm_count, (l->flags & HELIX_LAUNCH_INDEPENDENT) != 0,
+                                  stream, &n);
       break;
     case HELIX_OP_CONV_F16: {
       if ((rc = current_device(&info, true)) != HELIX_OK) return rc;
       const helix::ConvGeom g = conv_geom(l->conv);
       rc = helix::conv_f16_launch(cfg, l->a, l->b, l->c, g, l->ws, l->ws_bytes, static_cast<int*>(status_dev),
-                                  info.sm_count, stream, &n);
+                                  info.sm_count, (l->flags & HELIX_LAUNCH_INDEPENDENT) != 0, stream, &n);
       break;
     }
     case HELIX_OP_GEMM_F32:

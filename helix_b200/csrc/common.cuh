@@ -207,6 +207,29 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---------------------------------------------------------------- TMA store (shared -> global)
+// 3-D tiled store of one box; elements outside the tensor are not written.  x * sizeof(element)
+// must be a multiple of 16 bytes and no coordinate may be negative.
+__device__ __forceinline__ void tma_store_3d(const void* desc, const void* smem_src, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+          reinterpret_cast<uint64_t>(desc)),
+      "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// until the bulk stores committed by this thread have finished READING shared memory
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// until they have completed altogether
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// launch_dependents: the next kernel on the stream may start being scheduled (when it was launched
+// with the programmatic-serialization attribute).  wait: returns once every kernel this one depends
+// on has completed and its memory is visible.  Both are no-ops for a plain launch.
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---------------------------------------------------------------- misc loads
 __device__ __forceinline__ uint4 ldg_stream_16(const void* p) {
   uint4 v;

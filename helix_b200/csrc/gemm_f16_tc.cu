@@ -46,6 +46,7 @@ constexpr int kConvProducerWarps = 8;       // gather warps: 16 tile rows each, 
 constexpr int kConvRowsPerThread = 4;
 constexpr int kConvThreads = kConvProducerWarps * 32 + 32 + 128;  // + MMA warp + 4 epilogue warps
 constexpr int kGemmThreads = 32 + 32 + 128;                       // TMA warp + MMA warp + 4 epilogue warps
+constexpr int kStoreStagingBytes = 4 * 32 * 128;                  // one 32-row x 128-byte box per epilogue warp
 
 enum OutMode { kOutDirect = 0, kOutSplitSlice = 1, kOutStreamSlot = 2 };
 
@@ -69,6 +70,8 @@ struct GemmParams {
   int dp_rounds;   // whole tiles each CTA computes on its own
   int sk_tiles;    // tiles whose K slabs are dealt out
   int sk_upc;      // K slabs per CTA in the dealt part (<= num_kb, so a range touches <= 2 tiles)
+  int tma_store;   // whole tiles leave through shared memory and a TMA store (tmap_c is valid)
+  int independent; // nothing read or written here is written by the kernel queued just before
   int* status;
   // convolution only
   const __half* x;
@@ -149,20 +152,26 @@ struct SmemLayout {
 template <int BN, bool CONV>
 __global__ void __launch_bounds__(CONV ? kConvThreads : kGemmThreads, 1)
 gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                   const GemmParams p) {
+                   const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
   using L = SmemLayout<BN>;
   constexpr int kProducerWarps = CONV ? kConvProducerWarps : 1;
   constexpr int kMmaWarp = kProducerWarps;
   constexpr int kTmemCols = L::tmem_cols();
   constexpr uint32_t kIdesc = umma_idesc_f16(kBM, BN);
 
+  // The next kernel on the stream may be scheduled as soon as every CTA of this one has started:
+  // its CTAs then fill SMs as ours retire instead of waiting for the whole grid to drain.
+  griddep_launch_dependents();
+
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int stages = p.stages;
   uint8_t* sA = smem;
   uint8_t* sB = smem + (size_t)stages * kATileBytes;
+  // output staging for the TMA store: one 32-row x 128-byte swizzled box per epilogue warp
+  uint8_t* sC = smem + (size_t)stages * L::kStageBytes;
   // barriers: full[8], empty[8], tmem_full[2], tmem_empty[2]; then tmem pointer, abort flag, conv table
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)stages * L::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sC + kStoreStagingBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + 8;
   uint64_t* tmem_full = bars + 16;
@@ -189,6 +198,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     mbar_fence_init();
     if (!CONV) tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (p.tma_store) tma_prefetch_desc(&tmap_c);
   }
   if (CONV) {
     // (r, s, c) of every 8-channel chunk of the K axis, K ordered (r, s, c)
@@ -207,6 +217,11 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_smem;
+
+  // Everything above touched only this CTA's shared memory and TMEM, so it may overlap the tail of
+  // the preceding kernel.  From here on global memory is read and written: unless the caller
+  // declared the launch independent of its predecessor, wait for that kernel to complete.
+  if (!p.independent) griddep_wait();
 
   if (warp < kProducerWarps) {
     // ------------------------------------------------------------------ producers
@@ -367,6 +382,66 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       const int trow = quarter * 32 + lane;      // row inside the tile
       const int row = w.m_blk * kBM + trow;      // index on the 128-row (A side) axis
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      if constexpr (BN >= 64) {
+        if (p.tma_store && w.mode == kOutDirect) {
+          // Fast path: 64 columns at a time go TMEM -> registers -> fp16 -> this warp's swizzled
+          // 32 x 128-byte staging box -> one TMA store (full 128-byte lines, edges clipped by the
+          // tensor map).  The TMEM load of the next 64 columns is in flight while the current ones
+          // are converted and stored.
+          uint8_t* stage_box = sC + (size_t)quarter * (32 * 128);
+          const uint32_t row_base = smem_u32(stage_box) + lane * 128;
+          uint32_t ra[32], rb[32], na[32], nb[32];
+          // registers of a TMEM load are valid only after tcgen05.wait::ld, so the two register sets
+          // alternate by name instead of being copied
+          auto emit = [&](const uint32_t (&lo)[32], const uint32_t (&hi)[32], int c0) {
+            const int col0 = w.n_blk * BN + c0;
+            if (col0 >= p.PN) return;   // warp-uniform: padding columns only
+            if (lane == 0) tma_store_wait_read();   // the previous box has left the staging buffer
+            __syncwarp();
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+              const uint32_t* src = ch < 4 ? &lo[ch * 8] : &hi[(ch - 4) * 8];
+              __half2 h0 = __floats2half2_rn(__uint_as_float(src[0]), __uint_as_float(src[1]));
+              __half2 h1 = __floats2half2_rn(__uint_as_float(src[2]), __uint_as_float(src[3]));
+              __half2 h2 = __floats2half2_rn(__uint_as_float(src[4]), __uint_as_float(src[5]));
+              __half2 h3 = __floats2half2_rn(__uint_as_float(src[6]), __uint_as_float(src[7]));
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + ((ch ^ (lane & 7)) << 4)),
+                           "r"(*reinterpret_cast<uint32_t*>(&h0)), "r"(*reinterpret_cast<uint32_t*>(&h1)),
+                           "r"(*reinterpret_cast<uint32_t*>(&h2)), "r"(*reinterpret_cast<uint32_t*>(&h3))
+                           : "memory");
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&tmap_c, stage_box, col0, w.m_blk * kBM + quarter * 32, w.b);
+              tma_store_commit();
+            }
+          };
+          tmem_ld_32x32b_x32(taddr, ra);
+          tmem_ld_32x32b_x32(taddr + 32, rb);
+#pragma unroll
+          for (int c0 = 0; c0 < BN; c0 += 128) {
+            tmem_ld_wait();
+            if (c0 + 64 < BN) {
+              tmem_ld_32x32b_x32(taddr + c0 + 64, na);
+              tmem_ld_32x32b_x32(taddr + c0 + 96, nb);
+            }
+            emit(ra, rb, c0);
+            if (c0 + 64 < BN) {
+              tmem_ld_wait();
+              if (c0 + 128 < BN) {
+                tmem_ld_32x32b_x32(taddr + c0 + 128, ra);
+                tmem_ld_32x32b_x32(taddr + c0 + 160, rb);
+              }
+              emit(na, nb, c0 + 64);
+            }
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+          continue;
+        }
+      }
       constexpr int kChunk = BN >= 32 ? 32 : 16;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += kChunk) {
@@ -436,6 +511,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
     }
+    if (p.tma_store && lane == 0) tma_store_wait_all();   // staged boxes are in global memory before exit
   }
 
   // ------------------------------------------------------------------ teardown
@@ -601,7 +677,8 @@ void gemm_f16_get_config(int idx, helix_cfg_t* out) {
 }
 
 static int max_stages(int bn, bool conv) {
-  const int budget = 227 * 1024 - 1024 /*alignment slack*/ - 256 /*barriers*/ - (conv ? kConvTableEntries * 4 : 0);
+  const int budget = 227 * 1024 - 1024 /*alignment slack*/ - 256 /*barriers*/ - kStoreStagingBytes -
+                     (conv ? kConvTableEntries * 4 : 0);
   int s = budget / (kATileBytes + bn * kBK * 2);
   return std::min(s, 8);
 }
@@ -690,8 +767,8 @@ size_t gemm_f16_workspace_bytes(const helix_cfg_t* cfg, int M, int N, int K, int
 }
 
 template <int BN, bool CONV>
-static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
-                                  size_t smem, cudaStream_t stream) {
+static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                                  const GemmParams& p, int grid, size_t smem, cudaStream_t stream) {
   constexpr int threads = CONV ? kConvThreads : kGemmThreads;
   auto kern = gemm_f16_tc_kernel<BN, CONV>;
   // the opt-in shared-memory size is sticky per function and device: raise it only when needed
@@ -707,13 +784,31 @@ static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, 
       granted[dev] = smem;
     }
   }
-  kern<<<grid, threads, smem, stream>>>(ta, tb, p);
-  return cudaGetLastError();
+  // Programmatic dependent launch: this kernel may be scheduled while the previous kernel on the
+  // stream drains; the kernel itself waits (griddepcontrol.wait) before it touches global memory
+  // unless the launch was declared independent.
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(grid);
+  lc.blockDim = dim3(threads);
+  lc.dynamicSmemBytes = smem;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&lc, kern, ta, tb, tc, p);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    kern<<<grid, threads, smem, stream>>>(ta, tb, tc, p);   // plain launch: the in-kernel wait is a no-op
+    e = cudaGetLastError();
+  }
+  return e;
 }
 
 static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& ta, const CUtensorMap& tb,
                          GemmParams& p, void* C, int64_t ldc, int64_t sc, void* ws, size_t ws_bytes, int sm_count,
-                         cudaStream_t stream, int64_t* launches) {
+                         bool independent, cudaStream_t stream, int64_t* launches) {
   const int bn = cfg.tile_n;
   p.tiles_m = (p.PM + kBM - 1) / kBM;
   p.tiles_n = (p.PN + bn - 1) / bn;
@@ -760,12 +855,21 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
       reduce = true;
     }
   }
-  const size_t smem = 1024 + (size_t)p.stages * (kATileBytes + bn * kBK * 2) + 256 + (conv ? kConvTableEntries * 4 : 0);
+  const size_t smem = 1024 + (size_t)p.stages * (kATileBytes + bn * kBK * 2) + kStoreStagingBytes + 256 +
+                      (conv ? kConvTableEntries * 4 : 0);
+  // whole tiles of a row-major, 16-byte-aligned C leave through a TMA store
+  CUtensorMap tc = tb;
+  p.tma_store = 0;
+  if (!p.swap && bn >= 64 && (ldc & 7) == 0 && (sc & 7) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+      make_tmap(&tc, C, p.PN, p.PM, p.batch, ldc, sc, 32) == HELIX_OK)
+    p.tma_store = 1;
+  // a launch that shares its workspace with its neighbours on the stream is never independent of them
+  p.independent = (independent && !fixup && !reduce) ? 1 : 0;
   cudaError_t e = cudaErrorInvalidValue;
 #define HELIX_BN_CASE(BNV)                                                                 \
   case BNV:                                                                                \
-    e = conv ? launch_variant<BNV, true>(ta, tb, p, grid, smem, stream)                    \
-             : launch_variant<BNV, false>(ta, tb, p, grid, smem, stream);                  \
+    e = conv ? launch_variant<BNV, true>(ta, tb, tc, p, grid, smem, stream)                \
+             : launch_variant<BNV, false>(ta, tb, tc, p, grid, smem, stream);              \
     break;
   switch (bn) {
     HELIX_BN_CASE(256)
@@ -798,7 +902,8 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
 
 int gemm_f16_launch(const helix_cfg_t* cfg_in, const void* A, int64_t lda, const void* B, int64_t ldb, void* C,
                     int64_t ldc, int M, int N, int K, int batch, int64_t sa, int64_t sb, int64_t sc, void* ws,
-                    size_t ws_bytes, int* status_dev, int sm_count, cudaStream_t stream, int64_t* launches) {
+                    size_t ws_bytes, int* status_dev, int sm_count, bool independent, cudaStream_t stream,
+                    int64_t* launches) {
   if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) return HELIX_ERR_INVALID;
   if (batch <= 0) batch = 1;
   if (lda == 0) lda = K;
@@ -832,11 +937,12 @@ int gemm_f16_launch(const helix_cfg_t* cfg_in, const void* A, int64_t lda, const
     if ((rc = make_tmap(&ta, B, K, N, batch, ldb, sb, kBM)) != HELIX_OK) return rc;
     if ((rc = make_tmap(&tb, A, K, M, batch, lda, sa, cfg.tile_n)) != HELIX_OK) return rc;
   }
-  return launch_common(cfg, false, ta, tb, p, C, ldc, sc, ws, ws_bytes, sm_count, stream, launches);
+  return launch_common(cfg, false, ta, tb, p, C, ldc, sc, ws, ws_bytes, sm_count, independent, stream, launches);
 }
 
 int conv_f16_launch(const helix_cfg_t* cfg_in, const void* x, const void* w, void* y, const ConvGeom& g, void* ws,
-                    size_t ws_bytes, int* status_dev, int sm_count, cudaStream_t stream, int64_t* launches) {
+                    size_t ws_bytes, int* status_dev, int sm_count, bool independent, cudaStream_t stream,
+                    int64_t* launches) {
   if (!x || !w || !y || g.NB <= 0 || g.H <= 0 || g.W <= 0 || g.C <= 0 || g.KO <= 0 || g.R <= 0 || g.S <= 0 ||
       g.stride <= 0 || g.pad < 0 || g.Ho <= 0 || g.Wo <= 0)
     return HELIX_ERR_INVALID;
@@ -855,8 +961,8 @@ int conv_f16_launch(const helix_cfg_t* cfg_in, const void* x, const void* w, voi
       as_gemm.op = HELIX_OP_GEMM_F16;
       use = &as_gemm;
     }
-    return gemm_f16_launch(use, x, g.C, w, g.C, y, N, M, N, K, 1, 0, 0, 0, ws, ws_bytes, status_dev, sm_count, stream,
-                           launches);
+    return gemm_f16_launch(use, x, g.C, w, g.C, y, N, M, N, K, 1, 0, 0, 0, ws, ws_bytes, status_dev, sm_count,
+                           independent, stream, launches);
   }
   helix_cfg_t cfg;
   if (cfg_in && cfg_in->tile_m != 0) {
@@ -877,7 +983,7 @@ int conv_f16_launch(const helix_cfg_t* cfg_in, const void* x, const void* w, voi
   CUtensorMap tb;
   int rc;
   if ((rc = make_tmap(&tb, w, K, N, 1, K, 0, cfg.tile_n)) != HELIX_OK) return rc;
-  return launch_common(cfg, true, tb, tb, p, y, N, 0, ws, ws_bytes, sm_count, stream, launches);
+  return launch_common(cfg, true, tb, tb, p, y, N, 0, ws, ws_bytes, sm_count, independent, stream, launches);
 }
 
 }  // namespace helix

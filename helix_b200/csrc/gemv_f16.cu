@@ -21,7 +21,11 @@ template <int MRHS, int RPW, int UNROLL>
 __global__ void __launch_bounds__(256)
 gemv_f16_kernel(const __half* __restrict__ W, int64_t ldw, const __half* __restrict__ X, int64_t ldx,
                 __half* __restrict__ Y, int64_t ldy, int64_t ldy_inner, float* __restrict__ partial,
-                int rows, int K, int m, int split_k, int k_per_split) {
+                int rows, int K, int m, int split_k, int k_per_split, int independent) {
+  // Let the next kernel on the stream be scheduled while this one drains; unless the caller
+  // declared the launch independent of its predecessor, wait for that kernel before reading.
+  griddep_launch_dependents();
+  if (!independent) griddep_wait();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int warps_per_block = blockDim.x >> 5;
@@ -127,6 +131,10 @@ int gemv_f16_default_split(int rows, int K, int sm_count) {
   return split;
 }
 
+// Set by gemv_f16_launch for the duration of one call: the caller declared the launch independent
+// of the kernel queued before it (HELIX_LAUNCH_INDEPENDENT).
+static thread_local bool independent = false;
+
 template <int MRHS, int RPW, int UNROLL>
 static int launch_gemv(const __half* W, int64_t ldw, const __half* X, int64_t ldx, __half* Y, int64_t ldy,
                        int64_t ldy_inner, float* partial, int rows, int K, int m, int split_k, int sm_count,
@@ -139,8 +147,24 @@ static int launch_gemv(const __half* W, int64_t ldw, const __half* X, int64_t ld
   int k_per_split = (K + split_k - 1) / split_k;
   k_per_split = (k_per_split + 255) / 256 * 256;
   dim3 grid(blocks, split_k);
-  gemv_f16_kernel<MRHS, RPW, UNROLL><<<grid, warps * 32, 0, stream>>>(W, ldw, X, ldx, Y, ldy, ldy_inner, partial,
-                                                                      rows, K, m, split_k, k_per_split);
+  // split-K shares its scratch with neighbouring launches, so it always orders itself after them
+  const int indep = (independent && split_k == 1) ? 1 : 0;
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = grid;
+  lc.blockDim = dim3(warps * 32);
+  lc.dynamicSmemBytes = 0;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  if (cudaLaunchKernelEx(&lc, gemv_f16_kernel<MRHS, RPW, UNROLL>, W, ldw, X, ldx, Y, ldy, ldy_inner, partial, rows, K,
+                         m, split_k, k_per_split, indep) != cudaSuccess) {
+    (void)cudaGetLastError();
+    gemv_f16_kernel<MRHS, RPW, UNROLL><<<grid, warps * 32, 0, stream>>>(W, ldw, X, ldx, Y, ldy, ldy_inner, partial,
+                                                                        rows, K, m, split_k, k_per_split, indep);
+  }
   ++*launches;
   if (split_k > 1) {
     const int n = rows * m;
@@ -172,7 +196,11 @@ static int launch_gemv_variant(int rpw, int unroll, const __half* W, int64_t ldw
 
 int gemv_f16_launch(const helix_cfg_t* cfg, const void* W, int64_t ldw, const void* X, int64_t ldx, void* Y,
                     int64_t ldy, int64_t ldy_inner, int rows, int K, int m, void* ws, size_t ws_bytes,
-                    int sm_count, cudaStream_t stream, int64_t* launches) {
+                    int sm_count, bool independent_of_previous, cudaStream_t stream, int64_t* launches) {
+  struct Scope {
+    explicit Scope(bool v) { independent = v; }
+    ~Scope() { independent = false; }
+  } scope(independent_of_previous);
   if (!W || !X || !Y || rows <= 0 || K <= 0 || m <= 0 || m > 8) return HELIX_ERR_INVALID;
   if (ldw == 0) ldw = K;
   if (ldx == 0) ldx = K;

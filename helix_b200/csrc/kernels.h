@@ -12,7 +12,7 @@ size_t gemv_f16_workspace_bytes(int rows, int m, int split_k);
 int gemv_f16_default_split(int rows, int K, int sm_count);
 int gemv_f16_launch(const helix_cfg_t* cfg, const void* W, int64_t ldw, const void* X, int64_t ldx, void* Y,
                     int64_t ldy, int64_t ldy_inner, int rows, int K, int m, void* ws, size_t ws_bytes,
-                    int sm_count, cudaStream_t stream, int64_t* launches);
+                    int sm_count, bool independent_of_previous, cudaStream_t stream, int64_t* launches);
 
 // Variant with the split-K partials in an array that is part of the library image.
 size_t gemv_f16_static_capacity_floats();
@@ -39,8 +39,10 @@ void gemm_f16_default_config(int M, int N, int K, int batch, int sm_count, bool 
 size_t gemm_f16_workspace_bytes(const helix_cfg_t* cfg, int M, int N, int K, int batch, int sm_count);
 int gemm_f16_launch(const helix_cfg_t* cfg, const void* A, int64_t lda, const void* B, int64_t ldb, void* C,
                     int64_t ldc, int M, int N, int K, int batch, int64_t sa, int64_t sb, int64_t sc, void* ws,
-                    size_t ws_bytes, int* status_dev, int sm_count, cudaStream_t stream, int64_t* launches);
+                    size_t ws_bytes, int* status_dev, int sm_count, bool independent, cudaStream_t stream,
+                    int64_t* launches);
 int conv_f16_launch(const helix_cfg_t* cfg, const void* x, const void* w, void* y, const ConvGeom& g, void* ws,
-                    size_t ws_bytes, int* status_dev, int sm_count, cudaStream_t stream, int64_t* launches);
+                    size_t ws_bytes, int* status_dev, int sm_count, bool independent, cudaStream_t stream,
+                    int64_t* launches);
 
 }  // namespace helix

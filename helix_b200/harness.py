@@ -13,7 +13,7 @@ import os
 import torch
 
 from . import costmodel, ops
-from ._lib import OP_CONV_F16, OP_GEMM_F16, OP_GEMM_F32, OP_GEMV_F16
+from ._lib import LAUNCH_INDEPENDENT, OP_CONV_F16, OP_GEMM_F16, OP_GEMM_F32, OP_GEMV_F16
 
 ROTATE_BYTES = 300e6      # more than twice the 126 MB L2
 
@@ -54,6 +54,9 @@ def time_gemm_f16(M, N, K, cfg=None, batch=None, iters=20):
     s = 1.0 / math.sqrt(K)
     bufs = [(_randn(sa, s), _randn(sb, s), torch.empty(sc, device="cuda", dtype=torch.float16)) for _ in range(nbuf)]
     ls = [ops.launch_gemm_f16(a, bb, c, cfg) for a, bb, c in bufs]
+    if len(ls) > 1:
+        for l in ls:
+            l.flags = LAUNCH_INDEPENDENT     # rotating buffer sets: neighbours share nothing
     reps = max(1, 4 // len(ls))
     avg, _, _ = ops.time_launches(ls * reps, warmup=3, iters=iters, use_graph=True)
     return avg
@@ -67,6 +70,9 @@ def time_gemv_f16(rows, K, m, cfg=None, transposed=False, iters=30):
     oshape = (rows, m) if transposed else (m, rows)
     ys = [torch.empty(oshape, device="cuda", dtype=torch.float16) for _ in range(nbuf)]
     ls = [ops.launch_gemv_f16(w, x, y, cfg, out_transposed=transposed) for w, y in zip(ws, ys)]
+    if len(ls) > 1:
+        for l in ls:
+            l.flags = LAUNCH_INDEPENDENT
     reps = max(1, 4 // len(ls))
     avg, _, _ = ops.time_launches(ls * reps, warmup=3, iters=iters, use_graph=True)
     return avg
@@ -165,7 +171,8 @@ def profile_fp16(fast=False, progress=None):
             t1 = time_gemv_f16(2048, 4096, 1, c); tick()
             t2 = time_gemv_f16(16384, 8192, 1, c); tick()
             b1, b2 = 2.0 * (2048 * 4096), 2.0 * (16384 * 8192)
-            fixed, per_byte = _two_point(t1, b1, t2, b2)
+            per_byte = max((t2 - t1) / (b2 - b1), 1e-15)
+            fixed = max(t1 - b1 * per_byte, 0.0)
             d[(0, 1, rpw, unroll, 0, split)] = (float(fixed), float(per_byte))
             best_rate = max(best_rate, b2 / t2 / 1e9)
     d[("hbm_gbs",)] = best_rate

@@ -12,6 +12,7 @@ import math
 import torch
 
 from . import ops, workloads
+from ._lib import LAUNCH_INDEPENDENT
 
 STEM_CHANNEL_PAD = 8  # NHWC activations need C % 8 == 0 (16-byte rule); C = 3 is stored as 8
 
@@ -68,7 +69,10 @@ class Sweep:
             out = torch.empty(so, dtype=torch.float16, device=self.device)
             self.tensors.append((a, b, out))
             cfg = cfg_for(u) if cfg_for is not None else None
-            self.launches.append(self._prepare(u, a, b, out, cfg))
+            l = self._prepare(u, a, b, out, cfg)
+            # units of a sweep share no buffers, so a launch need not wait for its predecessor
+            l.flags = LAUNCH_INDEPENDENT
+            self.launches.append(l)
         self.flops = sum(workloads.unit_flops(u) for u in self.units)
         self.bytes = sum(workloads.unit_bytes(u) for u in self.units)
 

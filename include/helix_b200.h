@@ -104,7 +104,14 @@ typedef struct helix_launch {
   int64_t ldc_inner;     /* GEMV: element stride between rows of W in Y (0 = 1) */
   void* ws;              /* workspace or NULL                                   */
   size_t ws_bytes;
+  uint32_t flags;        /* HELIX_LAUNCH_* bits                                 */
 } helix_launch_t;
+
+/* The caller asserts that nothing this launch reads or writes is written by the kernel queued just
+ * before it on the same stream (independent shapes of a sweep).  The kernel then does not wait for
+ * that kernel to finish before it loads operands, so consecutive launches overlap at their edges.
+ * Without the flag only the set-up phase overlaps.  Ignored for launches that use a workspace. */
+#define HELIX_LAUNCH_INDEPENDENT 1u
 
 /* Library version (major*100 + minor). */
 int helix_version(void);
