@@ -920,7 +920,10 @@ int gemm_f16_launch(const helix_cfg_t* cfg_in, const void* A, int64_t lda, const
     // the automatic choice degrades to the workspace-free schedule when no scratch was passed
     if (!ws || ws_bytes < gemm_f16_workspace_bytes(&cfg, M, N, K, batch, sm_count)) cfg.stream_k = 0;
   }
-  if (cfg.tile_m != kBM || cfg.cta_group > 1) return HELIX_ERR_UNSUPPORTED;
+  if (cfg.cta_group == 2)   // CTA pairs sharing a 256 x BN tile: its own kernel
+    return gemm_f16_pair_launch(cfg, A, lda, B, ldb, C, ldc, M, N, K, batch, sa, sb, sc, status_dev, sm_count,
+                                independent, stream, launches);
+  if (cfg.tile_m != kBM || cfg.cta_group > 2) return HELIX_ERR_UNSUPPORTED;
   const bool swap = cfg.swap_ab != 0;
   GemmParams p{};
   p.PM = swap ? N : M;

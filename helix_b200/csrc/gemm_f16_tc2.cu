@@ -1,0 +1,452 @@
+// fp16 GEMM on CTA pairs: tcgen05.mma.cta_group::2 with a 256 x BN tile per pair of SMs.
+//
+// Same contract as the one-CTA kernel in gemm_f16_tc.cu (C[M,N] = A[M,K] * B[N,K]^T, fp32
+// accumulate in TMEM, fp16 out) for the large, compute-bound shapes.  Two CTAs of a cluster share
+// one output tile: CTA r loads its own 128 rows of A and its own half (BN/2 rows) of the B tile,
+// the even CTA issues one MMA per K=16 step for both tensor cores, and each CTA keeps the
+// accumulator of its 128 rows in its own TMEM.  Per CTA a K slab is 16 KiB of A plus BN/2 x 128
+// bytes of B (32 KiB at BN = 256 against 48 KiB for the one-CTA 128 x 256 tile), so the
+// shared-memory ring is 6 deep instead of 4 and each loaded byte feeds 1.5x the math: the TMA
+// latency that the 4-stage ring leaves exposed is covered.
+//
+// Synchronisation (all waits bounded):
+//   full[s]   lives in the even CTA; it expects the bytes of BOTH CTAs' loads.  Each CTA's TMA
+//             loads name that barrier through its cluster address (no multicast: every CTA fetches
+//             only its own boxes).
+//   empty[s]  and tmem_full[a] exist in both CTAs and are signalled together by one
+//             tcgen05.commit addressed to both CTAs of the pair.
+//   tmem_empty[a] lives in the even CTA and counts the 8 epilogue warps of the pair; the odd CTA's
+//             warps arrive on it remotely.
+#include <cuda.h>
+
+#include <algorithm>
+#include <mutex>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace helix {
+
+namespace {
+
+constexpr int kBM = 128;   // rows per CTA; the pair covers 256
+constexpr int kBK = 64;
+constexpr int kATileBytes = kBM * kBK * 2;
+constexpr int kThreads = 32 + 32 + 128;
+constexpr int kStagingBytes = 4 * 32 * 128;
+
+struct Gemm2Params {
+  __half* C;
+  int64_t ldc, stride_c;
+  int PM, PN, K, batch;
+  int tiles_m, tiles_n, num_kb, total_tiles;  // tiles_m counts 256-row pair tiles
+  int raster, stages;
+  int tma_store, independent;
+  int* status;
+};
+
+struct Tile2 {
+  int m_blk, n_blk, b;
+};
+
+__device__ __forceinline__ Tile2 decode_tile2(const Gemm2Params& p, int t) {
+  Tile2 w;
+  const int per_batch = p.tiles_m * p.tiles_n;
+  w.b = t / per_batch;
+  int r = t - w.b * per_batch;
+  const int group = p.raster * p.tiles_n;
+  const int gid = r / group;
+  const int first_m = gid * p.raster;
+  const int gm = min(p.raster, p.tiles_m - first_m);
+  r -= gid * group;
+  w.m_blk = first_m + r % gm;
+  w.n_blk = r / gm;
+  return w;
+}
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load whose completion bytes are credited to a barrier that may live in the other CTA of the pair
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const void* desc, uint32_t bar_cluster_addr, int x,
+                                                 int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, "
+      "%5}], [%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+template <int NCOLS>
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(NCOLS)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+template <int NCOLS>
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(NCOLS) : "memory");
+}
+__device__ __forceinline__ void umma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                 bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// One arrival on the barrier at this shared-memory offset in BOTH CTAs of the pair, once every
+// MMA issued so far has completed.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint32_t mask = 3;
+  asm volatile(
+      "{\n\t.reg .b16 lo, hi;\n\t"
+      "mov.b32 {lo, hi}, %1;\n\t"
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], lo;\n\t}" ::"r"(
+          smem_u32(bar)),
+      "r"(mask)
+      : "memory");
+}
+
+template <int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_c, const Gemm2Params p) {
+  constexpr int kBHalfBytes = (BN / 2) * kBK * 2;
+  constexpr int kStageBytes = kATileBytes + kBHalfBytes;
+  constexpr int kTmemCols = 2 * BN <= 256 ? 256 : 512;
+  constexpr uint32_t kIdesc = umma_idesc_f16(2 * kBM, BN);
+
+  griddep_launch_dependents();
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int stages = p.stages;
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + (size_t)stages * kATileBytes;
+  uint8_t* sC = smem + (size_t)stages * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sC + kStagingBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + 8;
+  uint64_t* tmem_full = bars + 16;
+  uint64_t* tmem_empty = bars + 18;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 20);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 8);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    if (p.tma_store) tma_prefetch_desc(&tmap_c);
+  }
+  if (warp == 1) tmem_alloc_pair<kTmemCols>(tmem_ptr_smem);
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();   // both CTAs' barriers exist before anything is signalled across the pair
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (!p.independent) griddep_wait();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (each CTA)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < p.total_tiles && ok; t += num_pairs) {
+        const Tile2 w = decode_tile2(p, t);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status);
+          if (!ok) break;
+          if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kStageBytes);
+          const uint32_t full_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          tma_load_3d_pair(sA + (size_t)stage * kATileBytes, &tmap_a, full_leader, kb * kBK,
+                           w.m_blk * 2 * kBM + (int)rank * kBM, w.b);
+          tma_load_3d_pair(sB + (size_t)stage * kBHalfBytes, &tmap_b, full_leader, kb * kBK,
+                           w.n_blk * BN + (int)rank * (BN / 2), w.b);
+          if (++stage == stages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (even CTA only)
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int idx = 0;
+      for (int t = pair; t < p.total_tiles && ok; t += num_pairs, ++idx) {
+        const int acc = idx & 1;
+        const uint32_t acc_phase = (idx >> 1) & 1;
+        ok = mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint64_t da = umma_desc_sw128(smem_u32(sA + (size_t)stage * kATileBytes));
+          const uint64_t db = umma_desc_sw128(smem_u32(sB + (size_t)stage * kBHalfBytes));
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) umma_f16_ss_pair(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kb > 0) || (k > 0));
+          umma_commit_pair(&empty_bar[stage]);
+          if (++stage == stages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit_pair(&tmem_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (each CTA: its 128 rows)
+    const int quarter = warp & 3;
+    bool ok = true;
+    const bool vec_ok = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && ((p.stride_c & 7) == 0);
+    int idx = 0;
+    for (int t = pair; t < p.total_tiles && ok; t += num_pairs, ++idx) {
+      const Tile2 w = decode_tile2(p, t);
+      const int acc = idx & 1;
+      const uint32_t acc_phase = (idx >> 1) & 1;
+      ok = mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row0 = w.m_blk * 2 * kBM + (int)rank * kBM + quarter * 32;
+      const int row = row0 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      uint8_t* stage_box = sC + (size_t)quarter * (32 * 128);
+      const uint32_t row_base = smem_u32(stage_box) + lane * 128;
+      uint32_t ra[32], rb[32], na[32], nb[32];
+      auto emit = [&](const uint32_t (&lo)[32], const uint32_t (&hi)[32], int c0) {
+        const int col0 = w.n_blk * BN + c0;
+        if (col0 >= p.PN || row0 >= p.PM) return;   // warp-uniform: nothing but padding
+        if (p.tma_store) {
+          if (lane == 0) tma_store_wait_read();
+          __syncwarp();
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            const uint32_t* src = ch < 4 ? &lo[ch * 8] : &hi[(ch - 4) * 8];
+            __half2 h0 = __floats2half2_rn(__uint_as_float(src[0]), __uint_as_float(src[1]));
+            __half2 h1 = __floats2half2_rn(__uint_as_float(src[2]), __uint_as_float(src[3]));
+            __half2 h2 = __floats2half2_rn(__uint_as_float(src[4]), __uint_as_float(src[5]));
+            __half2 h3 = __floats2half2_rn(__uint_as_float(src[6]), __uint_as_float(src[7]));
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + ((ch ^ (lane & 7)) << 4)),
+                         "r"(*reinterpret_cast<uint32_t*>(&h0)), "r"(*reinterpret_cast<uint32_t*>(&h1)),
+                         "r"(*reinterpret_cast<uint32_t*>(&h2)), "r"(*reinterpret_cast<uint32_t*>(&h3))
+                         : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&tmap_c, stage_box, col0, row0, w.b);
+            tma_store_commit();
+          }
+        } else if (row < p.PM) {
+          __half* dst = p.C + (int64_t)w.b * p.stride_c + (int64_t)row * p.ldc + col0;
+#pragma unroll
+          for (int jj = 0; jj < 64; jj += 8) {
+            const uint32_t* src = jj < 32 ? &lo[jj] : &hi[jj - 32];
+            if (vec_ok && col0 + jj + 8 <= p.PN) {
+              uint4 v;
+              __half2 h0 = __floats2half2_rn(__uint_as_float(src[0]), __uint_as_float(src[1]));
+              __half2 h1 = __floats2half2_rn(__uint_as_float(src[2]), __uint_as_float(src[3]));
+              __half2 h2 = __floats2half2_rn(__uint_as_float(src[4]), __uint_as_float(src[5]));
+              __half2 h3 = __floats2half2_rn(__uint_as_float(src[6]), __uint_as_float(src[7]));
+              v.x = *reinterpret_cast<uint32_t*>(&h0);
+              v.y = *reinterpret_cast<uint32_t*>(&h1);
+              v.z = *reinterpret_cast<uint32_t*>(&h2);
+              v.w = *reinterpret_cast<uint32_t*>(&h3);
+              *reinterpret_cast<uint4*>(dst + jj) = v;
+            } else {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                if (col0 + jj + q < p.PN) dst[jj + q] = __float2half_rn(__uint_as_float(src[q]));
+            }
+          }
+        }
+      };
+      tmem_ld_32x32b_x32(taddr, ra);
+      tmem_ld_32x32b_x32(taddr + 32, rb);
+#pragma unroll
+      for (int c0 = 0; c0 < BN; c0 += 128) {
+        tmem_ld_wait();
+        if (c0 + 64 < BN) {
+          tmem_ld_32x32b_x32(taddr + c0 + 64, na);
+          tmem_ld_32x32b_x32(taddr + c0 + 96, nb);
+        }
+        emit(ra, rb, c0);
+        if (c0 + 64 < BN) {
+          tmem_ld_wait();
+          if (c0 + 128 < BN) {
+            tmem_ld_32x32b_x32(taddr + c0 + 128, ra);
+            tmem_ld_32x32b_x32(taddr + c0 + 160, rb);
+          }
+          emit(na, nb, c0 + 64);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
+    }
+    if (p.tma_store && lane == 0) tma_store_wait_all();
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();   // nothing of the pair still refers to this CTA's barriers or shared memory
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc_pair<kTmemCols>(tmem_base);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+int make_map(CUtensorMap* map, const void* base, int64_t inner, int64_t rows, int64_t batch, int64_t ld, int64_t bs,
+             int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return HELIX_ERR_CUDA;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld & 7) || (batch > 1 && (bs & 7))) return HELIX_ERR_ALIGN;
+  if (batch <= 1) bs = rows * ld;
+  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)std::max<int64_t>(batch, 1)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)bs * 2};
+  cuuint32_t box[3] = {(cuuint32_t)kBK, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? HELIX_OK : HELIX_ERR_CUDA;
+}
+
+template <int BN>
+cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const Gemm2Params& p,
+                        int grid, size_t smem, cudaStream_t stream) {
+  auto kern = gemm_f16_tc2_kernel<BN>;
+  static std::mutex mu;
+  static size_t granted[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && granted[dev] < smem) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+      granted[dev] = smem;
+    }
+  }
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(grid);
+  lc.blockDim = dim3(kThreads);
+  lc.dynamicSmemBytes = smem;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&lc, kern, ta, tb, tc, p);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    kern<<<grid, kThreads, smem, stream>>>(ta, tb, tc, p);
+    e = cudaGetLastError();
+  }
+  return e;
+}
+
+}  // namespace
+
+int gemm_f16_pair_max_stages(int bn) {
+  const int budget = 227 * 1024 - 1024 - 256 - kStagingBytes;
+  return std::min(8, budget / (kATileBytes + (bn / 2) * kBK * 2));
+}
+
+// cta_group = 2 configurations: whole 256 x BN tiles round-robin over CTA pairs.
+int gemm_f16_pair_launch(const helix_cfg_t& cfg, const void* A, int64_t lda, const void* B, int64_t ldb, void* C,
+                         int64_t ldc, int M, int N, int K, int batch, int64_t sa, int64_t sb, int64_t sc,
+                         int* status_dev, int sm_count, bool independent, cudaStream_t stream, int64_t* launches) {
+  const int bn = cfg.tile_n;
+  if (bn != 256 && bn != 128) return HELIX_ERR_UNSUPPORTED;
+  if (cfg.swap_ab || cfg.stream_k || cfg.split_k > 1) return HELIX_ERR_UNSUPPORTED;
+  Gemm2Params p{};
+  p.PM = M; p.PN = N; p.K = K; p.batch = batch;
+  p.C = static_cast<__half*>(C);
+  p.ldc = ldc; p.stride_c = sc;
+  p.status = status_dev;
+  p.tiles_m = (M + 2 * kBM - 1) / (2 * kBM);
+  p.tiles_n = (N + bn - 1) / bn;
+  p.num_kb = (K + kBK - 1) / kBK;
+  const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n * batch;
+  if (tiles <= 0 || tiles > 0x3fffffff) return HELIX_ERR_INVALID;
+  p.total_tiles = (int)tiles;
+  p.raster = cfg.raster > 0 ? cfg.raster : 8;
+  const int smax = gemm_f16_pair_max_stages(bn);
+  p.stages = cfg.stages > 0 ? std::min(cfg.stages, smax) : smax;
+  if (p.stages < 2) return HELIX_ERR_UNSUPPORTED;
+  p.independent = independent ? 1 : 0;
+  CUtensorMap ta, tb, tc;
+  int rc;
+  if ((rc = make_map(&ta, A, K, M, batch, lda, sa, kBM)) != HELIX_OK) return rc;
+  if ((rc = make_map(&tb, B, K, N, batch, ldb, sb, bn / 2)) != HELIX_OK) return rc;
+  tc = tb;
+  p.tma_store = 0;
+  if ((ldc & 7) == 0 && (sc & 7) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+      make_map(&tc, C, N, M, batch, ldc, sc, 32) == HELIX_OK)
+    p.tma_store = 1;
+  const int pairs = (int)std::min<int64_t>(tiles, sm_count / 2);
+  const size_t smem = 1024 + (size_t)p.stages * (kATileBytes + (bn / 2) * kBK * 2) + kStagingBytes + 256;
+  const cudaError_t e = bn == 256 ? launch_pair<256>(ta, tb, tc, p, 2 * pairs, smem, stream)
+                                  : launch_pair<128>(ta, tb, tc, p, 2 * pairs, smem, stream);
+  if (e != cudaSuccess) return HELIX_ERR_CUDA;
+  ++*launches;
+  return HELIX_OK;
+}
+
+}  // namespace helix

@@ -211,3 +211,38 @@ def test_gemm_stream_k_needs_workspace():
     with pytest.raises(Exception) as e:
         ops.run(l)
     assert "-3" in str(e.value)
+
+
+def _pair(bn, stages=0):
+    return ops.make_cfg(OP_GEMM_F16, tile_m=128, tile_n=bn, tile_k=64, stages=stages, cta_group=2)
+
+
+@pytest.mark.parametrize("bn,shape", [
+    (256, (256, 256, 64)),        # one pair tile, one slab
+    (128, (256, 128, 256)),
+    (256, (512, 768, 1024)),      # several tiles per pair, ring wraps
+    (256, (300, 520, 264)),       # ragged M, N, K
+    (128, (2048, 2304, 512)),     # more tiles than CTA pairs
+    (256, (100, 40, 72)),         # smaller than one tile
+])
+def test_gemm_cta_pairs(oracle, bn, shape):
+    """tcgen05.mma.cta_group::2: two CTAs share a 256 x BN tile."""
+    M, N, K = shape
+    a, b = datagen.c3_gemm(M, N, K, seed=14)
+    got = _run(a, b, _pair(bn))
+    _, ref32 = oracle.hgemm_fast(a, b)
+    util.assert_f16_close(got, ref32, f"CTA pairs {shape} bn={bn}")
+
+
+def test_gemm_cta_pairs_known_answer_and_batch(oracle):
+    K = 128
+    a = np.zeros((256, K), np.float16)
+    a[np.arange(256), (np.arange(256) * 5) % K] = 1
+    b = np.random.default_rng(3).standard_normal((256, K)).astype(np.float16)
+    got = _run(a, b, _pair(256))
+    assert np.array_equal(got, b[:, (np.arange(256) * 5) % K].T)   # rows 128..255 come from the odd CTA
+    ab, bb = datagen.c3_gemm(260, 136, 192, seed=15, batch=3)
+    gb = _run(ab, bb, _pair(128, stages=2))
+    for i in range(3):
+        _, ref32 = oracle.hgemm_naive(ab[i], bb[i])
+        util.assert_f16_close(gb[i], ref32, f"CTA pairs batch {i}")
