@@ -43,6 +43,15 @@ def max_stages(tile_n):
     return min(8, budget // (TILE_M * TILE_K * 2 + tile_n * TILE_K * 2))
 
 
+def pair_max_stages(tile_n):
+    budget = 227 * 1024 - 1024 - 256 - 16384
+    return min(8, budget // (TILE_M * TILE_K * 2 + (tile_n // 2) * TILE_K * 2))
+
+
+# two CTAs share a 256 x 256 tile (tcgen05.mma.cta_group::2); each CTA holds 128 rows
+PAIR_KEY = (pair_max_stages(256), TILE_M, 256, 2, 0, 0)
+
+
 def gemm_keys():
     """Every GEMM configuration of the search space, as dictionary keys."""
     keys = []
@@ -50,6 +59,7 @@ def gemm_keys():
         for swap in (0, 1):
             for mode in (0, 1):
                 keys.append((max_stages(bn), TILE_M, bn, 1, swap, mode))
+    keys.append(PAIR_KEY)
     return keys
 
 
@@ -79,6 +89,10 @@ def gemm_time(prof_dict, key, M, N, K, batch=1, conv=False):
         t_slab = max(t_slab, prof_dict.get(("conv_slab", bn), t_slab))
     sms = _param(prof_dict, "sm_count", DEFAULT_SMS)
     pm, pn = (N, M) if swap else (M, N)
+    if group == 2:
+        if conv or swap or mode or pm <= tm:
+            return float("inf")
+        tm, sms = 2 * tm, sms // 2      # a pair of SMs is one scheduling slot for a 256-row tile
     tiles_m, tiles_n = -(-pm // tm), -(-pn // bn)
     tiles = tiles_m * tiles_n * batch
     nkb = -(-K // TILE_K)
@@ -93,6 +107,8 @@ def gemm_time(prof_dict, key, M, N, K, batch=1, conv=False):
         slabs = rounds * nkb + max(-(-tail * nkb // sms), min(4, nkb))
         active = min(tiles * nkb, sms)
         extra = prof_dict.get(("streamk_overhead", bn), 8e-6)
+    if group == 2:
+        active *= 2
     t = t_fixed + slabs * t_slab + extra
     # HBM floor: operand bytes at the streaming rate of the SMs that take part
     per_sm = _param(prof_dict, "dram_gbs_per_sm", 40.0) * 1e9

@@ -170,7 +170,7 @@ int helix_get_config(int op, int idx, helix_cfg_t* out) {
     case HELIX_OP_CONV_F16:
       helix::gemm_f16_get_config(idx, out);
       out->op = HELIX_OP_CONV_F16;
-      if (out->swap_ab) return HELIX_ERR_UNSUPPORTED;
+      if (out->swap_ab || out->cta_group != 1) return HELIX_ERR_UNSUPPORTED;
       break;
     case HELIX_OP_GEMV_F16:
       out->op = HELIX_OP_GEMV_F16;

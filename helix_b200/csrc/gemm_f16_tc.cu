@@ -660,11 +660,20 @@ static const int kTileNs[] = {256, 128, 64, 32, 16};
 constexpr int kNumTileNs = sizeof(kTileNs) / sizeof(kTileNs[0]);
 
 // tile widths x {plain, swap_ab} x {tile list, stream-K}
-int gemm_f16_num_configs() { return kNumTileNs * 4; }
+// ... plus the two CTA-pair configurations (256 x 256 and 256 x 128 per pair)
+int gemm_f16_num_configs() { return kNumTileNs * 4 + 2; }
 void gemm_f16_get_config(int idx, helix_cfg_t* out) {
   *out = helix_cfg_t{};
   out->op = HELIX_OP_GEMM_F16;
   out->tile_m = kBM;
+  if (idx >= kNumTileNs * 4) {
+    out->tile_n = idx == kNumTileNs * 4 ? 256 : 128;
+    out->tile_k = kBK;
+    out->cta_group = 2;
+    out->split_k = 1;
+    out->raster = 8;
+    return;
+  }
   out->tile_n = kTileNs[idx % kNumTileNs];
   out->tile_k = kBK;
   out->stages = 0;
@@ -740,6 +749,19 @@ void gemm_f16_default_config(int M, int N, int K, int batch, int sm_count, bool 
     }
   }
   out->stages = max_stages(out->tile_n, conv);
+  // CTA pairs on a 256 x 256 tile: half the B bytes per CTA and a 6-deep ring; measured about
+  // 0.41 us per 64-deep slab of a pair tile, i.e. twice the work of a 128 x 256 slab in less time.
+  if (!conv && !swap && M > kBM && N >= 128) {
+    const int64_t pair_tiles = (int64_t)((M + 2 * kBM - 1) / (2 * kBM)) * ((N + 255) / 256) * batch;
+    const int64_t pairs = std::max(1, sm_count / 2);
+    const double t2 = (double)((pair_tiles + pairs - 1) / pairs) * num_kb * 0.41 + 4.0;
+    if (t2 < best) {
+      out->cta_group = 2;
+      out->tile_n = 256;
+      out->stream_k = 0;
+      out->stages = gemm_f16_pair_max_stages(256);
+    }
+  }
 }
 
 // Stream-K decomposition of `tiles` tiles over `grid` CTAs.
