@@ -166,7 +166,7 @@ def extras(peaks):
     """Per-configuration figures beside the headline: GEMV GB/s, dense GEMM sweep, convs, fp32 GEMM."""
     import torch
     from helix_b200 import datagen, ops
-    from helix_b200._lib import LAUNCH_INDEPENDENT
+    from helix_b200._lib import LAUNCH_INDEPENDENT, LAUNCH_STATIC_A
     out = {}
     dev = "cuda"
     # fp16 GEMV 4096 x 4096, m = 1: rotating W buffers (12 x 32 MiB > 2 x L2), CUDA-graph timing
@@ -175,11 +175,17 @@ def extras(peaks):
     x = torch.randn(1, K, device=dev, dtype=torch.float16)
     ys = [torch.empty(1, rows, device=dev, dtype=torch.float16) for _ in ws]
     ls = [ops.launch_gemv_f16(w, x, y) for w, y in zip(ws, ys)]
-    for l in ls:
-        l.flags = LAUNCH_INDEPENDENT     # twelve distinct W / y pairs: neighbours share only the read-only x
-    avg, _, _ = ops.time_launches(ls, warmup=5, iters=50, use_graph=True)
-    gb = (rows * K * 2 + K * 2 + rows * 2) / avg / 1e9
-    out["gemv_4096x4096_m1"] = {"us": avg * 1e6, "GB/s": gb, "frac_hbm_peak": gb / peaks["hbm_gbs"]}
+    gemv_bytes = rows * K * 2 + K * 2 + rows * 2
+    res = {}
+    # twelve distinct W / y pairs sharing only the read-only x: consecutive launches are independent.
+    # Also reported: weights-static ordering (X may come from the previous kernel) and full ordering.
+    for name, flag in (("independent", LAUNCH_INDEPENDENT), ("static_weights", LAUNCH_STATIC_A), ("ordered", 0)):
+        for l in ls:
+            l.flags = flag
+        avg, _, _ = ops.time_launches(ls, warmup=5, iters=50, use_graph=True)
+        gb = gemv_bytes / avg / 1e9
+        res[name] = {"us": avg * 1e6, "GB/s": gb, "frac_hbm_peak": gb / peaks["hbm_gbs"]}
+    out["gemv_4096x4096_m1"] = dict(res["independent"], launch_ordering=res)
     del ws, ys, ls
     # fp16 dense GEMM sweep
     gem = {}

@@ -62,6 +62,7 @@ class Launch(ctypes.Structure):
 
 
 LAUNCH_INDEPENDENT = 1
+LAUNCH_STATIC_A = 2
 
 
 # name -> (restype, argtypes); every symbol include/helix_b200.h declares

@@ -90,7 +90,8 @@ int dispatch(const helix_launch_t* l, void* status_dev, cudaStream_t stream) {
     case HELIX_OP_GEMV_F16:
       if ((rc = current_device(&info, false)) != HELIX_OK) return rc;
       rc = helix::gemv_f16_launch(cfg, l->a, l->lda, l->b, l->ldb, l->c, l->ldc, l->ldc_inner, l->N, l->K, l->M,
-                                  l->ws, l->ws_bytes, info.sm_count, (l->flags & HELIX_LAUNCH_INDEPENDENT) != 0,
+                                  l->ws, l->ws_bytes, info.sm_count,
+                                  (l->flags & HELIX_LAUNCH_INDEPENDENT) ? 2 : (l->flags & HELIX_LAUNCH_STATIC_A) ? 1 : 0,
                                   stream, &n);
       break;
     case HELIX_OP_CONV_F16: {

@@ -751,7 +751,7 @@ void gemm_f16_default_config(int M, int N, int K, int batch, int sm_count, bool 
   out->stages = max_stages(out->tile_n, conv);
   // CTA pairs on a 256 x 256 tile: half the B bytes per CTA and a 6-deep ring; measured about
   // 0.41 us per 64-deep slab of a pair tile, i.e. twice the work of a 128 x 256 slab in less time.
-  if (!conv && !swap && M > kBM && N >= 128) {
+  if (!conv && !swap && M > kBM && N >= 128 && num_kb >= 8) {   // short K is epilogue bound: no gain
     const int64_t pair_tiles = (int64_t)((M + 2 * kBM - 1) / (2 * kBM)) * ((N + 255) / 256) * batch;
     const int64_t pairs = std::max(1, sm_count / 2);
     const double t2 = (double)((pair_tiles + pairs - 1) / pairs) * num_kb * 0.41 + 4.0;

@@ -21,11 +21,17 @@ template <int MRHS, int RPW, int UNROLL>
 __global__ void __launch_bounds__(256)
 gemv_f16_kernel(const __half* __restrict__ W, int64_t ldw, const __half* __restrict__ X, int64_t ldx,
                 __half* __restrict__ Y, int64_t ldy, int64_t ldy_inner, float* __restrict__ partial,
-                int rows, int K, int m, int split_k, int k_per_split, int independent) {
-  // Let the next kernel on the stream be scheduled while this one drains; unless the caller
-  // declared the launch independent of its predecessor, wait for that kernel before reading.
+                int rows, int K, int m, int split_k, int k_per_split, int order_mode) {
+  // Let the next kernel on the stream be scheduled while this one drains.  How this launch orders
+  // itself after the kernel queued before it (order_mode):
+  //   0  wait for it before touching global memory (safe default);
+  //   1  W is not written by it (weights): the first batch of W loads is issued, THEN the kernel
+  //      waits, then reads X and later writes Y -- launch latency and ramp-up hide behind the
+  //      predecessor's tail while X may still be its output;
+  //   2  nothing is shared with it: never wait.
   griddep_launch_dependents();
-  if (!independent) griddep_wait();
+  bool waited = order_mode != 1;
+  if (order_mode == 0) griddep_wait();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int warps_per_block = blockDim.x >> 5;
@@ -56,6 +62,10 @@ gemv_f16_kernel(const __half* __restrict__ W, int64_t ldw, const __half* __restr
           if (k < k_end) wv[u][r] = ldg_stream_16(wrow[r] + k);
           else wv[u][r] = make_uint4(0u, 0u, 0u, 0u);
         }
+      }
+      if (!waited) {   // warp-uniform
+        griddep_wait();
+        waited = true;
       }
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
@@ -91,6 +101,10 @@ gemv_f16_kernel(const __half* __restrict__ W, int64_t ldw, const __half* __restr
         for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
         acc[r][i] = v;
       }
+    if (!waited) {   // empty K range: still order the stores after the predecessor
+      griddep_wait();
+      waited = true;
+    }
     if (lane == 0) {
 #pragma unroll
       for (int r = 0; r < RPW; ++r) {
@@ -124,16 +138,17 @@ size_t gemv_f16_workspace_bytes(int rows, int m, int split_k) {
 }
 
 int gemv_f16_default_split(int rows, int K, int sm_count) {
-  // Enough row groups to give every SM a few warps of work; otherwise cut K.
+  // Cut K only when there are too few rows to give every SM a few warps: the partials cost a
+  // second launch and forbid overlapping with the neighbouring launches.
   const int groups = (rows + 1) / 2;
   int split = 1;
-  while (split < 16 && (int64_t)groups * split < (int64_t)sm_count * 16 && K / (split * 2) >= 2048) split *= 2;
+  while (split < 16 && (int64_t)groups * split < (int64_t)sm_count * 4 && K / (split * 2) >= 2048) split *= 2;
   return split;
 }
 
-// Set by gemv_f16_launch for the duration of one call: the caller declared the launch independent
-// of the kernel queued before it (HELIX_LAUNCH_INDEPENDENT).
-static thread_local bool independent = false;
+// Set by gemv_f16_launch for the duration of one call: how the launch orders itself after the
+// kernel queued before it (see order_mode in the kernel).
+static thread_local int independent = 0;
 
 template <int MRHS, int RPW, int UNROLL>
 static int launch_gemv(const __half* W, int64_t ldw, const __half* X, int64_t ldx, __half* Y, int64_t ldy,
@@ -148,7 +163,7 @@ static int launch_gemv(const __half* W, int64_t ldw, const __half* X, int64_t ld
   k_per_split = (k_per_split + 255) / 256 * 256;
   dim3 grid(blocks, split_k);
   // split-K shares its scratch with neighbouring launches, so it always orders itself after them
-  const int indep = (independent && split_k == 1) ? 1 : 0;
+  const int indep = split_k == 1 ? independent : 0;
   cudaLaunchConfig_t lc = {};
   lc.gridDim = grid;
   lc.blockDim = dim3(warps * 32);
@@ -196,11 +211,11 @@ static int launch_gemv_variant(int rpw, int unroll, const __half* W, int64_t ldw
 
 int gemv_f16_launch(const helix_cfg_t* cfg, const void* W, int64_t ldw, const void* X, int64_t ldx, void* Y,
                     int64_t ldy, int64_t ldy_inner, int rows, int K, int m, void* ws, size_t ws_bytes,
-                    int sm_count, bool independent_of_previous, cudaStream_t stream, int64_t* launches) {
+                    int sm_count, int order_mode, cudaStream_t stream, int64_t* launches) {
   struct Scope {
-    explicit Scope(bool v) { independent = v; }
-    ~Scope() { independent = false; }
-  } scope(independent_of_previous);
+    explicit Scope(int v) { independent = v; }
+    ~Scope() { independent = 0; }
+  } scope(order_mode);
   if (!W || !X || !Y || rows <= 0 || K <= 0 || m <= 0 || m > 8) return HELIX_ERR_INVALID;
   if (ldw == 0) ldw = K;
   if (ldx == 0) ldx = K;

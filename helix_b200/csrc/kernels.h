@@ -12,7 +12,7 @@ size_t gemv_f16_workspace_bytes(int rows, int m, int split_k);
 int gemv_f16_default_split(int rows, int K, int sm_count);
 int gemv_f16_launch(const helix_cfg_t* cfg, const void* W, int64_t ldw, const void* X, int64_t ldx, void* Y,
                     int64_t ldy, int64_t ldy_inner, int rows, int K, int m, void* ws, size_t ws_bytes,
-                    int sm_count, bool independent_of_previous, cudaStream_t stream, int64_t* launches);
+                    int sm_count, int order_mode, cudaStream_t stream, int64_t* launches);
 
 // Variant with the split-K partials in an array that is part of the library image.
 size_t gemv_f16_static_capacity_floats();

@@ -112,6 +112,10 @@ typedef struct helix_launch {
  * that kernel to finish before it loads operands, so consecutive launches overlap at their edges.
  * Without the flag only the set-up phase overlaps.  Ignored for launches that use a workspace. */
 #define HELIX_LAUNCH_INDEPENDENT 1u
+/* GEMV: the caller asserts that operand `a` (the matrix W: weights) is not written by the kernel
+ * queued just before this launch, while X may be.  The kernel issues its first batch of W loads,
+ * then waits for that kernel, then reads X: launch latency and ramp-up hide behind its tail. */
+#define HELIX_LAUNCH_STATIC_A 2u
 
 /* Library version (major*100 + minor). */
 int helix_version(void);

@@ -246,3 +246,22 @@ def test_gemm_cta_pairs_known_answer_and_batch(oracle):
     for i in range(3):
         _, ref32 = oracle.hgemm_naive(ab[i], bb[i])
         util.assert_f16_close(gb[i], ref32, f"CTA pairs batch {i}")
+
+
+def test_gemm_independent_launch_chain_matches_ordered(oracle):
+    """HELIX_LAUNCH_INDEPENDENT lets consecutive launches overlap at their edges; results are unchanged."""
+    a, b = datagen.c3_gemm(1024, 768, 512, seed=16)
+    ad, bd = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    ref = ops.gemm_f16(ad, bd)
+    outs = [torch.full((1024, 768), float("nan"), dtype=torch.float16, device="cuda") for _ in range(8)]
+    for i, o in enumerate(outs):
+        cfg = _pair(256) if i % 2 else _cfg(128)
+        l = ops.launch_gemm_f16(ad, bd, o, cfg)
+        l.flags = 1
+        ops.run(l)
+    torch.cuda.synchronize()
+    ops.check_status()
+    _, ref32 = oracle.hgemm_fast(a, b)
+    for o in outs:
+        util.assert_f16_close(o.cpu().numpy(), ref32, "independent chain")
+    assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[3])

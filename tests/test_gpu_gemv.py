@@ -70,3 +70,22 @@ def test_gemv_rejects_bad_arguments():
     w24 = torch.zeros((8, 24), dtype=torch.float16, device="cuda")
     with pytest.raises(Exception):
         ops.run(ops.launch_gemv_f16(w24, x9, torch.zeros((9, 8), dtype=torch.float16, device="cuda")))
+
+
+@pytest.mark.parametrize("flag", [1, 2])
+def test_gemv_launch_ordering_flags_do_not_change_results(oracle, flag):
+    """INDEPENDENT (1) and STATIC_A (2) only move the wait for the preceding kernel; a chain of launches on
+    distinct outputs must give bit-identical results to fully ordered launches."""
+    w, x = datagen.c2_gemv(2048, 4096, 1, seed=5)
+    wd, xd = torch.from_numpy(w).cuda(), torch.from_numpy(x).cuda()
+    outs = [torch.full((1, 2048), float("nan"), dtype=torch.float16, device="cuda") for _ in range(6)]
+    ref = ops.gemv_f16(wd, xd)
+    for o in outs:
+        l = ops.launch_gemv_f16(wd, xd, o)
+        l.flags = flag
+        ops.run(l)
+    torch.cuda.synchronize()
+    for o in outs:
+        assert torch.equal(o, ref)
+    _, ref32 = oracle.hgemm_naive(x, w)
+    util.assert_f16_close(ref.cpu().numpy(), ref32, "gemv flags")
