@@ -231,6 +231,39 @@ def extras(peaks):
     return out
 
 
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, averaged over the launches of
+# one sweep step) for each kernel of the sweep, from one single-pass ncu capture of
+#   python bench.py --steps 1 --warmup 3 --no-extras
+# Filled in below only for the kernels that capture listed; the others report null.
+SWEEP_DRAM_BYTES_PER_LAUNCH = {
+    "gemm_f16_tc2_kernel<256>": 15781729, "gemm_f16_tc2_kernel<192>": 34548875,
+    "gemm_f16_tc_kernel<256,0>": 33245932, "gemm_f16_tc_kernel<64,0>": 88540024,
+    "gemm_f16_tc_kernel<128,0>": 21824768,
+}
+
+
+def kernel_breakdown(sw, ops):
+    """Time the sweep's launches grouped by the kernel they resolve to (CUDA-graph replay, events on the
+    launching stream): launches, seconds and algorithmic flop / bytes per group."""
+    from helix_b200 import workloads
+    groups = {}
+    for u, l in zip(sw.units, sw.launches):
+        g = groups.setdefault(ops.kernel_name(l), {"launches": [], "flop": 0.0, "bytes": 0.0})
+        g["launches"].append(l)
+        g["flop"] += workloads.unit_flops(u)
+        g["bytes"] += workloads.unit_bytes(u)
+    out = {}
+    for name, g in groups.items():
+        avg, _, _ = ops.time_launches(g["launches"], warmup=3, iters=10, use_graph=True)
+        n = len(g["launches"])
+        out[name] = {"launches": n, "us": avg * n * 1e6, "flop": g["flop"], "bytes": g["bytes"]}
+    total = sum(v["us"] for v in out.values())
+    for v in out.values():
+        v["share"] = v["us"] / total
+        v["TFLOP/s"] = v["flop"] / (v["us"] * 1e-6) / 1e12
+    return out
+
+
 def bench_helix(args, rank, world, local_rank):
     import torch
     if not torch.cuda.is_available():
@@ -314,6 +347,12 @@ def bench_helix(args, rank, world, local_rank):
         return
     peak = peaks["tflops_sustained"]
     per_gpu = value / world
+    # dominant kernel: the group with the largest share of the step's device time
+    groups = kernel_breakdown(sw, ops)
+    ops.check_status()
+    top = max(groups, key=lambda k: groups[k]["share"])
+    tg = groups[top]
+    traffic = SWEEP_DRAM_BYTES_PER_LAUNCH.get(top)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -321,10 +360,19 @@ def bench_helix(args, rank, world, local_rank):
         "config": {"workload": WORKLOAD, "units_per_step_per_gpu": len(units), "flop_per_step_per_gpu": sw.flops,
                    "cache": "operands of one step total %.1f GB per GPU (> L2), one buffer set per unit" % (sw.bytes / 1e9),
                    "cuda_graph": graph is not None, "parallelism": f"independent replicas of the sweep x{world}"},
-        "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s", "frac": per_gpu / peak,
-                     "traffic": None, "kernel": "gemm_f16_tc_kernel (all tile widths, GEMM and convolution)",
-                     "peak_source": peaks["source"] + " (sustained bf16 cuBLAS)",
-                     "hbm_floor_frac": (sw.bytes / (ms_per_step * 1e-3) / 1e9) / peaks["hbm_gbs"]},
+        "roofline": {"bound": "tensor", "achieved": tg["TFLOP/s"], "peak": peak, "unit": "TFLOP/s",
+                     "frac": tg["TFLOP/s"] / peak, "traffic": traffic,
+                     "kernel": top, "launches_per_step": tg["launches"], "share_of_step": tg["share"],
+                     "us_per_launch": tg["us"] / tg["launches"],
+                     "algorithmic_flop_per_launch": tg["flop"] / tg["launches"],
+                     "algorithmic_bytes_per_launch": tg["bytes"] / tg["launches"],
+                     "peak_source": peaks["source"] + " (sustained bf16 cuBLAS; burst %.0f)" % peaks["tflops"],
+                     "whole_sweep": {"achieved": per_gpu, "frac": per_gpu / peak,
+                                     "hbm_floor_frac": (sw.bytes / (ms_per_step * 1e-3) / 1e9) / peaks["hbm_gbs"]},
+                     "kernels": {k: {"launches": v["launches"], "us": round(v["us"], 2), "share": round(v["share"], 4),
+                                     "TFLOP/s": round(v["TFLOP/s"], 1),
+                                     "dram_bytes_per_launch": SWEEP_DRAM_BYTES_PER_LAUNCH.get(k)}
+                                 for k, v in sorted(groups.items(), key=lambda kv: -kv[1]["share"])}},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": hs.h2d_bytes * world,
                 "d2h_bytes_per_step": hs.d2h_bytes * world, "ms_per_step": e2e_s * 1e3},
         "gpu_launches": launches_per_step * args.steps,

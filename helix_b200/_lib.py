@@ -38,12 +38,12 @@ class Cfg(ctypes.Structure):
                 ("tile_k", ctypes.c_int), ("stages", ctypes.c_int), ("cta_group", ctypes.c_int),
                 ("split_k", ctypes.c_int), ("swap_ab", ctypes.c_int), ("raster", ctypes.c_int),
                 ("thread_m", ctypes.c_int), ("thread_n", ctypes.c_int), ("load_group", ctypes.c_int),
-                ("stream_k", ctypes.c_int), ("reserved", ctypes.c_int * 3)]
+                ("stream_k", ctypes.c_int), ("conv_gather", ctypes.c_int), ("reserved", ctypes.c_int * 2)]
 
     def key(self):
         """Hashable identity used as the prof_dict key."""
         return (self.op, self.tile_m, self.tile_n, self.tile_k, self.stages, self.cta_group,
-                self.split_k, self.swap_ab, self.load_group, self.stream_k)
+                self.split_k, self.swap_ab, self.load_group, self.stream_k, self.conv_gather)
 
     def copy(self):
         c = Cfg()
@@ -88,6 +88,8 @@ SIGNATURES = {
     "helix_conv2d_f16_nhwc_host": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I]),
     "helix_gemv_f16_static": (_I, [_P, _L, _P, _L, _P, _L, _L, _I, _I, _I, _I, _P]),
     "helix_launch_count": (_L, []),
+    "helix_trace_buffer": (_I, [_P, _Z]),
+    "helix_trace_words_per_cta": (_I, []),
 }
 
 _lib = None

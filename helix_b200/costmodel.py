@@ -35,7 +35,7 @@ SGEMM_TILES = ((128, 128, 16, 8, 8), (128, 64, 16, 8, 4), (64, 128, 16, 4, 8), (
 
 def is_valid_config(tile_n, swap_ab, mode, stages):
     """Analogue of is_valid_config (build_Ampere_FP16.py:30-39): what the library can launch."""
-    return tile_n in GEMM_TILE_NS and swap_ab in (0, 1) and mode in (0, 1) and 0 <= stages <= 8
+    return (tile_n in GEMM_TILE_NS or tile_n in PAIR_TILE_NS) and swap_ab in (0, 1) and mode in (0, 1) and 0 <= stages <= 8
 
 
 def max_stages(tile_n):
@@ -48,8 +48,11 @@ def pair_max_stages(tile_n):
     return min(8, budget // (TILE_M * TILE_K * 2 + (tile_n // 2) * TILE_K * 2))
 
 
-# two CTAs share a 256 x 256 tile (tcgen05.mma.cta_group::2); each CTA holds 128 rows
-PAIR_KEY = (pair_max_stages(256), TILE_M, 256, 2, 0, 0)
+# two CTAs share a 256 x 256 tile (tcgen05.mma.cta_group::2); each CTA holds 128 rows.
+# The 256 x 192 pair tile exists for tile counts that quantise badly at 256 x 256.
+PAIR_TILE_NS = (256, 192)
+PAIR_KEYS = tuple((pair_max_stages(bn), TILE_M, bn, 2, 0, 0) for bn in PAIR_TILE_NS)
+PAIR_KEY = PAIR_KEYS[0]
 
 
 def gemm_keys():
@@ -59,7 +62,7 @@ def gemm_keys():
         for swap in (0, 1):
             for mode in (0, 1):
                 keys.append((max_stages(bn), TILE_M, bn, 1, swap, mode))
-    keys.append(PAIR_KEY)
+    keys.extend(PAIR_KEYS)
     return keys
 
 

@@ -201,8 +201,7 @@ int helix_default_config(const helix_launch_t* l, helix_cfg_t* out) {
       const helix::ConvGeom g = conv_geom(l->conv);
       const int64_t M = (int64_t)g.NB * g.Ho * g.Wo, K = (int64_t)g.R * g.S * g.C;
       if (M <= 0 || M > 0x7fffffff || K <= 0 || K > 0x7fffffff) return HELIX_ERR_INVALID;
-      const bool as_gemm = g.R == 1 && g.S == 1 && g.stride == 1 && g.pad == 0;
-      helix::gemm_f16_default_config((int)M, g.KO, (int)K, 1, sms, !as_gemm, out);
+      helix::conv_f16_default_config(g, sms, out);
       return HELIX_OK;
     }
     case HELIX_OP_GEMV_F16:
@@ -234,8 +233,7 @@ size_t helix_workspace_bytes(const helix_launch_t* l) {
       const int64_t M = (int64_t)g.NB * g.Ho * g.Wo, K = (int64_t)g.R * g.S * g.C;
       if (M <= 0 || M > 0x7fffffff || K > 0x7fffffff) return 0;
       helix_cfg_t cfg = l->cfg;
-      const bool as_gemm = g.R == 1 && g.S == 1 && g.stride == 1 && g.pad == 0;
-      if (!have_cfg) helix::gemm_f16_default_config((int)M, g.KO, (int)K, 1, sms, !as_gemm, &cfg);
+      if (!have_cfg) helix::conv_f16_default_config(g, sms, &cfg);
       return helix::gemm_f16_workspace_bytes(&cfg, (int)M, g.KO, (int)K, 1, sms);
     }
     case HELIX_OP_GEMV_F16: {
@@ -496,5 +494,12 @@ int helix_gemv_f16_static(const void* W, int64_t ldw, const void* X, int64_t ldx
 }
 
 int64_t helix_launch_count(void) { return g_launches.load(); }
+
+int helix_trace_buffer(void* device_buf, size_t bytes) {
+  helix::gemm_f16_set_trace(device_buf, bytes);
+  return HELIX_OK;
+}
+
+int helix_trace_words_per_cta(void) { return helix::gemm_f16_trace_words_per_cta(); }
 
 }  // extern "C"

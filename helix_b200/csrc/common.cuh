@@ -101,6 +101,21 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* desc, ui
       : "memory");
 }
 
+// 4-D im2col load from an NHWC tensor (map dimensions C, W, H, N): `pixels-per-column` pixels
+// starting at base pixel (w, h, n) and walking the map's bounding box in W, then H, then N with
+// the map's traversal strides; each pixel contributes `channels-per-pixel` channels from c, read
+// at (w + off_w, h + off_h).  Pixels outside the tensor arrive as zeros and still count towards
+// the transaction bytes.  c * sizeof(element) must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_im2col_4d(void* smem_dst, const void* desc, uint64_t* bar, int c, int w,
+                                                   int h, int n, uint16_t off_w, uint16_t off_h) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, "
+      "%6}], [%2], {%7, %8};" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(desc)), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w),
+      "h"(off_h)
+      : "memory");
+}
+
 // ---------------------------------------------------------------- cp.async (16-byte, zero-fill)
 __device__ __forceinline__ void cp_async_16_zfill(uint32_t smem_dst, const void* gsrc, bool valid) {
   const int src_bytes = valid ? 16 : 0;

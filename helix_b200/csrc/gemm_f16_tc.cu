@@ -30,6 +30,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstring>
 #include <mutex>
 #include <unordered_map>
 
@@ -76,7 +77,22 @@ struct GemmParams {
   // convolution only
   const __half* x;
   ConvGeom g;
+  int im2col;      // A tiles come from an im2col tensor map over x (C a multiple of 64): no gather warps
+  // optional per-CTA timeline (null = off): kTraceWords 64-bit words per CTA, see trace_mark
+  unsigned long long* trace;
 };
+
+// Timeline layout per CTA: [0] globaltimer at start, [1] clock64 at start, [2] clock64 when global
+// memory may be touched, [3] clock64 and [4] globaltimer at teardown; then for each of the first
+// kTraceTiles work items six clock64 stamps: producer first / last request, MMA issue start / end,
+// epilogue start / end.
+constexpr int kTraceTiles = 20;
+constexpr int kTraceWords = 8 + 6 * kTraceTiles;
+
+__device__ __forceinline__ void trace_mark(const GemmParams& p, int idx, int slot) {
+  if (p.trace != nullptr && idx < kTraceTiles)
+    p.trace[(size_t)blockIdx.x * kTraceWords + 8 + idx * 6 + slot] = (unsigned long long)clock64();
+}
 
 struct WorkItem {
   int m_blk, n_blk, b;
@@ -186,6 +202,10 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   const int grid = gridDim.x;
 
   if (threadIdx.x == 0) {
+    if (p.trace != nullptr) {
+      p.trace[(size_t)cta * kTraceWords + 0] = global_timer_ns();
+      p.trace[(size_t)cta * kTraceWords + 1] = (unsigned long long)clock64();
+    }
     for (int s = 0; s < stages; ++s) {
       mbar_init(&full_bar[s], CONV ? kConvProducerWarps * 32 + 1 : 1);
       mbar_init(&empty_bar[s], 1);
@@ -222,6 +242,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   // the preceding kernel.  From here on global memory is read and written: unless the caller
   // declared the launch independent of its predecessor, wait for that kernel to complete.
   if (!p.independent) griddep_wait();
+  if (threadIdx.x == 0 && p.trace != nullptr) p.trace[(size_t)cta * kTraceWords + 2] = (unsigned long long)clock64();
 
   if (warp < kProducerWarps) {
     // ------------------------------------------------------------------ producers
@@ -231,7 +252,19 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         uint32_t phase = 0;
         bool ok = true;
         WorkItem w;
+        const int cblocks = p.im2col ? p.g.C / kBK : 1;   // 64-channel blocks per filter tap
         for (int idx = 0; ok && get_item(p, cta, grid, idx, w); ++idx) {
+          // convolution through the im2col map: base pixel of the tile's first output pixel
+          int pix_w = 0, pix_h = 0, pix_n = 0;
+          if (p.im2col) {
+            const int m0 = w.m_blk * kBM;
+            const int HoWo = p.g.Ho * p.g.Wo;
+            pix_n = m0 / HoWo;
+            const int rem = m0 - pix_n * HoWo;
+            const int ho = rem / p.g.Wo;
+            pix_h = ho * p.g.stride - p.g.pad;
+            pix_w = (rem - ho * p.g.Wo) * p.g.stride - p.g.pad;
+          }
           for (int kb = w.kb0; kb < w.kb1 && ok; kb += p.load_group) {
             // Wait for a whole group of free stages first, then request the group's slabs back to
             // back: every row then has load_group * 128 contiguous bytes in flight at once.
@@ -243,15 +276,26 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
               if (++s2 == stages) { s2 = 0; ph2 ^= 1; }
             }
             if (!ok) break;
+            if (kb == w.kb0) trace_mark(p, idx, 0);
             for (int g = 0; g < gcount; ++g) {
               mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
-              tma_load_3d(sA + (size_t)stage * kATileBytes, &tmap_a, &full_bar[stage], (kb + g) * kBK,
-                          w.m_blk * kBM, w.b);
+              if (p.im2col) {
+                // K is ordered (r, s, c): slab kb is filter tap kb / cblocks, channels 64 * (kb % cblocks)
+                const int tap = (kb + g) / cblocks;
+                const int cb = (kb + g) - tap * cblocks;
+                const int fr = tap / p.g.S;
+                tma_load_im2col_4d(sA + (size_t)stage * kATileBytes, &tmap_a, &full_bar[stage], cb * kBK, pix_w,
+                                   pix_h, pix_n, (uint16_t)(tap - fr * p.g.S), (uint16_t)fr);
+              } else {
+                tma_load_3d(sA + (size_t)stage * kATileBytes, &tmap_a, &full_bar[stage], (kb + g) * kBK,
+                            w.m_blk * kBM, w.b);
+              }
               tma_load_3d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, &full_bar[stage], (kb + g) * kBK,
                           w.n_blk * BN, w.b);
               if (++stage == stages) { stage = 0; phase ^= 1; }
             }
           }
+          trace_mark(p, idx, 1);
         }
       }
     } else {
@@ -306,6 +350,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
           if (!ok) break;
           if (threadIdx.x == 0) {
+            if (kb == w.kb0) trace_mark(p, idx, 0);
             mbar_arrive_expect_tx(&full_bar[stage], L::kBTileBytes);
             tma_load_3d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, &full_bar[stage], kb * kBK, w.n_blk * BN, 0);
           }
@@ -329,6 +374,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           cp_async_mbar_arrive_noinc(&full_bar[stage]);
           if (++stage == stages) { stage = 0; phase ^= 1; }
         }
+        if (threadIdx.x == 0) trace_mark(p, idx, 1);
       }
       cp_async_wait<0>();  // nothing of this thread's is in flight when the CTA tears down
     }
@@ -345,6 +391,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         ok = mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status);
         if (!ok) break;
         tc_fence_after_sync();
+        trace_mark(p, idx, 2);
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status);
@@ -364,6 +411,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           if (++stage == stages) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit(&tmem_full[acc]);
+        trace_mark(p, idx, 3);
       }
     }
   } else {
@@ -379,6 +427,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       ok = mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status);
       if (!ok) break;
       tc_fence_after_sync();
+      if (quarter == 0 && lane == 0) trace_mark(p, idx, 4);
       const int trow = quarter * 32 + lane;      // row inside the tile
       const int row = w.m_blk * kBM + trow;      // index on the 128-row (A side) axis
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
@@ -439,6 +488,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+          if (quarter == 0 && lane == 0) trace_mark(p, idx, 5);
           continue;
         }
       }
@@ -510,6 +560,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (quarter == 0 && lane == 0) trace_mark(p, idx, 5);
     }
     if (p.tma_store && lane == 0) tma_store_wait_all();   // staged boxes are in global memory before exit
   }
@@ -517,6 +568,10 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   // ------------------------------------------------------------------ teardown
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0 && p.trace != nullptr) {
+    p.trace[(size_t)cta * kTraceWords + 3] = (unsigned long long)clock64();
+    p.trace[(size_t)cta * kTraceWords + 4] = global_timer_ns();
+  }
   if (warp == kMmaWarp) {
     __syncwarp();
     tc_fence_after_sync();
@@ -656,18 +711,93 @@ static int make_tmap(CUtensorMap* map, const void* base, int64_t K, int64_t rows
   return HELIX_OK;
 }
 
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const int*, const int*, cuuint32_t, cuuint32_t,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeIm2colFn get_encode_im2col_fn() {
+  static EncodeIm2colFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeIm2colFn>(sym);
+  });
+  return fn;
+}
+
+// The im2col path needs whole 64-channel blocks per filter tap (one 128-byte swizzled row per
+// pixel), window parameters inside the tensor map's field widths, and an activation tensor of
+// at least 128 KiB (smaller ones stay on the gathering kernel, as do all other geometries).
+static bool conv_im2col_eligible(const ConvGeom& g) {
+  const int64_t bytes = (int64_t)g.NB * g.H * g.W * g.C * 2;
+  return (g.C % kBK) == 0 && g.stride >= 1 && g.stride <= 8 && g.pad <= 127 && g.R <= 128 && g.S <= 128 &&
+         g.pad - (g.R - 1) >= -128 && g.pad - (g.S - 1) >= -128 && bytes >= 131072 && g.C <= 65535 &&
+         get_encode_im2col_fn() != nullptr;
+}
+
+// Activations x[N][H][W][C] as a 4-D im2col map (dimensions C, W, H, N): one load brings 128
+// consecutive output pixels x 64 channels for one filter tap, 128-byte swizzled like a GEMM A tile.
+// The bounding box [-pad, extent - 1 + pad - (filter - 1)] holds the window origins; stepping it
+// with the convolution stride visits exactly Wo x Ho origins per image.
+static int make_tmap_im2col(CUtensorMap* map, const void* x, const ConvGeom& g) {
+  EncodeIm2colFn fn = get_encode_im2col_fn();
+  if (!fn) return HELIX_ERR_CUDA;
+  if (reinterpret_cast<uintptr_t>(x) & 15) return HELIX_ERR_ALIGN;
+  struct Key {
+    const void* x;
+    int v[8];
+    bool operator==(const Key& o) const { return x == o.x && std::memcmp(v, o.v, sizeof(v)) == 0; }
+  };
+  struct KeyHash {
+    size_t operator()(const Key& k) const {
+      size_t h = reinterpret_cast<size_t>(k.x);
+      for (int i = 0; i < 8; ++i) h ^= (size_t)k.v[i] + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+      return h;
+    }
+  };
+  static std::mutex mu;
+  static std::unordered_map<Key, CUtensorMap, KeyHash> cache;
+  const Key key{x, {g.NB, g.H, g.W, g.C, g.R, g.S, g.stride, g.pad}};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *map = it->second;
+      return HELIX_OK;
+    }
+  }
+  cuuint64_t dims[4] = {(cuuint64_t)g.C, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.NB};
+  cuuint64_t strides[3] = {(cuuint64_t)g.C * 2, (cuuint64_t)g.W * g.C * 2, (cuuint64_t)g.H * g.W * g.C * 2};
+  int lower[2] = {-g.pad, -g.pad};                              // (w, h)
+  int upper[2] = {g.pad - (g.S - 1), g.pad - (g.R - 1)};
+  cuuint32_t estr[4] = {1, (cuuint32_t)g.stride, (cuuint32_t)g.stride, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(x), dims, strides, lower, upper,
+                  (cuuint32_t)kBK, (cuuint32_t)kBM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return HELIX_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache.size() >= 4096) cache.clear();
+  cache.emplace(key, *map);
+  return HELIX_OK;
+}
+
 static const int kTileNs[] = {256, 128, 64, 32, 16};
 constexpr int kNumTileNs = sizeof(kTileNs) / sizeof(kTileNs[0]);
 
 // tile widths x {plain, swap_ab} x {tile list, stream-K}
-// ... plus the two CTA-pair configurations (256 x 256 and 256 x 128 per pair)
-int gemm_f16_num_configs() { return kNumTileNs * 4 + 2; }
+// ... plus the three CTA-pair configurations (256 x 256, 256 x 192 and 256 x 128 per pair)
+static const int kPairTileNs[] = {256, 128, 192};
+int gemm_f16_num_configs() { return kNumTileNs * 4 + 3; }
 void gemm_f16_get_config(int idx, helix_cfg_t* out) {
   *out = helix_cfg_t{};
   out->op = HELIX_OP_GEMM_F16;
   out->tile_m = kBM;
   if (idx >= kNumTileNs * 4) {
-    out->tile_n = idx == kNumTileNs * 4 ? 256 : 128;
+    out->tile_n = kPairTileNs[std::min(idx - kNumTileNs * 4, 2)];
     out->tile_k = kBK;
     out->cta_group = 2;
     out->split_k = 1;
@@ -708,7 +838,8 @@ static double slab_us(int bn) {
 // the scripts layer supersedes it).  Skinny M goes on the UMMA N axis (swap_ab); otherwise the
 // tile width minimising waves x slabs x slab time wins; stream-K is used when whole-tile
 // scheduling would leave a large part of the machine idle.
-void gemm_f16_default_config(int M, int N, int K, int batch, int sm_count, bool conv, helix_cfg_t* out) {
+static void default_config_impl(int M, int N, int K, int batch, int sm_count, bool conv, bool allow_pair,
+                                helix_cfg_t* out) {
   *out = helix_cfg_t{};
   out->op = conv ? HELIX_OP_CONV_F16 : HELIX_OP_GEMM_F16;
   out->tile_m = kBM;
@@ -751,17 +882,42 @@ void gemm_f16_default_config(int M, int N, int K, int batch, int sm_count, bool 
   out->stages = max_stages(out->tile_n, conv);
   // CTA pairs on a 256 x 256 tile: half the B bytes per CTA and a 6-deep ring; measured about
   // 0.41 us per 64-deep slab of a pair tile, i.e. twice the work of a 128 x 256 slab in less time.
-  if (!conv && !swap && M > kBM && N >= 128 && num_kb >= 8) {   // short K is epilogue bound: no gain
-    const int64_t pair_tiles = (int64_t)((M + 2 * kBM - 1) / (2 * kBM)) * ((N + 255) / 256) * batch;
+  if (allow_pair && !conv && !swap && M > kBM && N >= 128 && num_kb >= 8) {   // short K is epilogue bound: no gain
+    // 256 x 192 pair tiles are there for tile counts that quantise badly at 256 x 256
     const int64_t pairs = std::max(1, sm_count / 2);
-    const double t2 = (double)((pair_tiles + pairs - 1) / pairs) * num_kb * 0.41 + 4.0;
-    if (t2 < best) {
-      out->cta_group = 2;
-      out->tile_n = 256;
-      out->stream_k = 0;
-      out->stages = gemm_f16_pair_max_stages(256);
+    const int widths[2] = {256, 192};
+    const double slab[2] = {0.40, 0.365};   // measured: the narrower tile re-reads A from shared memory more often
+    for (int i = 0; i < 2; ++i) {
+      const int bn = widths[i];
+      const int64_t pair_tiles = (int64_t)((M + 2 * kBM - 1) / (2 * kBM)) * ((N + bn - 1) / bn) * batch;
+      const double t2 = (double)((pair_tiles + pairs - 1) / pairs) * num_kb * slab[i] + 4.0;
+      if (t2 < best) {
+        best = t2;
+        out->cta_group = 2;
+        out->tile_n = bn;
+        out->stream_k = 0;
+        out->stages = gemm_f16_pair_max_stages(bn);
+      }
     }
   }
+}
+
+void gemm_f16_default_config(int M, int N, int K, int batch, int sm_count, bool conv, helix_cfg_t* out) {
+  default_config_impl(M, N, K, batch, sm_count, conv, true, out);
+}
+
+// Convolution: a 1x1, stride-1, unpadded one is a plain GEMM over the pixel list; geometries the
+// im2col tensor map covers run the GEMM kernel's schedule (one-CTA tiles); the rest gather.
+void conv_f16_default_config(const ConvGeom& g, int sm_count, helix_cfg_t* out) {
+  const int M = (int)std::min<int64_t>((int64_t)g.NB * g.Ho * g.Wo, 0x7fffffff);
+  const int K = (int)std::min<int64_t>((int64_t)g.R * g.S * g.C, 0x7fffffff);
+  if (g.R == 1 && g.S == 1 && g.stride == 1 && g.pad == 0)
+    default_config_impl(M, g.KO, K, 1, sm_count, false, true, out);
+  else if (conv_im2col_eligible(g))
+    default_config_impl(M, g.KO, K, 1, sm_count, false, false, out);
+  else
+    default_config_impl(M, g.KO, K, 1, sm_count, true, false, out);
+  out->op = HELIX_OP_CONV_F16;
 }
 
 // Stream-K decomposition of `tiles` tiles over `grid` CTAs.
@@ -787,6 +943,19 @@ size_t gemm_f16_workspace_bytes(const helix_cfg_t* cfg, int M, int N, int K, int
   if (cfg->split_k <= 1) return 0;
   return (size_t)cfg->split_k * std::max(batch, 1) * (size_t)M * N * sizeof(float);
 }
+
+// Timeline capture: while a buffer is set, every one-CTA GEMM / convolution launch whose grid fits
+// writes its per-CTA stamps there (later launches overwrite earlier ones).
+static std::mutex g_trace_mu;
+static unsigned long long* g_trace_buf = nullptr;
+static size_t g_trace_bytes = 0;
+
+void gemm_f16_set_trace(void* device_buf, size_t bytes) {
+  std::lock_guard<std::mutex> lock(g_trace_mu);
+  g_trace_buf = static_cast<unsigned long long*>(device_buf);
+  g_trace_bytes = device_buf ? bytes : 0;
+}
+int gemm_f16_trace_words_per_cta() { return kTraceWords; }
 
 template <int BN, bool CONV>
 static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
@@ -887,6 +1056,10 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
     p.tma_store = 1;
   // a launch that shares its workspace with its neighbours on the stream is never independent of them
   p.independent = (independent && !fixup && !reduce) ? 1 : 0;
+  {
+    std::lock_guard<std::mutex> lock(g_trace_mu);
+    p.trace = (g_trace_buf && g_trace_bytes >= (size_t)grid * kTraceWords * 8) ? g_trace_buf : nullptr;
+  }
   cudaError_t e = cudaErrorInvalidValue;
 #define HELIX_BN_CASE(BNV)                                                                 \
   case BNV:                                                                                \
@@ -989,11 +1162,13 @@ int conv_f16_launch(const helix_cfg_t* cfg_in, const void* x, const void* w, voi
     return gemm_f16_launch(use, x, g.C, w, g.C, y, N, M, N, K, 1, 0, 0, 0, ws, ws_bytes, status_dev, sm_count,
                            independent, stream, launches);
   }
+  const bool gather_forced = cfg_in && cfg_in->tile_m != 0 && cfg_in->conv_gather != 0;
+  const bool im2col = !gather_forced && conv_im2col_eligible(g);
   helix_cfg_t cfg;
   if (cfg_in && cfg_in->tile_m != 0) {
     cfg = *cfg_in;
   } else {
-    gemm_f16_default_config(M, N, K, 1, sm_count, true, &cfg);
+    conv_f16_default_config(g, sm_count, &cfg);
     if (!ws || ws_bytes < gemm_f16_workspace_bytes(&cfg, M, N, K, 1, sm_count)) cfg.stream_k = 0;
   }
   if (cfg.tile_m != kBM || cfg.cta_group > 1 || cfg.swap_ab) return HELIX_ERR_UNSUPPORTED;
@@ -1005,9 +1180,16 @@ int conv_f16_launch(const helix_cfg_t* cfg_in, const void* x, const void* w, voi
   p.status = status_dev;
   p.x = static_cast<const __half*>(x);
   p.g = g;
-  CUtensorMap tb;
+  CUtensorMap ta, tb;
   int rc;
   if ((rc = make_tmap(&tb, w, K, N, 1, K, 0, cfg.tile_n)) != HELIX_OK) return rc;
+  if (im2col) {
+    // Same kernel as a GEMM: the one producer thread asks the im2col map for 128 pixels x 64
+    // channels of one filter tap per K slab.
+    if ((rc = make_tmap_im2col(&ta, x, g)) != HELIX_OK) return rc;
+    p.im2col = 1;
+    return launch_common(cfg, false, ta, tb, p, y, N, 0, ws, ws_bytes, sm_count, independent, stream, launches);
+  }
   return launch_common(cfg, true, tb, tb, p, y, N, 0, ws, ws_bytes, sm_count, independent, stream, launches);
 }
 

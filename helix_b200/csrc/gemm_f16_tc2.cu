@@ -413,7 +413,7 @@ int gemm_f16_pair_launch(const helix_cfg_t& cfg, const void* A, int64_t lda, con
                          int64_t ldc, int M, int N, int K, int batch, int64_t sa, int64_t sb, int64_t sc,
                          int* status_dev, int sm_count, bool independent, cudaStream_t stream, int64_t* launches) {
   const int bn = cfg.tile_n;
-  if (bn != 256 && bn != 128) return HELIX_ERR_UNSUPPORTED;
+  if (bn != 256 && bn != 192 && bn != 128) return HELIX_ERR_UNSUPPORTED;
   if (cfg.swap_ab || cfg.stream_k || cfg.split_k > 1) return HELIX_ERR_UNSUPPORTED;
   Gemm2Params p{};
   p.PM = M; p.PN = N; p.K = K; p.batch = batch;
@@ -442,8 +442,9 @@ int gemm_f16_pair_launch(const helix_cfg_t& cfg, const void* A, int64_t lda, con
     p.tma_store = 1;
   const int pairs = (int)std::min<int64_t>(tiles, sm_count / 2);
   const size_t smem = 1024 + (size_t)p.stages * (kATileBytes + (bn / 2) * kBK * 2) + kStagingBytes + 256;
-  const cudaError_t e = bn == 256 ? launch_pair<256>(ta, tb, tc, p, 2 * pairs, smem, stream)
-                                  : launch_pair<128>(ta, tb, tc, p, 2 * pairs, smem, stream);
+  const cudaError_t e = bn == 256   ? launch_pair<256>(ta, tb, tc, p, 2 * pairs, smem, stream)
+                        : bn == 192 ? launch_pair<192>(ta, tb, tc, p, 2 * pairs, smem, stream)
+                                    : launch_pair<128>(ta, tb, tc, p, 2 * pairs, smem, stream);
   if (e != cudaSuccess) return HELIX_ERR_CUDA;
   ++*launches;
   return HELIX_OK;

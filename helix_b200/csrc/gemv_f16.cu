@@ -250,9 +250,8 @@ int gemv_f16_launch(const helix_cfg_t* cfg, const void* W, int64_t ldw, const vo
 // Split-K GEMV whose partial sums live in a buffer that is part of the library image.
 //
 // Some users of this library may not create device memory at the moment they need a GEMV: a
-// decode loop that has handed every byte of HBM to its own pool, or code that runs while a
-// stream is being recorded, cannot call cudaMalloc (it may fail, it synchronises the device, and
-// it is not allowed during recording).  For them the fp32 partials of the split-K variant are
+// decode loop that has handed every byte of HBM to its own pool cannot call cudaMalloc (it may
+// fail, and it synchronises the device).  For them the fp32 partials of the split-K variant are
 // kept in the fixed array below instead of a caller-supplied workspace.  Every GPU on which the
 // library is loaded carries these 4 MiB until the process exits.
 //
@@ -265,7 +264,7 @@ static __device__ __align__(256) float g_gemv_static_scratch[kGemvStaticFloats];
 size_t gemv_f16_static_capacity_floats() { return kGemvStaticFloats; }
 
 // The set-up (symbol lookup) happens in the first call made on each device, so that first call
-// should be issued outside any stream recording.  All calls share the one array: it still holds
+// should come before any stream capture.  All calls share the one array: it still holds
 // the previous call's partials when a call starts, which is harmless because the kernel writes
 // every slot the reduction reads before it is read (nothing has to start at zero) -- but two
 // calls that may run on the GPU at the same time (different streams) would overwrite each

@@ -130,12 +130,14 @@ def profile_fp16(fast=False, progress=None):
     if fast:                                         # interpolate 128 between 64 and 256
         f64, f256 = measured[64], measured[256]
         measured[128] = tuple(a + (b - a) * (128 - 64) / (256 - 64) for a, b in zip(f64, f256))
-    # CTA pairs on 256 x 256 tiles: 256 pair tiles on sms/2 pairs
-    pair_cfg = ops.make_cfg(OP_GEMM_F16, 128, 256, 64, cta_group=2)
-    pair_waves = -(-256 // (sms // 2))
-    t1 = time_gemm_f16(4096, 4096, 512, pair_cfg); tick()
-    t2 = time_gemm_f16(4096, 4096, 4096, pair_cfg); tick()
-    d[costmodel.PAIR_KEY] = tuple(float(v) for v in _two_point(t1, pair_waves * 8, t2, pair_waves * 64))
+    # CTA pairs on 256 x BN tiles: 16 x ceil(4096 / BN) pair tiles on sms/2 pairs
+    for pkey in costmodel.PAIR_KEYS:
+        bn = pkey[2]
+        pair_cfg = ops.make_cfg(OP_GEMM_F16, 128, bn, 64, cta_group=2)
+        pair_waves = -(-(16 * -(-4096 // bn)) // (sms // 2))
+        t1 = time_gemm_f16(4096, 4096, 512, pair_cfg); tick()
+        t2 = time_gemm_f16(4096, 4096, 4096, pair_cfg); tick()
+        d[pkey] = tuple(float(v) for v in _two_point(t1, pair_waves * 8, t2, pair_waves * 64))
     skinny = {}
     for bn in ((16,) if fast else (32, 16)):          # skinny M on the UMMA N axis: everything streams from DRAM
         N = 128 * sms

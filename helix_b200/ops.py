@@ -71,13 +71,39 @@ def configs(op):
     return out
 
 
+def default_config(launch):
+    """The configuration the library picks for `launch` when its cfg is left zero (helix_default_config)."""
+    c = Cfg()
+    check(_lib.load().helix_default_config(ctypes.byref(launch), ctypes.byref(c)), "helix_default_config")
+    return c
+
+
+def kernel_name(launch):
+    """Name of the main kernel `launch` resolves to, as a profiler lists it."""
+    c = launch.cfg if launch.cfg.tile_n or launch.cfg.tile_m else default_config(launch)
+    if launch.op == _lib.OP_GEMV_F16:
+        return "gemv_f16_kernel"
+    if launch.op == _lib.OP_GEMM_F32:
+        return "sgemm_f32_kernel<%d,%d>" % (c.tile_m, c.tile_n)
+    if c.cta_group == 2:
+        return "gemm_f16_tc2_kernel<%d>" % c.tile_n
+    gathers = False
+    if launch.op == OP_CONV_F16:
+        n, h, w, ch, _, r, s, stride, pad = list(launch.conv)
+        as_gemm = r == 1 and s == 1 and stride == 1 and pad == 0
+        im2col = ch % 64 == 0 and n * h * w * ch * 2 >= 131072 and stride <= 8 and not c.conv_gather
+        gathers = not as_gemm and not im2col
+    return "gemm_f16_tc_kernel<%d,%d>" % (c.tile_n, 1 if gathers else 0)
+
+
 def make_cfg(op, tile_m=128, tile_n=128, tile_k=64, stages=0, cta_group=1, split_k=1, swap_ab=0, raster=8,
-             thread_m=0, thread_n=0, load_group=0, stream_k=0):
+             thread_m=0, thread_n=0, load_group=0, stream_k=0, conv_gather=0):
     c = Cfg()
     c.op, c.tile_m, c.tile_n, c.tile_k, c.stages = op, tile_m, tile_n, tile_k, stages
     c.cta_group, c.split_k, c.swap_ab, c.raster, c.thread_m, c.thread_n = cta_group, split_k, swap_ab, raster, thread_m, thread_n
     c.load_group = load_group
     c.stream_k = stream_k
+    c.conv_gather = conv_gather
     return c
 
 
@@ -241,6 +267,27 @@ def time_launches(launches, warmup=3, iters=20, use_graph=False):
                                           ctypes.byref(avg), ctypes.byref(mn), ctypes.byref(mx)),
           "helix_time_launches")
     return avg.value, mn.value, mx.value
+
+
+def capture_timeline(launch, warm=2):
+    """Run `launch` (a one-CTA fp16 GEMM / convolution) with timeline capture on and return an int64
+    array [CTAs, words] of the stamps described at helix_trace_buffer; rows of CTAs that did not run
+    stay zero."""
+    lib = _lib.load()
+    words = lib.helix_trace_words_per_cta()
+    ctas = device_info().sm_count
+    buf = torch.zeros((ctas, words), dtype=torch.int64, device="cuda")
+    for _ in range(warm):
+        run(launch)
+    torch.cuda.synchronize()
+    check(lib.helix_trace_buffer(buf.data_ptr(), buf.numel() * 8), "helix_trace_buffer")
+    try:
+        run(launch)
+        torch.cuda.synchronize()
+    finally:
+        lib.helix_trace_buffer(None, 0)
+    check_status()
+    return buf.cpu().numpy()
 
 
 def launch_count():

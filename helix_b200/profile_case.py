@@ -1,6 +1,6 @@
 """Run one operator a few times on seeded data -- the target of `ncu` captures.
 
-  python -m helix_b200.profile_case gemm M N K [--batch B] [--bn 256] [--stream-k] [--swap] [--reps 3]
+  python -m helix_b200.profile_case gemm M N K [--batch B] [--bn 256] [--pair] [--stream-k] [--swap] [--reps 3]
   python -m helix_b200.profile_case conv B IC H W OC kH kW stride pad [--bn 128] [--reps 3]
   python -m helix_b200.profile_case gemv ROWS K [--m 1] [--reps 3]
   python -m helix_b200.profile_case sgemm M N K [--reps 3]
@@ -25,6 +25,8 @@ def main(argv=None):
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--stream-k", action="store_true")
     ap.add_argument("--swap", action="store_true")
+    ap.add_argument("--pair", action="store_true", help="CTA-pair kernel (cta_group 2) with the --bn tile width")
+    ap.add_argument("--gather", action="store_true", help="conv: gathering producer warps even where a tensor map applies")
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--reps", type=int, default=3)
     args = ap.parse_args(argv)
@@ -34,7 +36,9 @@ def main(argv=None):
         a, b = datagen.c3_gemm(M, N, K, seed=2, batch=args.batch)
         a, b = torch.from_numpy(a).to(dev), torch.from_numpy(b).to(dev)
         cfg = None
-        if args.bn:
+        if args.bn and args.pair:
+            cfg = ops.make_cfg(OP_GEMM_F16, 128, args.bn, 64, cta_group=2)
+        elif args.bn:
             cfg = ops.make_cfg(OP_GEMM_F16, 128, args.bn, 64, stream_k=int(args.stream_k), swap_ab=int(args.swap),
                                load_group=2)
         for _ in range(args.reps):
@@ -43,7 +47,10 @@ def main(argv=None):
         geom = tuple(args.dims)
         x, w = datagen.c4_conv(*geom, seed=3)
         x, w = torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev)
-        cfg = ops.make_cfg(OP_CONV_F16, 128, args.bn, 64, stream_k=int(args.stream_k)) if args.bn else None
+        cfg = None
+        if args.bn:
+            cfg = ops.make_cfg(OP_CONV_F16, 128, args.bn, 64, stream_k=int(args.stream_k),
+                               conv_gather=int(args.gather))
         for _ in range(args.reps):
             out = ops.conv2d_f16_nhwc(x, w, geom[7], geom[8], cfg=cfg)
     elif args.op == "gemv":

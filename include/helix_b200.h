@@ -85,7 +85,10 @@ typedef struct helix_cfg {
   int stream_k;  /* GEMM_F16/CONV: 1 = whole waves of tiles round-robin, the K slabs of the
                     remaining tiles dealt evenly to all CTAs (needs a workspace); overrides
                     split_k                                                              */
-  int reserved[3];
+  int conv_gather; /* CONV_F16: 0 = activations arrive through an im2col tensor map wherever the
+                      geometry allows it (C a multiple of 64, tensor of 128 KiB or more);
+                      1 = always use the gathering (cp.async) producer warps               */
+  int reserved[2];
 } helix_cfg_t;
 
 /* A fully described launch; the tagged union the timing entry point iterates. */
@@ -197,14 +200,23 @@ int helix_conv2d_f16_nhwc_host(const void* x, const void* w, void* y, int N, int
  * of a caller workspace, so split_k * m * rows may not exceed HELIX_GEMV_STATIC_FLOATS, else
  * HELIX_ERR_CAPACITY.  It has no counterpart in the reference.  Meant for callers that cannot
  * allocate when they need the product, e.g. a decode loop that has given all HBM to its own
- * pool, or code running while a stream is being recorded.  The first call on each device looks
- * up the array's device address, so make that call outside any stream recording.  The array is
- * shared by all calls and keeps the last call's partials; a call overwrites every slot before
+ * pool.  The first call on each device looks up the array's device address (the set-up), so
+ * make that first call before any stream capture begins.  The array is shared by all calls and keeps the last call's partials; a call overwrites every slot before
  * reading it, so nothing needs clearing, but calls that can overlap on the GPU (different
  * streams) corrupt each other and must be ordered by the caller. */
 #define HELIX_GEMV_STATIC_FLOATS (1u << 20)
 int helix_gemv_f16_static(const void* W, int64_t ldw, const void* X, int64_t ldx, void* Y, int64_t ldy,
                           int64_t ldy_inner, int rows, int K, int m, int split_k, void* stream);
+
+/* Timeline capture for tuning the one-CTA fp16 GEMM / convolution kernel (the reference has only
+ * whole-kernel cudaEvent times, gemm.cu:622-660).  While a device buffer is set, each such launch
+ * whose grid fits writes helix_trace_words_per_cta() 64-bit words per CTA into it: [0] globaltimer
+ * and [1] clock64 at CTA start, [2] clock64 when global memory may first be touched, [3] clock64
+ * and [4] globaltimer at teardown, then from word 8 on, for each of the first 20 work items of the
+ * CTA, six clock64 stamps: first / last load request, MMA issue start / end, epilogue start / end.
+ * Later launches overwrite earlier ones.  Pass NULL to switch capture off (the default). */
+int helix_trace_buffer(void* device_buf, size_t bytes);
+int helix_trace_words_per_cta(void);
 
 /* Number of kernel launches this process has queued through the library (all ops). */
 int64_t helix_launch_count(void);

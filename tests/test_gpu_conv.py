@@ -96,6 +96,34 @@ def test_conv_benchmark_layers_sampled(oracle, layer):
         util.assert_f16_close(y[img:img + 1].cpu().numpy(), y32, f"layer {layer} image {img}")
 
 
+@pytest.mark.parametrize("geom", [
+    (2, 64, 32, 32, 64, 3, 3, 1, 1),      # 3x3 same-size: padding on all four sides
+    (3, 64, 30, 30, 72, 3, 3, 1, 1),      # M = 2700: tiles start mid-row and the last one is ragged
+    (2, 128, 33, 31, 64, 3, 3, 2, 1),     # stride 2, odd sizes, two 64-channel blocks per tap
+    (2, 64, 40, 40, 128, 1, 1, 2, 0),     # strided 1x1 (ResNet downsample)
+    (2, 64, 31, 37, 64, 3, 3, 3, 0),      # stride 3 that does not divide the extent, no padding
+    (2, 64, 24, 24, 32, 5, 5, 1, 2),      # 5x5
+    (1, 64, 40, 40, 64, 7, 7, 2, 3),      # 7x7 stride 2 pad 3
+    (2, 64, 32, 32, 64, 1, 3, 1, 1),      # 1x3 filter with padding also on the 1-tap axis
+    (2, 192, 20, 20, 80, 3, 3, 1, 1),     # three channel blocks, narrow ragged N
+])
+def test_conv_im2col_tensor_map_matches_gather_and_oracle(oracle, geom):
+    """Activations through the im2col tensor map (C a multiple of 64, tensor of 128 KiB or more)
+    against the gathering producer on the same tile configuration -- same accumulation order, so
+    the two must agree bit for bit -- and against the oracle."""
+    B, C, H, W, OC, kh, kw, stride, pad = geom
+    assert C % 64 == 0 and B * H * W * C * 2 >= 131072
+    x, w = datagen.c4_conv(*geom, seed=21)
+    bn = 64 if OC <= 64 else 128
+    tma = _run(x, w, stride, pad, ops.make_cfg(OP_CONV_F16, tile_m=128, tile_n=bn, tile_k=64))
+    gather = _run(x, w, stride, pad, ops.make_cfg(OP_CONV_F16, tile_m=128, tile_n=bn, tile_k=64, conv_gather=1))
+    assert np.array_equal(tma, gather)
+    auto = _run(x, w, stride, pad)
+    _, y32 = oracle.conv2d_nhwc_f16(x, w, stride, pad)
+    util.assert_f16_close(tma, y32, f"im2col conv {geom}")
+    util.assert_f16_close(auto, y32, f"im2col conv {geom} default configuration")
+
+
 @pytest.mark.parametrize("geom,bn", [((2, 64, 14, 14, 128, 3, 3, 1, 1), 128), ((5, 32, 9, 9, 72, 3, 3, 2, 1), 64),
                                      ((32, 128, 28, 28, 128, 3, 3, 1, 1), 128)])
 def test_conv_stream_k(oracle, geom, bn):

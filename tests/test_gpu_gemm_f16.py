@@ -224,6 +224,9 @@ def _pair(bn, stages=0):
     (256, (300, 520, 264)),       # ragged M, N, K
     (128, (2048, 2304, 512)),     # more tiles than CTA pairs
     (256, (100, 40, 72)),         # smaller than one tile
+    (192, (256, 192, 128)),       # 96-row B halves, three 64-column epilogue chunks
+    (192, (1024, 1000, 520)),     # ragged last 192-wide column of tiles, ring wraps
+    (192, (2304, 2112, 256)),     # more tiles than CTA pairs
 ])
 def test_gemm_cta_pairs(oracle, bn, shape):
     """tcgen05.mma.cta_group::2: two CTAs share a 256 x BN tile."""

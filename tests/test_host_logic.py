@@ -18,7 +18,7 @@ def synthetic_dict():
     d = {("sm_count",): 148, ("dram_gbs_per_sm",): 40.0, ("hbm_gbs",): 6000.0}
     slab = {256: 0.45e-6, 128: 0.31e-6, 64: 0.27e-6, 32: 0.26e-6, 16: 0.25e-6}
     for key in costmodel.gemm_keys():
-        d[key] = (4e-6, slab[key[2]])
+        d[key] = (4e-6, {256: 0.41e-6, 192: 0.33e-6}[key[2]] if key[3] == 2 else slab[key[2]])
     for bn in (256, 128, 64):
         d[("streamk_overhead", bn)] = 8e-6 + bn * 4e-8
         d[("conv_slab", bn)] = 0.6e-6

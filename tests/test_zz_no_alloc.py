@@ -1,7 +1,7 @@
 """GPU test of helix_gemv_f16_static, the split-K GEMV that never calls the device allocator.
 
 The entry point exists for callers that are not in a position to allocate when they need the
-product (all HBM already owned by their own pool, or a stream being recorded): its split-K
+product (all HBM already owned by their own pool): its split-K
 partial sums go to a fixed array inside the library.  This file is named so that pytest collects
 it after every other test file; it must pass both alone in a fresh process and at the end of a
 full run, because the fixed array is shared by all calls and keeps whatever the last one left.
