@@ -39,12 +39,12 @@ def is_valid_config(tile_n, swap_ab, mode, stages):
 
 
 def max_stages(tile_n):
-    budget = 227 * 1024 - 1024 - 256
+    budget = 227 * 1024 - 1024 - 256 - 32768     # alignment slack, barriers, output staging
     return min(8, budget // (TILE_M * TILE_K * 2 + tile_n * TILE_K * 2))
 
 
 def pair_max_stages(tile_n):
-    budget = 227 * 1024 - 1024 - 256 - 16384
+    budget = 227 * 1024 - 1024 - 256 - 32768
     return min(8, budget // (TILE_M * TILE_K * 2 + (tile_n // 2) * TILE_K * 2))
 
 

@@ -23,6 +23,32 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   return t;
 }
 
+// Division of a non-negative 31-bit integer by a divisor fixed at launch, as a multiply and a
+// shift (round-up reciprocal: mul = ceil(2^(31 + ceil(log2 d)) / d), exact for 0 <= a < 2^31).
+// A hardware-emulated integer division costs a single thread some 150 cycles, and the tile
+// decoders below sit on the critical path between two tiles of a persistent CTA.
+struct FastDiv {
+  uint32_t d, mul, shr;
+};
+inline FastDiv make_fastdiv(int divisor) {
+  FastDiv f{static_cast<uint32_t>(divisor > 0 ? divisor : 1), 0u, 0u};
+  if (f.d > 1) {
+    uint32_t lg = 0;
+    while ((1ull << lg) < f.d) ++lg;
+    const uint32_t p = 31 + lg;
+    f.mul = static_cast<uint32_t>(((1ull << p) + f.d - 1) / f.d);
+    f.shr = p - 32;
+  }
+  return f;
+}
+__device__ __forceinline__ int fast_div(int a, const FastDiv& f) {
+  return f.d == 1 ? a : static_cast<int>(__umulhi(static_cast<uint32_t>(a), f.mul) >> f.shr);
+}
+__device__ __forceinline__ void fast_divmod(int a, const FastDiv& f, int& q, int& r) {
+  q = fast_div(a, f);
+  r = a - q * static_cast<int>(f.d);
+}
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(
@@ -235,6 +261,8 @@ __device__ __forceinline__ void tma_store_3d(const void* desc, const void* smem_
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // until the bulk stores committed by this thread have finished READING shared memory
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// until at most one committed bulk store of this thread is still reading shared memory
+__device__ __forceinline__ void tma_store_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 // until they have completed altogether
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 

@@ -46,8 +46,9 @@ constexpr int kConvTableEntries = 4096;     // 8-channel chunks of the K axis (K
 constexpr int kConvProducerWarps = 8;       // gather warps: 16 tile rows each, 4 per thread
 constexpr int kConvRowsPerThread = 4;
 constexpr int kConvThreads = kConvProducerWarps * 32 + 32 + 128;  // + MMA warp + 4 epilogue warps
-constexpr int kGemmThreads = 32 + 32 + 128;                       // TMA warp + MMA warp + 4 epilogue warps
-constexpr int kStoreStagingBytes = 4 * 32 * 128;                  // one 32-row x 128-byte box per epilogue warp
+constexpr int kGemmProducerWarps = 4;      // TMA-issuing warps: K slab n belongs to warp n % load_warps
+constexpr int kGemmThreads = kGemmProducerWarps * 32 + 32 + 128;  // TMA warps + MMA warp + 4 epilogue warps
+constexpr int kStoreStagingBytes = 4 * 2 * 32 * 128;              // two 32-row x 128-byte boxes per epilogue warp
 
 enum OutMode { kOutDirect = 0, kOutSplitSlice = 1, kOutStreamSlot = 2 };
 
@@ -62,7 +63,9 @@ struct GemmParams {
   int tiles_m, tiles_n, num_kb;
   int raster;
   int stages;
-  int load_group;  // K slabs the TMA producer requests back to back (DRAM page locality)
+  int load_warps;  // warps that issue TMA loads (1..kGemmProducerWarps); an issuing thread is held for
+                   // a few hundred cycles per tensor copy, so several issuers are needed to keep the
+                   // ring full
   // tile-list schedule (stream_k == 0): items = tiles x split_k, item t of CTA c is c + i*grid
   int split_k, kb_per_split;
   int total_items;
@@ -80,6 +83,8 @@ struct GemmParams {
   int im2col;      // A tiles come from an im2col tensor map over x (C a multiple of 64): no gather warps
   // optional per-CTA timeline (null = off): kTraceWords 64-bit words per CTA, see trace_mark
   unsigned long long* trace;
+  // reciprocals of the divisors the tile decoders use
+  FastDiv fd_per_batch, fd_group, fd_raster, fd_split, fd_num_kb, fd_howo, fd_wo, fd_cblocks, fd_s;
 };
 
 // Timeline layout per CTA: [0] globaltimer at start, [1] clock64 at start, [2] clock64 when global
@@ -87,8 +92,14 @@ struct GemmParams {
 // kTraceTiles work items six clock64 stamps: producer first / last request, MMA issue start / end,
 // epilogue start / end.
 constexpr int kTraceTiles = 20;
-constexpr int kTraceWords = 8 + 6 * kTraceTiles;
+constexpr int kTraceSlabs = 32;   // per-slab stamps of the CTA's first K slabs: request issued, data consumed
+constexpr int kTraceWords = 8 + 6 * kTraceTiles + 2 * kTraceSlabs;
 
+__device__ __forceinline__ void trace_slab(const GemmParams& p, int which, int n) {
+  if (p.trace != nullptr && n < kTraceSlabs)
+    p.trace[(size_t)blockIdx.x * kTraceWords + 8 + 6 * kTraceTiles + which * kTraceSlabs + n] =
+        (unsigned long long)clock64();
+}
 __device__ __forceinline__ void trace_mark(const GemmParams& p, int idx, int slot) {
   if (p.trace != nullptr && idx < kTraceTiles)
     p.trace[(size_t)blockIdx.x * kTraceWords + 8 + idx * 6 + slot] = (unsigned long long)clock64();
@@ -102,16 +113,19 @@ struct WorkItem {
 };
 
 __device__ __forceinline__ void decode_tile(const GemmParams& p, int t, WorkItem& w) {
-  const int per_batch = p.tiles_m * p.tiles_n;
-  w.b = t / per_batch;
-  int r = t - w.b * per_batch;
-  const int group = p.raster * p.tiles_n;
-  const int gid = r / group;
+  int r, gid;
+  fast_divmod(t, p.fd_per_batch, w.b, r);
+  fast_divmod(r, p.fd_group, gid, r);
   const int first_m = gid * p.raster;
   const int gm = min(p.raster, p.tiles_m - first_m);
-  r -= gid * group;
-  w.m_blk = first_m + r % gm;
-  w.n_blk = r / gm;
+  int q;
+  if (gm == p.raster) {
+    q = fast_div(r, p.fd_raster);
+  } else {
+    q = r / gm;   // the last, narrower raster group only
+  }
+  w.m_blk = first_m + (r - q * gm);
+  w.n_blk = q;
 }
 
 // The idx-th work item of CTA `cta`; every role of the CTA walks the same sequence.
@@ -119,8 +133,9 @@ __device__ __forceinline__ bool get_item(const GemmParams& p, int cta, int grid,
   if (!p.stream_k) {
     int t = cta + idx * grid;
     if (t >= p.total_items) return false;
-    const int ks = t % p.split_k;
-    decode_tile(p, t / p.split_k, w);
+    int tile, ks;
+    fast_divmod(t, p.fd_split, tile, ks);
+    decode_tile(p, tile, w);
     w.kb0 = ks * p.kb_per_split;
     w.kb1 = min(p.num_kb, w.kb0 + p.kb_per_split);
     w.mode = p.split_k > 1 ? kOutSplitSlice : kOutDirect;
@@ -141,7 +156,7 @@ __device__ __forceinline__ bool get_item(const GemmParams& p, int cta, int grid,
   const int u0 = min(sk_units, cta * p.sk_upc);
   const int u1 = min(sk_units, u0 + p.sk_upc);
   if (u0 >= u1) return false;
-  const int j0 = u0 / p.num_kb;
+  const int j0 = fast_div(u0, p.fd_num_kb);
   const int split = min(u1, (j0 + 1) * p.num_kb);
   int j, a, b;
   if (s == 0) { j = j0; a = u0; b = split; }
@@ -170,7 +185,7 @@ __global__ void __launch_bounds__(CONV ? kConvThreads : kGemmThreads, 1)
 gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                    const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
   using L = SmemLayout<BN>;
-  constexpr int kProducerWarps = CONV ? kConvProducerWarps : 1;
+  constexpr int kProducerWarps = CONV ? kConvProducerWarps : kGemmProducerWarps;
   constexpr int kMmaWarp = kProducerWarps;
   constexpr int kTmemCols = L::tmem_cols();
   constexpr uint32_t kIdesc = umma_idesc_f16(kBM, BN);
@@ -247,55 +262,53 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   if (warp < kProducerWarps) {
     // ------------------------------------------------------------------ producers
     if (!CONV) {
-      if (lane == 0) {
-        int stage = 0;
-        uint32_t phase = 0;
+      // Producer warp j requests the K slabs n = j, j + load_warps, ... of the CTA's slab sequence
+      // (slabs are numbered through all work items; slab n lives in ring stage n % stages).  A
+      // tensor copy holds its issuing thread for a few hundred cycles whatever the box size, so
+      // one thread alone cannot keep the ring full; consecutive slabs issued by different warps
+      // also land in the same DRAM pages close in time.
+      if (lane == 0 && warp < p.load_warps) {
         bool ok = true;
+        int n_start = 0;      // number of the first slab of the current work item
+        int my_n = warp;      // next slab this warp requests; its ring stage and use parity follow it
+        int stage = warp;     // load_warps <= stages, so no wrap yet
+        uint32_t phase = 0;
         WorkItem w;
-        const int cblocks = p.im2col ? p.g.C / kBK : 1;   // 64-channel blocks per filter tap
         for (int idx = 0; ok && get_item(p, cta, grid, idx, w); ++idx) {
           // convolution through the im2col map: base pixel of the tile's first output pixel
           int pix_w = 0, pix_h = 0, pix_n = 0;
           if (p.im2col) {
-            const int m0 = w.m_blk * kBM;
-            const int HoWo = p.g.Ho * p.g.Wo;
-            pix_n = m0 / HoWo;
-            const int rem = m0 - pix_n * HoWo;
-            const int ho = rem / p.g.Wo;
+            int rem, ho, wo;
+            fast_divmod(w.m_blk * kBM, p.fd_howo, pix_n, rem);
+            fast_divmod(rem, p.fd_wo, ho, wo);
             pix_h = ho * p.g.stride - p.g.pad;
-            pix_w = (rem - ho * p.g.Wo) * p.g.stride - p.g.pad;
+            pix_w = wo * p.g.stride - p.g.pad;
           }
-          for (int kb = w.kb0; kb < w.kb1 && ok; kb += p.load_group) {
-            // Wait for a whole group of free stages first, then request the group's slabs back to
-            // back: every row then has load_group * 128 contiguous bytes in flight at once.
-            const int gcount = min(p.load_group, w.kb1 - kb);
-            int s2 = stage;
-            uint32_t ph2 = phase;
-            for (int g = 0; g < gcount && ok; ++g) {
-              ok = mbar_wait(&empty_bar[s2], ph2 ^ 1, abort_flag, p.status);
-              if (++s2 == stages) { s2 = 0; ph2 ^= 1; }
-            }
+          const int nkb = w.kb1 - w.kb0;
+          if (warp == 0) trace_mark(p, idx, 0);
+          for (; my_n < n_start + nkb; my_n += p.load_warps) {
+            const int kb = w.kb0 + (my_n - n_start);
+            ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status);
             if (!ok) break;
-            if (kb == w.kb0) trace_mark(p, idx, 0);
-            for (int g = 0; g < gcount; ++g) {
-              mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
-              if (p.im2col) {
-                // K is ordered (r, s, c): slab kb is filter tap kb / cblocks, channels 64 * (kb % cblocks)
-                const int tap = (kb + g) / cblocks;
-                const int cb = (kb + g) - tap * cblocks;
-                const int fr = tap / p.g.S;
-                tma_load_im2col_4d(sA + (size_t)stage * kATileBytes, &tmap_a, &full_bar[stage], cb * kBK, pix_w,
-                                   pix_h, pix_n, (uint16_t)(tap - fr * p.g.S), (uint16_t)fr);
-              } else {
-                tma_load_3d(sA + (size_t)stage * kATileBytes, &tmap_a, &full_bar[stage], (kb + g) * kBK,
-                            w.m_blk * kBM, w.b);
-              }
-              tma_load_3d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, &full_bar[stage], (kb + g) * kBK,
-                          w.n_blk * BN, w.b);
-              if (++stage == stages) { stage = 0; phase ^= 1; }
+            trace_slab(p, 0, my_n);
+            mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
+            if (p.im2col) {
+              // K is ordered (r, s, c): slab kb is filter tap kb / cblocks, channels 64 * (kb % cblocks)
+              int tap, cb, fr, fs;
+              fast_divmod(kb, p.fd_cblocks, tap, cb);
+              fast_divmod(tap, p.fd_s, fr, fs);
+              tma_load_im2col_4d(sA + (size_t)stage * kATileBytes, &tmap_a, &full_bar[stage], cb * kBK, pix_w,
+                                 pix_h, pix_n, (uint16_t)fs, (uint16_t)fr);
+            } else {
+              tma_load_3d(sA + (size_t)stage * kATileBytes, &tmap_a, &full_bar[stage], kb * kBK, w.m_blk * kBM, w.b);
             }
+            tma_load_3d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, &full_bar[stage], kb * kBK, w.n_blk * BN,
+                        w.b);
+            stage += p.load_warps;
+            if (stage >= stages) { stage -= stages; phase ^= 1; }
           }
-          trace_mark(p, idx, 1);
+          n_start += nkb;
+          if (warp == 0) trace_mark(p, idx, 1);
         }
       }
     } else {
@@ -384,6 +397,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      int nslab = 0;
       WorkItem w;
       for (int idx = 0; ok && get_item(p, cta, grid, idx, w); ++idx) {
         const int acc = idx & 1;
@@ -396,6 +410,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status);
           if (!ok) break;
+          trace_slab(p, 1, nslab++);
           // The gathered A tile was written through the generic proxy (cp.async); order those
           // writes, now visible through the barrier, before the tensor core's async-proxy reads.
           if (CONV) fence_proxy_async_smem();
@@ -421,6 +436,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const bool vec_ok = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
                         ((p.stride_c & 7) == 0);
     WorkItem w;
+    int box = 0;   // staging box in use; alternates over the whole run of the warp, across tiles
     for (int idx = 0; ok && get_item(p, cta, grid, idx, w); ++idx) {
       const int acc = idx & 1;
       const uint32_t acc_phase = (idx >> 1) & 1;
@@ -437,15 +453,18 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           // 32 x 128-byte staging box -> one TMA store (full 128-byte lines, edges clipped by the
           // tensor map).  The TMEM load of the next 64 columns is in flight while the current ones
           // are converted and stored.
-          uint8_t* stage_box = sC + (size_t)quarter * (32 * 128);
-          const uint32_t row_base = smem_u32(stage_box) + lane * 128;
+          // two staging boxes per warp: one is filled while the TMA store of the other drains
+          uint8_t* const stage_boxes = sC + (size_t)quarter * (2 * 32 * 128);
           uint32_t ra[32], rb[32], na[32], nb[32];
           // registers of a TMEM load are valid only after tcgen05.wait::ld, so the two register sets
           // alternate by name instead of being copied
           auto emit = [&](const uint32_t (&lo)[32], const uint32_t (&hi)[32], int c0) {
             const int col0 = w.n_blk * BN + c0;
             if (col0 >= p.PN) return;   // warp-uniform: padding columns only
-            if (lane == 0) tma_store_wait_read();   // the previous box has left the staging buffer
+            uint8_t* stage_box = stage_boxes + box * (32 * 128);
+            const uint32_t row_base = smem_u32(stage_box) + lane * 128;
+            box ^= 1;
+            if (lane == 0) tma_store_wait_read_1();   // the store issued two boxes ago has left this buffer
             __syncwarp();
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch) {
@@ -812,7 +831,7 @@ void gemm_f16_get_config(int idx, helix_cfg_t* out) {
   out->swap_ab = (idx / kNumTileNs) & 1;
   out->stream_k = (idx / kNumTileNs) >> 1;
   out->raster = 8;
-  out->load_group = 2;
+  out->load_group = 2;   // measured: two issuing warps keep the ring full, more add nothing
 }
 
 static int max_stages(int bn, bool conv) {
@@ -826,11 +845,11 @@ static int max_stages(int bn, bool conv) {
 // time of the slab plus the part of the TMA latency the ring cannot hide at that stage count.
 static double slab_us(int bn) {
   switch (bn) {
-    case 256: return 0.45;
-    case 128: return 0.31;
-    case 64: return 0.27;
-    case 32: return 0.26;
-    default: return 0.25;
+    case 256: return 0.43;
+    case 128: return 0.34;
+    case 64: return 0.33;
+    case 32: return 0.33;
+    default: return 0.33;
   }
 }
 
@@ -847,7 +866,7 @@ static void default_config_impl(int M, int N, int K, int batch, int sm_count, bo
   out->cta_group = 1;
   out->raster = 8;
   out->split_k = 1;
-  out->load_group = 2;
+  out->load_group = 2;   // measured: two issuing warps keep the ring full, more add nothing
   const int num_kb = (K + kBK - 1) / kBK;
   const bool swap = !conv && M <= 64 && N >= 2 * M && N >= 128;
   const int pm = swap ? N : M, pn = swap ? M : N;
@@ -886,7 +905,7 @@ static void default_config_impl(int M, int N, int K, int batch, int sm_count, bo
     // 256 x 192 pair tiles are there for tile counts that quantise badly at 256 x 256
     const int64_t pairs = std::max(1, sm_count / 2);
     const int widths[2] = {256, 192};
-    const double slab[2] = {0.40, 0.365};   // measured: the narrower tile re-reads A from shared memory more often
+    const double slab[2] = {0.36, 0.345};   // measured: the narrower tile re-reads A from shared memory more often
     for (int i = 0; i < 2; ++i) {
       const int bn = widths[i];
       const int64_t pair_tiles = (int64_t)((M + 2 * kBM - 1) / (2 * kBM)) * ((N + bn - 1) / bn) * batch;
@@ -1010,7 +1029,11 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
   const int smax = max_stages(bn, conv);
   p.stages = cfg.stages > 0 ? std::min(cfg.stages, smax) : smax;
   if (p.stages < (conv ? 3 : 2)) return HELIX_ERR_UNSUPPORTED;
-  p.load_group = std::max(1, std::min(cfg.load_group > 0 ? cfg.load_group : 1, p.stages / 2));
+  // Never more issuing warps than ring stages: a warp waits on a stage's "empty" barrier by
+  // parity, which is only meaningful while it is at most one use of that stage ahead of the
+  // consumer; with load_warps <= stages its previous slab guarantees that.
+  p.load_warps = std::max(1, std::min({cfg.load_group > 0 ? cfg.load_group : 2, kGemmProducerWarps,
+                                       p.stages}));
   p.swap = cfg.swap_ab ? 1 : 0;
   p.C = static_cast<__half*>(C);
   p.ldc = ldc;
@@ -1056,6 +1079,15 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
     p.tma_store = 1;
   // a launch that shares its workspace with its neighbours on the stream is never independent of them
   p.independent = (independent && !fixup && !reduce) ? 1 : 0;
+  p.fd_per_batch = make_fastdiv(p.tiles_m * p.tiles_n);
+  p.fd_group = make_fastdiv(p.raster * p.tiles_n);
+  p.fd_raster = make_fastdiv(p.raster);
+  p.fd_split = make_fastdiv(p.split_k);
+  p.fd_num_kb = make_fastdiv(p.num_kb);
+  p.fd_howo = make_fastdiv(p.im2col ? p.g.Ho * p.g.Wo : 1);
+  p.fd_wo = make_fastdiv(p.im2col ? p.g.Wo : 1);
+  p.fd_cblocks = make_fastdiv(p.im2col ? p.g.C / kBK : 1);
+  p.fd_s = make_fastdiv(p.im2col ? p.g.S : 1);
   {
     std::lock_guard<std::mutex> lock(g_trace_mu);
     p.trace = (g_trace_buf && g_trace_bytes >= (size_t)grid * kTraceWords * 8) ? g_trace_buf : nullptr;

@@ -32,8 +32,9 @@ namespace {
 constexpr int kBM = 128;   // rows per CTA; the pair covers 256
 constexpr int kBK = 64;
 constexpr int kATileBytes = kBM * kBK * 2;
-constexpr int kThreads = 32 + 32 + 128;
-constexpr int kStagingBytes = 4 * 32 * 128;
+constexpr int kPairProducerWarps = 3;   // warp 0 and warps 6, 7 issue TMA loads (slab n: issuer n % load_warps)
+constexpr int kThreads = 32 + 32 + 128 + 64;
+constexpr int kStagingBytes = 4 * 2 * 32 * 128;   // two 32-row x 128-byte boxes per epilogue warp
 
 struct Gemm2Params {
   __half* C;
@@ -41,8 +42,10 @@ struct Gemm2Params {
   int PM, PN, K, batch;
   int tiles_m, tiles_n, num_kb, total_tiles;  // tiles_m counts 256-row pair tiles
   int raster, stages;
+  int load_warps;   // issuing warps per CTA, <= stages (see the one-CTA kernel's producer)
   int tma_store, independent;
   int* status;
+  FastDiv fd_per_batch, fd_group, fd_raster;   // reciprocals for the tile decoder
 };
 
 struct Tile2 {
@@ -51,16 +54,14 @@ struct Tile2 {
 
 __device__ __forceinline__ Tile2 decode_tile2(const Gemm2Params& p, int t) {
   Tile2 w;
-  const int per_batch = p.tiles_m * p.tiles_n;
-  w.b = t / per_batch;
-  int r = t - w.b * per_batch;
-  const int group = p.raster * p.tiles_n;
-  const int gid = r / group;
+  int r, gid;
+  fast_divmod(t, p.fd_per_batch, w.b, r);
+  fast_divmod(r, p.fd_group, gid, r);
   const int first_m = gid * p.raster;
   const int gm = min(p.raster, p.tiles_m - first_m);
-  r -= gid * group;
-  w.m_blk = first_m + r % gm;
-  w.n_blk = r / gm;
+  const int q = gm == p.raster ? fast_div(r, p.fd_raster) : r / gm;   // plain division in the last group only
+  w.m_blk = first_m + (r - q * gm);
+  w.n_blk = q;
   return w;
 }
 
@@ -180,15 +181,22 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   if (!p.independent) griddep_wait();
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer (each CTA)
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
+  if (warp == 0 || warp >= 6) {
+    // ------------------------------------------------------------------ TMA producers (each CTA)
+    // Issuer j requests the slabs n = j, j + load_warps, ... of the CTA's slab sequence; slab n
+    // lives in ring stage n % stages.  One thread cannot keep the ring full: a tensor copy holds
+    // its issuing thread for a few hundred cycles.
+    const int issuer = warp == 0 ? 0 : warp - 5;
+    if (lane == 0 && issuer < p.load_warps) {
       bool ok = true;
+      int n_start = 0;
+      int my_n = issuer;     // next slab this issuer requests; stage and use parity follow it
+      int stage = issuer;    // load_warps <= stages
+      uint32_t phase = 0;
       for (int t = pair; t < p.total_tiles && ok; t += num_pairs) {
         const Tile2 w = decode_tile2(p, t);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (; my_n < n_start + p.num_kb; my_n += p.load_warps) {
+          const int kb = my_n - n_start;
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status);
           if (!ok) break;
           if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kStageBytes);
@@ -197,8 +205,10 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                            w.m_blk * 2 * kBM + (int)rank * kBM, w.b);
           tma_load_3d_pair(sB + (size_t)stage * kBHalfBytes, &tmap_b, full_leader, kb * kBK,
                            w.n_blk * BN + (int)rank * (BN / 2), w.b);
-          if (++stage == stages) { stage = 0; phase ^= 1; }
+          stage += p.load_warps;
+          if (stage >= stages) { stage -= stages; phase ^= 1; }
         }
+        n_start += p.num_kb;
       }
     }
   } else if (warp == 1) {
@@ -235,6 +245,7 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     bool ok = true;
     const bool vec_ok = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && ((p.stride_c & 7) == 0);
     int idx = 0;
+    int box = 0;   // staging box in use; alternates over the whole run of the warp, across tiles
     for (int t = pair; t < p.total_tiles && ok; t += num_pairs, ++idx) {
       const Tile2 w = decode_tile2(p, t);
       const int acc = idx & 1;
@@ -245,14 +256,16 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int row0 = w.m_blk * 2 * kBM + (int)rank * kBM + quarter * 32;
       const int row = row0 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
-      uint8_t* stage_box = sC + (size_t)quarter * (32 * 128);
-      const uint32_t row_base = smem_u32(stage_box) + lane * 128;
+      uint8_t* const stage_boxes = sC + (size_t)quarter * (2 * 32 * 128);
       uint32_t ra[32], rb[32], na[32], nb[32];
       auto emit = [&](const uint32_t (&lo)[32], const uint32_t (&hi)[32], int c0) {
         const int col0 = w.n_blk * BN + c0;
         if (col0 >= p.PN || row0 >= p.PM) return;   // warp-uniform: nothing but padding
         if (p.tma_store) {
-          if (lane == 0) tma_store_wait_read();
+          uint8_t* stage_box = stage_boxes + box * (32 * 128);
+          const uint32_t row_base = smem_u32(stage_box) + lane * 128;
+          box ^= 1;
+          if (lane == 0) tma_store_wait_read_1();   // the store issued two boxes ago has left this buffer
           __syncwarp();
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch) {
@@ -430,6 +443,10 @@ int gemm_f16_pair_launch(const helix_cfg_t& cfg, const void* A, int64_t lda, con
   const int smax = gemm_f16_pair_max_stages(bn);
   p.stages = cfg.stages > 0 ? std::min(cfg.stages, smax) : smax;
   if (p.stages < 2) return HELIX_ERR_UNSUPPORTED;
+  p.load_warps = std::max(1, std::min({cfg.load_group > 0 ? cfg.load_group : 2, kPairProducerWarps, p.stages}));
+  p.fd_per_batch = make_fastdiv(p.tiles_m * p.tiles_n);
+  p.fd_group = make_fastdiv(p.raster * p.tiles_n);
+  p.fd_raster = make_fastdiv(p.raster);
   p.independent = independent ? 1 : 0;
   CUtensorMap ta, tb, tc;
   int rc;

@@ -37,7 +37,7 @@ def key_to_cfg(key, conv=False):
         return ops.make_cfg(OP_GEMV_F16, tile_m=1, tile_n=key[2], tile_k=256, split_k=key[5], load_group=key[3])
     stages, tm, bn, group, swap, mode = key
     return ops.make_cfg(OP_CONV_F16 if conv else OP_GEMM_F16, tile_m=tm, tile_n=bn, tile_k=costmodel.TILE_K,
-                        stages=0, cta_group=group, swap_ab=swap, stream_k=mode, load_group=2)
+                        stages=0, cta_group=group, swap_ab=swap, stream_k=mode, load_group=0)
 
 
 def _randn(shape, scale):
@@ -116,7 +116,7 @@ def profile_fp16(fast=False, progress=None):
     tick = progress or (lambda: None)
 
     def cfg(bn, swap=0, mode=0):
-        return ops.make_cfg(OP_GEMM_F16, 128, bn, 64, swap_ab=swap, stream_k=mode, load_group=2)
+        return ops.make_cfg(OP_GEMM_F16, 128, bn, 64, swap_ab=swap, stream_k=mode, load_group=0)
 
     measured = {}
     wide = (256, 64) if fast else (256, 128, 64)

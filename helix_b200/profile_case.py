@@ -40,7 +40,7 @@ def main(argv=None):
             cfg = ops.make_cfg(OP_GEMM_F16, 128, args.bn, 64, cta_group=2)
         elif args.bn:
             cfg = ops.make_cfg(OP_GEMM_F16, 128, args.bn, 64, stream_k=int(args.stream_k), swap_ab=int(args.swap),
-                               load_group=2)
+                               load_group=0)
         for _ in range(args.reps):
             out = ops.gemm_f16(a, b, cfg=cfg)
     elif args.op == "conv":
