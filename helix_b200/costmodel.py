@@ -99,6 +99,14 @@ def gemm_time(prof_dict, key, M, N, K, batch=1, conv=False):
     tiles_m, tiles_n = -(-pm // tm), -(-pn // bn)
     tiles = tiles_m * tiles_n * batch
     nkb = -(-K // TILE_K)
+    if not conv and group == 1 and not swap and mode == 0 and M <= tm and ("skinny_fixed",) in prof_dict:
+        # one row block of A against a long weight matrix: B streams from HBM once, the A box only
+        # carries M rows; bounded by the HBM rate reached with wide boxes or by what one CTA takes in
+        bytes_ = 2.0 * batch * (M * K + N * K + M * N)
+        slab_bytes = (min(M, tm) + bn) * TILE_K * 2.0
+        t_hbm = bytes_ / (_param(prof_dict, "hbm_wide_gbs", 5300.0) * 1e9)
+        t_cta = -(-tiles // sms) * nkb * slab_bytes / (_param(prof_dict, "wide_gbs_per_sm", 400.0) * 1e9)
+        return prof_dict[("skinny_fixed",)] + max(t_hbm, t_cta)
     rounds, tail = divmod(tiles, sms)
     if mode == 0:
         slabs = (rounds + (1 if tail else 0)) * nkb

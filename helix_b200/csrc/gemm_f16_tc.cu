@@ -91,9 +91,6 @@ struct GemmParams {
 // memory may be touched, [3] clock64 and [4] globaltimer at teardown; then for each of the first
 // kTraceTiles work items six clock64 stamps: producer first / last request, MMA issue start / end,
 // epilogue start / end.
-constexpr int kTraceTiles = 20;
-constexpr int kTraceSlabs = 32;   // per-slab stamps of the CTA's first K slabs: request issued, data consumed
-constexpr int kTraceWords = 8 + 6 * kTraceTiles + 2 * kTraceSlabs;
 
 __device__ __forceinline__ void trace_slab(const GemmParams& p, int which, int n) {
   if (p.trace != nullptr && n < kTraceSlabs)
@@ -868,6 +865,33 @@ static void default_config_impl(int M, int N, int K, int batch, int sm_count, bo
   out->split_k = 1;
   out->load_group = 2;   // measured: two issuing warps keep the ring full, more add nothing
   const int num_kb = (K + kBK - 1) / kBK;
+  // One row block of A (M <= 128) against a long weight matrix streams B from HBM once and is
+  // memory bound: the 16 KiB A box only carries M rows (rows beyond M are never fetched), so the
+  // widest tile moves the most bytes per tensor copy.  Measured on 8..128 x 4096..11008 x
+  // 4096..11008: about 5.3 TB/s once enough CTAs stream, 0.4 TB/s per CTA below that, and
+  // neither swap_ab, split-K nor stream-K does better.
+  if (!conv && M <= kBM && N >= 1024 && num_kb >= 8) {
+    const double bytes = 2.0 * batch * ((double)M * K + (double)N * K + (double)M * N);
+    double best_t = 1e30;
+    const int widths[2] = {256, 128};
+    for (int i = 0; i < 2; ++i) {
+      const int bn = widths[i];
+      const int64_t tiles = (int64_t)((N + bn - 1) / bn) * batch;
+      const int64_t rounds = (tiles + sm_count - 1) / sm_count;
+      // HBM time of the whole problem against the time one CTA needs for its own slabs at the
+      // rate a single SM takes boxes in (about 0.4 TB/s with two issuing warps)
+      const double slab_bytes = (double)(std::min(M, kBM) + bn) * kBK * 2;
+      const double t = std::max(bytes / 5.3e6, (double)rounds * num_kb * slab_bytes / 0.4e6) + 2.5;
+      if (t < best_t * 0.97) {   // ties go to the wider tile
+        best_t = t;
+        out->tile_n = bn;
+      }
+    }
+    out->swap_ab = 0;
+    out->stream_k = 0;
+    out->stages = max_stages(out->tile_n, false);
+    return;
+  }
   const bool swap = !conv && M <= 64 && N >= 2 * M && N >= 128;
   const int pm = swap ? N : M, pn = swap ? M : N;
   out->swap_ab = swap ? 1 : 0;
@@ -975,6 +999,10 @@ void gemm_f16_set_trace(void* device_buf, size_t bytes) {
   g_trace_bytes = device_buf ? bytes : 0;
 }
 int gemm_f16_trace_words_per_cta() { return kTraceWords; }
+unsigned long long* gemm_f16_trace_for_grid(int grid) {
+  std::lock_guard<std::mutex> lock(g_trace_mu);
+  return (g_trace_buf && g_trace_bytes >= (size_t)grid * kTraceWords * 8) ? g_trace_buf : nullptr;
+}
 
 template <int BN, bool CONV>
 static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
@@ -1088,10 +1116,7 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
   p.fd_wo = make_fastdiv(p.im2col ? p.g.Wo : 1);
   p.fd_cblocks = make_fastdiv(p.im2col ? p.g.C / kBK : 1);
   p.fd_s = make_fastdiv(p.im2col ? p.g.S : 1);
-  {
-    std::lock_guard<std::mutex> lock(g_trace_mu);
-    p.trace = (g_trace_buf && g_trace_bytes >= (size_t)grid * kTraceWords * 8) ? g_trace_buf : nullptr;
-  }
+  p.trace = gemm_f16_trace_for_grid(grid);
   cudaError_t e = cudaErrorInvalidValue;
 #define HELIX_BN_CASE(BNV)                                                                 \
   case BNV:                                                                                \

@@ -46,7 +46,18 @@ struct Gemm2Params {
   int tma_store, independent;
   int* status;
   FastDiv fd_per_batch, fd_group, fd_raster;   // reciprocals for the tile decoder
+  unsigned long long* trace;                   // optional per-CTA timeline (null = off)
 };
+
+__device__ __forceinline__ void trace2(const Gemm2Params& p, int word) {
+  if (p.trace != nullptr) p.trace[(size_t)blockIdx.x * kTraceWords + word] = (unsigned long long)clock64();
+}
+__device__ __forceinline__ void trace2_tile(const Gemm2Params& p, int idx, int slot) {
+  if (idx < kTraceTiles) trace2(p, 8 + idx * 6 + slot);
+}
+__device__ __forceinline__ void trace2_slab(const Gemm2Params& p, int which, int n) {
+  if (n < kTraceSlabs) trace2(p, 8 + 6 * kTraceTiles + which * kTraceSlabs + n);
+}
 
 struct Tile2 {
   int m_blk, n_blk, b;
@@ -158,6 +169,10 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const int num_pairs = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
+    if (p.trace != nullptr) {
+      p.trace[(size_t)blockIdx.x * kTraceWords + 0] = global_timer_ns();
+      trace2(p, 1);
+    }
     for (int s = 0; s < stages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -180,6 +195,7 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const uint32_t tmem_base = *tmem_ptr_smem;
 
   if (!p.independent) griddep_wait();
+  if (threadIdx.x == 0) trace2(p, 2);
 
   if (warp == 0 || warp >= 6) {
     // ------------------------------------------------------------------ TMA producers (each CTA)
@@ -193,12 +209,15 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int my_n = issuer;     // next slab this issuer requests; stage and use parity follow it
       int stage = issuer;    // load_warps <= stages
       uint32_t phase = 0;
-      for (int t = pair; t < p.total_tiles && ok; t += num_pairs) {
+      int tidx = 0;
+      for (int t = pair; t < p.total_tiles && ok; t += num_pairs, ++tidx) {
         const Tile2 w = decode_tile2(p, t);
+        if (issuer == 0) trace2_tile(p, tidx, 0);
         for (; my_n < n_start + p.num_kb; my_n += p.load_warps) {
           const int kb = my_n - n_start;
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status);
           if (!ok) break;
+          trace2_slab(p, 0, my_n);
           if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kStageBytes);
           const uint32_t full_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
           tma_load_3d_pair(sA + (size_t)stage * kATileBytes, &tmap_a, full_leader, kb * kBK,
@@ -209,6 +228,7 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (stage >= stages) { stage -= stages; phase ^= 1; }
         }
         n_start += p.num_kb;
+        if (issuer == 0) trace2_tile(p, tidx, 1);
       }
     }
   } else if (warp == 1) {
@@ -224,10 +244,12 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         ok = mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status);
         if (!ok) break;
         tc_fence_after_sync();
+        trace2_tile(p, idx, 2);
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status);
           if (!ok) break;
+          trace2_slab(p, 1, idx * p.num_kb + kb);
           tc_fence_after_sync();
           const uint64_t da = umma_desc_sw128(smem_u32(sA + (size_t)stage * kATileBytes));
           const uint64_t db = umma_desc_sw128(smem_u32(sB + (size_t)stage * kBHalfBytes));
@@ -237,6 +259,7 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (++stage == stages) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit_pair(&tmem_full[acc]);
+        trace2_tile(p, idx, 3);
       }
     }
   } else {
@@ -253,6 +276,7 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       ok = mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status);
       if (!ok) break;
       tc_fence_after_sync();
+      if (quarter == 0 && lane == 0) trace2_tile(p, idx, 4);
       const int row0 = w.m_blk * 2 * kBM + (int)rank * kBM + quarter * 32;
       const int row = row0 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
@@ -331,6 +355,7 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
+      if (quarter == 0 && lane == 0) trace2_tile(p, idx, 5);
     }
     if (p.tma_store && lane == 0) tma_store_wait_all();
   }
@@ -339,6 +364,10 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   tc_fence_before_sync();
   __syncthreads();
   cluster_sync_all();   // nothing of the pair still refers to this CTA's barriers or shared memory
+  if (threadIdx.x == 0 && p.trace != nullptr) {
+    trace2(p, 3);
+    p.trace[(size_t)blockIdx.x * kTraceWords + 4] = global_timer_ns();
+  }
   if (warp == 1) {
     __syncwarp();
     tc_fence_after_sync();
@@ -447,6 +476,7 @@ int gemm_f16_pair_launch(const helix_cfg_t& cfg, const void* A, int64_t lda, con
   p.fd_per_batch = make_fastdiv(p.tiles_m * p.tiles_n);
   p.fd_group = make_fastdiv(p.raster * p.tiles_n);
   p.fd_raster = make_fastdiv(p.raster);
+  p.trace = gemm_f16_trace_for_grid(2 * (int)std::min<int64_t>(tiles, sm_count / 2));
   p.independent = independent ? 1 : 0;
   CUtensorMap ta, tb, tc;
   int rc;

@@ -37,8 +37,13 @@ void gemm_f16_get_config(int idx, helix_cfg_t* out);
 // Fills *out with the library's default choice for the problem.
 void gemm_f16_default_config(int M, int N, int K, int batch, int sm_count, bool conv, helix_cfg_t* out);
 void conv_f16_default_config(const ConvGeom& g, int sm_count, helix_cfg_t* out);
+// Per-CTA timeline capture shared by the one-CTA and the CTA-pair kernel (layout: helix_b200.h).
+constexpr int kTraceTiles = 20;   // work items with six stamps each
+constexpr int kTraceSlabs = 32;   // first K slabs of the CTA: request issued, data consumed
+constexpr int kTraceWords = 8 + 6 * kTraceTiles + 2 * kTraceSlabs;
 void gemm_f16_set_trace(void* device_buf, size_t bytes);
 int gemm_f16_trace_words_per_cta();
+unsigned long long* gemm_f16_trace_for_grid(int grid);   // the capture buffer if one is set and large enough
 size_t gemm_f16_workspace_bytes(const helix_cfg_t* cfg, int M, int N, int K, int batch, int sm_count);
 int gemm_f16_launch(const helix_cfg_t* cfg, const void* A, int64_t lda, const void* B, int64_t ldb, void* C,
                     int64_t ldc, int M, int N, int K, int batch, int64_t sa, int64_t sb, int64_t sc, void* ws,

@@ -138,6 +138,17 @@ def profile_fp16(fast=False, progress=None):
         t1 = time_gemm_f16(4096, 4096, 512, pair_cfg); tick()
         t2 = time_gemm_f16(4096, 4096, 4096, pair_cfg); tick()
         d[pkey] = tuple(float(v) for v in _two_point(t1, pair_waves * 8, t2, pair_waves * 64))
+    # one row block of A against a long B with the widest tile: what a single CTA takes in (16 CTAs,
+    # two K values) and the HBM rate with every SM streaming
+    t1 = time_gemm_f16(8, 4096, 2048, cfg(256)); tick()
+    t2 = time_gemm_f16(8, 4096, 8192, cfg(256)); tick()
+    slab_bytes = (8 + 256) * 64 * 2.0
+    d[("wide_gbs_per_sm",)] = float((8192 - 2048) / 64 * slab_bytes / max(t2 - t1, 1e-9) / 1e9)
+    per_byte = max(t2 - t1, 1e-9) / (2.0 * 4096 * (8192 - 2048))
+    d[("skinny_fixed",)] = float(max(t1 - 2.0 * 4096 * 2048 * per_byte, 0.0))
+    t = time_gemm_f16(16, 256 * sms, 4096, cfg(256)); tick()
+    d[("hbm_wide_gbs",)] = float(2.0 * (16 * 4096 + 256 * sms * 4096 + 16 * 256 * sms) /
+                                  max(t - d[("skinny_fixed",)], 1e-9) / 1e9)
     skinny = {}
     for bn in ((16,) if fast else (32, 16)):          # skinny M on the UMMA N axis: everything streams from DRAM
         N = 128 * sms
