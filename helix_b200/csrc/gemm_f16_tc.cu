@@ -975,6 +975,7 @@ static void streamk_plan(int64_t tiles, int num_kb, int grid, int* dp_rounds, in
 
 size_t gemm_f16_workspace_bytes(const helix_cfg_t* cfg, int M, int N, int K, int batch, int sm_count) {
   if (!cfg) return 0;
+  if (cfg->cta_group == 2) return gemm_f16_pair_workspace_bytes(*cfg, M, N, K, batch, sm_count);
   if (cfg->stream_k) {
     const int bn = cfg->tile_n;
     const int pm = cfg->swap_ab ? N : M, pn = cfg->swap_ab ? M : N;
@@ -1173,8 +1174,8 @@ int gemm_f16_launch(const helix_cfg_t* cfg_in, const void* A, int64_t lda, const
     if (!ws || ws_bytes < gemm_f16_workspace_bytes(&cfg, M, N, K, batch, sm_count)) cfg.stream_k = 0;
   }
   if (cfg.cta_group == 2)   // CTA pairs sharing a 256 x BN tile: its own kernel
-    return gemm_f16_pair_launch(cfg, A, lda, B, ldb, C, ldc, M, N, K, batch, sa, sb, sc, status_dev, sm_count,
-                                independent, stream, launches);
+    return gemm_f16_pair_launch(cfg, A, lda, B, ldb, C, ldc, M, N, K, batch, sa, sb, sc, ws, ws_bytes, status_dev,
+                                sm_count, independent, stream, launches);
   if (cfg.tile_m != kBM || cfg.cta_group > 2) return HELIX_ERR_UNSUPPORTED;
   const bool swap = cfg.swap_ab != 0;
   GemmParams p{};

@@ -45,8 +45,19 @@ struct Gemm2Params {
   int load_warps;   // issuing warps per CTA, <= stages (see the one-CTA kernel's producer)
   int tma_store, independent;
   int* status;
-  FastDiv fd_per_batch, fd_group, fd_raster;   // reciprocals for the tile decoder
+  FastDiv fd_per_batch, fd_group, fd_raster, fd_num_kb;   // reciprocals for the tile decoder
   unsigned long long* trace;                   // optional per-CTA timeline (null = off)
+  // stream-K schedule: dp_rounds whole tiles per pair, then the K slabs of the sk_tiles remaining
+  // tiles dealt out in ranges of sk_upc slabs (<= num_kb, so a range touches at most two tiles);
+  // a pair that computes only part of a tile leaves its fp32 accumulator in a slot of `partial`
+  // ([2 * pairs][256][BN]) and a fix-up kernel adds the slots of each such tile in pair order.
+  int stream_k, dp_rounds, sk_tiles, sk_upc;
+  float* partial;
+};
+
+struct Item2 {
+  int tile, kb0, kb1;
+  int slot;   // < 0: the whole K range, result goes straight to C
 };
 
 __device__ __forceinline__ void trace2(const Gemm2Params& p, int word) {
@@ -74,6 +85,34 @@ __device__ __forceinline__ Tile2 decode_tile2(const Gemm2Params& p, int t) {
   w.m_blk = first_m + (r - q * gm);
   w.n_blk = q;
   return w;
+}
+
+// The idx-th work item of a pair; every role of both CTAs walks the same sequence.
+__device__ __forceinline__ bool get_item2(const Gemm2Params& p, int pair, int num_pairs, int idx, Item2& it) {
+  if (!p.stream_k || idx < p.dp_rounds) {
+    it.tile = pair + idx * num_pairs;
+    it.kb0 = 0;
+    it.kb1 = p.num_kb;
+    it.slot = -1;
+    return p.stream_k || it.tile < p.total_tiles;
+  }
+  const int s = idx - p.dp_rounds;   // first / second tile the pair's slab range touches
+  if (s > 1) return false;
+  const int sk_units = p.sk_tiles * p.num_kb;
+  const int u0 = min(sk_units, pair * p.sk_upc);
+  const int u1 = min(sk_units, u0 + p.sk_upc);
+  if (u0 >= u1) return false;
+  const int j0 = fast_div(u0, p.fd_num_kb);
+  const int split = min(u1, (j0 + 1) * p.num_kb);
+  int j, a, b;
+  if (s == 0) { j = j0; a = u0; b = split; }
+  else { j = j0 + 1; a = split; b = u1; }
+  if (a >= b) return false;
+  it.tile = p.dp_rounds * num_pairs + j;
+  it.kb0 = a - j * p.num_kb;
+  it.kb1 = b - j * p.num_kb;
+  it.slot = (it.kb0 == 0 && it.kb1 == p.num_kb) ? -1 : 2 * pair + s;
+  return true;
 }
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -209,12 +248,13 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int my_n = issuer;     // next slab this issuer requests; stage and use parity follow it
       int stage = issuer;    // load_warps <= stages
       uint32_t phase = 0;
-      int tidx = 0;
-      for (int t = pair; t < p.total_tiles && ok; t += num_pairs, ++tidx) {
-        const Tile2 w = decode_tile2(p, t);
+      Item2 it;
+      for (int tidx = 0; ok && get_item2(p, pair, num_pairs, tidx, it); ++tidx) {
+        const Tile2 w = decode_tile2(p, it.tile);
+        const int nkb = it.kb1 - it.kb0;
         if (issuer == 0) trace2_tile(p, tidx, 0);
-        for (; my_n < n_start + p.num_kb; my_n += p.load_warps) {
-          const int kb = my_n - n_start;
+        for (; my_n < n_start + nkb; my_n += p.load_warps) {
+          const int kb = it.kb0 + (my_n - n_start);
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status);
           if (!ok) break;
           trace2_slab(p, 0, my_n);
@@ -227,7 +267,7 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           stage += p.load_warps;
           if (stage >= stages) { stage -= stages; phase ^= 1; }
         }
-        n_start += p.num_kb;
+        n_start += nkb;
         if (issuer == 0) trace2_tile(p, tidx, 1);
       }
     }
@@ -237,8 +277,9 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      int idx = 0;
-      for (int t = pair; t < p.total_tiles && ok; t += num_pairs, ++idx) {
+      int nslab = 0;
+      Item2 it;
+      for (int idx = 0; ok && get_item2(p, pair, num_pairs, idx, it); ++idx) {
         const int acc = idx & 1;
         const uint32_t acc_phase = (idx >> 1) & 1;
         ok = mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status);
@@ -246,15 +287,16 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         tc_fence_after_sync();
         trace2_tile(p, idx, 2);
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = it.kb0; kb < it.kb1; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status);
           if (!ok) break;
-          trace2_slab(p, 1, idx * p.num_kb + kb);
+          trace2_slab(p, 1, nslab++);
           tc_fence_after_sync();
           const uint64_t da = umma_desc_sw128(smem_u32(sA + (size_t)stage * kATileBytes));
           const uint64_t db = umma_desc_sw128(smem_u32(sB + (size_t)stage * kBHalfBytes));
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) umma_f16_ss_pair(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kb > 0) || (k > 0));
+          for (int k = 0; k < kBK / 16; ++k)
+            umma_f16_ss_pair(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kb > it.kb0) || (k > 0));
           umma_commit_pair(&empty_bar[stage]);
           if (++stage == stages) { stage = 0; phase ^= 1; }
         }
@@ -267,10 +309,10 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int quarter = warp & 3;
     bool ok = true;
     const bool vec_ok = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && ((p.stride_c & 7) == 0);
-    int idx = 0;
     int box = 0;   // staging box in use; alternates over the whole run of the warp, across tiles
-    for (int t = pair; t < p.total_tiles && ok; t += num_pairs, ++idx) {
-      const Tile2 w = decode_tile2(p, t);
+    Item2 it;
+    for (int idx = 0; ok && get_item2(p, pair, num_pairs, idx, it); ++idx) {
+      const Tile2 w = decode_tile2(p, it.tile);
       const int acc = idx & 1;
       const uint32_t acc_phase = (idx >> 1) & 1;
       ok = mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status);
@@ -280,6 +322,25 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int row0 = w.m_blk * 2 * kBM + (int)rank * kBM + quarter * 32;
       const int row = row0 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      if (it.slot >= 0) {
+        // part of a tile's K range: the fp32 accumulator (padding included) goes to this pair's slot
+        float* dst = p.partial + ((size_t)it.slot * (2 * kBM) + rank * kBM + quarter * 32 + lane) * BN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int jj = 0; jj < 32; jj += 4)
+            *reinterpret_cast<float4*>(dst + c0 + jj) = make_float4(__uint_as_float(r[jj]), __uint_as_float(r[jj + 1]),
+                                                                    __uint_as_float(r[jj + 2]), __uint_as_float(r[jj + 3]));
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
+        if (quarter == 0 && lane == 0) trace2_tile(p, idx, 5);
+        continue;
+      }
       uint8_t* const stage_boxes = sC + (size_t)quarter * (2 * 32 * 128);
       uint32_t ra[32], rb[32], na[32], nb[32];
       auto emit = [&](const uint32_t (&lo)[32], const uint32_t (&hi)[32], int c0) {
@@ -375,6 +436,43 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   }
 }
 
+// Stream-K fix-up for pair tiles: a dealt-out tile whose K slabs were shared by several pairs is the
+// sum of their fp32 slots, added in pair order (deterministic) and rounded once.  Grid: (blocks per
+// tile, dealt-out tiles); one thread per four consecutive columns of a tile row.
+__global__ void gemm2_streamk_fixup_kernel(const Gemm2Params p, int bn, int num_pairs) {
+  const int j = blockIdx.y;
+  const int u_lo = j * p.num_kb, u_hi = (j + 1) * p.num_kb;
+  const int c_lo = u_lo / p.sk_upc, c_hi = (u_hi - 1) / p.sk_upc;
+  if (c_lo == c_hi) return;   // computed whole by one pair and already stored
+  const int quad = blockIdx.x * blockDim.x + threadIdx.x;
+  const int quads_per_row = bn >> 2;
+  if (quad >= 2 * kBM * quads_per_row) return;
+  const int trow = quad / quads_per_row, tcol = (quad - trow * quads_per_row) << 2;
+  const Tile2 w = decode_tile2(p, p.dp_rounds * num_pairs + j);
+  const int row = w.m_blk * 2 * kBM + trow, col = w.n_blk * bn + tcol;
+  if (row >= p.PM || col >= p.PN) return;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c = c_lo; c <= c_hi; ++c) {
+    const int first_tile = (c * p.sk_upc) / p.num_kb;
+    const int slot = 2 * c + (j == first_tile ? 0 : 1);
+    const float4 v = *reinterpret_cast<const float4*>(p.partial + ((size_t)slot * (2 * kBM) + trow) * bn + tcol);
+    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+  }
+  const float vals[4] = {s.x, s.y, s.z, s.w};
+  __half* dst = p.C + (int64_t)w.b * p.stride_c + (int64_t)row * p.ldc + col;
+  if (col + 3 < p.PN && (p.ldc & 3) == 0 && (p.stride_c & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 7) == 0) {
+    __half2 h0 = __floats2half2_rn(vals[0], vals[1]);
+    __half2 h1 = __floats2half2_rn(vals[2], vals[3]);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&h0);
+    pk.y = *reinterpret_cast<uint32_t*>(&h1);
+    *reinterpret_cast<uint2*>(dst) = pk;
+  } else {
+    for (int q = 0; q < 4; ++q)
+      if (col + q < p.PN) dst[q] = __float2half_rn(vals[q]);
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -450,13 +548,25 @@ int gemm_f16_pair_max_stages(int bn) {
   return std::min(8, budget / (kATileBytes + (bn / 2) * kBK * 2));
 }
 
-// cta_group = 2 configurations: whole 256 x BN tiles round-robin over CTA pairs.
+// Workspace of the stream-K schedule on CTA pairs: two fp32 slots of 256 x BN per pair.
+size_t gemm_f16_pair_workspace_bytes(const helix_cfg_t& cfg, int M, int N, int K, int batch, int sm_count) {
+  if (!cfg.stream_k) return 0;
+  const int bn = cfg.tile_n;
+  const int64_t tiles = (int64_t)((M + 2 * kBM - 1) / (2 * kBM)) * ((N + bn - 1) / bn) * std::max(batch, 1);
+  const int pairs = std::max(1, sm_count / 2);
+  if (tiles % pairs == 0 || (K + kBK - 1) / kBK < 2) return 0;
+  return (size_t)2 * pairs * 2 * kBM * bn * sizeof(float);
+}
+
+// cta_group = 2 configurations: 256 x BN tiles round-robin over CTA pairs; with stream_k the K
+// slabs of the tiles beyond the last whole round are dealt evenly to all pairs.
 int gemm_f16_pair_launch(const helix_cfg_t& cfg, const void* A, int64_t lda, const void* B, int64_t ldb, void* C,
-                         int64_t ldc, int M, int N, int K, int batch, int64_t sa, int64_t sb, int64_t sc,
-                         int* status_dev, int sm_count, bool independent, cudaStream_t stream, int64_t* launches) {
+                         int64_t ldc, int M, int N, int K, int batch, int64_t sa, int64_t sb, int64_t sc, void* ws,
+                         size_t ws_bytes, int* status_dev, int sm_count, bool independent, cudaStream_t stream,
+                         int64_t* launches) {
   const int bn = cfg.tile_n;
   if (bn != 256 && bn != 192 && bn != 128) return HELIX_ERR_UNSUPPORTED;
-  if (cfg.swap_ab || cfg.stream_k || cfg.split_k > 1) return HELIX_ERR_UNSUPPORTED;
+  if (cfg.swap_ab || cfg.split_k > 1) return HELIX_ERR_UNSUPPORTED;
   Gemm2Params p{};
   p.PM = M; p.PN = N; p.K = K; p.batch = batch;
   p.C = static_cast<__half*>(C);
@@ -476,8 +586,26 @@ int gemm_f16_pair_launch(const helix_cfg_t& cfg, const void* A, int64_t lda, con
   p.fd_per_batch = make_fastdiv(p.tiles_m * p.tiles_n);
   p.fd_group = make_fastdiv(p.raster * p.tiles_n);
   p.fd_raster = make_fastdiv(p.raster);
-  p.trace = gemm_f16_trace_for_grid(2 * (int)std::min<int64_t>(tiles, sm_count / 2));
-  p.independent = independent ? 1 : 0;
+  p.fd_num_kb = make_fastdiv(p.num_kb);
+  int pairs = (int)std::min<int64_t>(tiles, sm_count / 2);
+  bool fixup = false;
+  if (cfg.stream_k && p.num_kb >= 2 && sm_count >= 2 && tiles % (sm_count / 2) != 0) {
+    pairs = sm_count / 2;
+    p.stream_k = 1;
+    p.dp_rounds = (int)(tiles / pairs);
+    p.sk_tiles = (int)(tiles - (int64_t)p.dp_rounds * pairs);
+    const int64_t units = (int64_t)p.sk_tiles * p.num_kb;
+    int upc = (int)((units + pairs - 1) / pairs);
+    upc = std::max(upc, std::min(4, p.num_kb));   // no slivers; still <= num_kb because sk_tiles < pairs
+    p.sk_upc = std::max(1, upc);
+    const size_t need = (size_t)2 * pairs * 2 * kBM * bn * sizeof(float);
+    if (!ws || ws_bytes < need) return HELIX_ERR_WORKSPACE;
+    p.partial = static_cast<float*>(ws);
+    fixup = true;
+  }
+  p.trace = gemm_f16_trace_for_grid(2 * pairs);
+  // a launch that shares its workspace with its neighbours on the stream is never independent of them
+  p.independent = (independent && !fixup) ? 1 : 0;
   CUtensorMap ta, tb, tc;
   int rc;
   if ((rc = make_map(&ta, A, K, M, batch, lda, sa, kBM)) != HELIX_OK) return rc;
@@ -487,13 +615,18 @@ int gemm_f16_pair_launch(const helix_cfg_t& cfg, const void* A, int64_t lda, con
   if ((ldc & 7) == 0 && (sc & 7) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
       make_map(&tc, C, N, M, batch, ldc, sc, 32) == HELIX_OK)
     p.tma_store = 1;
-  const int pairs = (int)std::min<int64_t>(tiles, sm_count / 2);
   const size_t smem = 1024 + (size_t)p.stages * (kATileBytes + (bn / 2) * kBK * 2) + kStagingBytes + 256;
   const cudaError_t e = bn == 256   ? launch_pair<256>(ta, tb, tc, p, 2 * pairs, smem, stream)
                         : bn == 192 ? launch_pair<192>(ta, tb, tc, p, 2 * pairs, smem, stream)
                                     : launch_pair<128>(ta, tb, tc, p, 2 * pairs, smem, stream);
   if (e != cudaSuccess) return HELIX_ERR_CUDA;
   ++*launches;
+  if (fixup) {
+    const dim3 fgrid((2 * kBM * (bn >> 2) + 255) / 256, p.sk_tiles);
+    gemm2_streamk_fixup_kernel<<<fgrid, 256, 0, stream>>>(p, bn, pairs);
+    if (cudaGetLastError() != cudaSuccess) return HELIX_ERR_CUDA;
+    ++*launches;
+  }
   return HELIX_OK;
 }
 

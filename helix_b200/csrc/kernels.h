@@ -51,9 +51,11 @@ int gemm_f16_launch(const helix_cfg_t* cfg, const void* A, int64_t lda, const vo
                     int64_t* launches);
 // ---- gemm_f16_tc2.cu (CTA pairs, tcgen05.mma.cta_group::2)
 int gemm_f16_pair_max_stages(int bn);
+size_t gemm_f16_pair_workspace_bytes(const helix_cfg_t& cfg, int M, int N, int K, int batch, int sm_count);
 int gemm_f16_pair_launch(const helix_cfg_t& cfg, const void* A, int64_t lda, const void* B, int64_t ldb, void* C,
-                         int64_t ldc, int M, int N, int K, int batch, int64_t sa, int64_t sb, int64_t sc,
-                         int* status_dev, int sm_count, bool independent, cudaStream_t stream, int64_t* launches);
+                         int64_t ldc, int M, int N, int K, int batch, int64_t sa, int64_t sb, int64_t sc, void* ws,
+                         size_t ws_bytes, int* status_dev, int sm_count, bool independent, cudaStream_t stream,
+                         int64_t* launches);
 int conv_f16_launch(const helix_cfg_t* cfg, const void* x, const void* w, void* y, const ConvGeom& g, void* ws,
                     size_t ws_bytes, int* status_dev, int sm_count, bool independent, cudaStream_t stream,
                     int64_t* launches);

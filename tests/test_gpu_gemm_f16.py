@@ -237,6 +237,25 @@ def test_gemm_cta_pairs(oracle, bn, shape):
     util.assert_f16_close(got, ref32, f"CTA pairs {shape} bn={bn}")
 
 
+@pytest.mark.parametrize("bn,shape", [
+    (256, (1024, 768, 512)),      # 12 tiles on 74 pairs: every tile is shared by two pairs
+    (256, (256, 1280, 832)),      # 13 slabs per tile, ranges of 4: ranges straddle two tiles
+    (192, (2304, 2112, 256)),     # one whole round plus dealt-out tiles that each stay with one pair
+    (256, (2560, 2048, 1024)),    # 80 tiles: one round, six tiles dealt out over all pairs
+    (128, (300, 520, 264)),       # ragged M, N, K
+])
+def test_gemm_cta_pairs_stream_k(oracle, bn, shape):
+    """CTA pairs with the K slabs of the last partial round dealt to all pairs (fp32 slots + fix-up)."""
+    M, N, K = shape
+    a, b = datagen.c3_gemm(M, N, K, seed=17)
+    cfg = ops.make_cfg(OP_GEMM_F16, tile_m=128, tile_n=bn, tile_k=64, cta_group=2, stream_k=1)
+    got = _run(a, b, cfg)
+    _, ref32 = oracle.hgemm_fast(a, b)
+    util.assert_f16_close(got, ref32, f"CTA pairs stream-K {shape} bn={bn}")
+    again = _run(a, b, cfg)
+    assert np.array_equal(got, again)            # fixed summation order: bit-reproducible
+
+
 def test_gemm_cta_pairs_known_answer_and_batch(oracle):
     K = 128
     a = np.zeros((256, K), np.float16)
