@@ -80,11 +80,12 @@ typedef struct helix_cfg {
   int raster;    /* M-blocks per rasterisation group (L2 reuse), 0 = default         */
   int thread_m;  /* GEMM_F32: per-thread register block rows                         */
   int thread_n;  /* GEMM_F32: per-thread register block cols                         */
-  int load_group;/* GEMM_F16: K slabs requested back to back by the TMA producer (0 = 1);
+  int load_group;/* GEMM_F16/CONV: warps per CTA that issue TMA loads, consecutive K slabs going to
+                    different warps (0 = 2; at most 4, 3 for CTA pairs, never more than stages);
                     GEMV_F16: 16-byte loads in flight per thread and row (0 = default)  */
   int stream_k;  /* GEMM_F16/CONV: 1 = whole waves of tiles round-robin, the K slabs of the
-                    remaining tiles dealt evenly to all CTAs (needs a workspace); overrides
-                    split_k                                                              */
+                    remaining tiles dealt evenly to all CTAs or CTA pairs (needs a workspace);
+                    overrides split_k                                                    */
   int conv_gather; /* CONV_F16: 0 = activations arrive through an im2col tensor map wherever the
                       geometry allows it (C a multiple of 64, tensor of 128 KiB or more);
                       1 = always use the gathering (cp.async) producer warps               */
@@ -208,13 +209,15 @@ int helix_conv2d_f16_nhwc_host(const void* x, const void* w, void* y, int N, int
 int helix_gemv_f16_static(const void* W, int64_t ldw, const void* X, int64_t ldx, void* Y, int64_t ldy,
                           int64_t ldy_inner, int rows, int K, int m, int split_k, void* stream);
 
-/* Timeline capture for tuning the one-CTA fp16 GEMM / convolution kernel (the reference has only
- * whole-kernel cudaEvent times, gemm.cu:622-660).  While a device buffer is set, each such launch
- * whose grid fits writes helix_trace_words_per_cta() 64-bit words per CTA into it: [0] globaltimer
- * and [1] clock64 at CTA start, [2] clock64 when global memory may first be touched, [3] clock64
- * and [4] globaltimer at teardown, then from word 8 on, for each of the first 20 work items of the
- * CTA, six clock64 stamps: first / last load request, MMA issue start / end, epilogue start / end.
- * Later launches overwrite earlier ones.  Pass NULL to switch capture off (the default). */
+/* Timeline capture for tuning the fp16 GEMM / convolution kernels, one-CTA and CTA-pair (the
+ * reference has only whole-kernel cudaEvent times, gemm.cu:622-660).  While a device buffer is
+ * set, each such launch whose grid fits writes helix_trace_words_per_cta() 64-bit words per CTA
+ * into it: [0] globaltimer and [1] clock64 at CTA start, [2] clock64 when global memory may first
+ * be touched, [3] clock64 and [4] globaltimer at teardown; from word 8 on, for each of the first
+ * 20 work items of the CTA, six clock64 stamps: first / last load request, MMA issue start / end,
+ * epilogue start / end; then, for the CTA's first 32 K slabs, the clock64 at which each was
+ * requested (32 words) and at which the MMA issuer found it loaded (32 words).  Later launches
+ * overwrite earlier ones.  Pass NULL to switch capture off (the default). */
 int helix_trace_buffer(void* device_buf, size_t bytes);
 int helix_trace_words_per_cta(void);
 
