@@ -340,19 +340,18 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           base_off[it] = 0;
           inside[it] = 0;
           if (m < p.PM) {
-            const int n_img = m / HoWo;
-            const int rem = m - n_img * HoWo;
-            const int ho = rem / p.g.Wo;
-            const int wo = rem - ho * p.g.Wo;
+            int n_img, rem, ho, wo;
+            fast_divmod(m, p.fd_howo, n_img, rem);
+            fast_divmod(rem, p.fd_wo, ho, wo);
             const int hi0 = ho * p.g.stride - p.g.pad;
             const int wi0 = wo * p.g.stride - p.g.pad;
             base_off[it] = ((int64_t)n_img * p.g.H + hi0) * p.g.W * p.g.C + (int64_t)wi0 * p.g.C;
-            uint32_t bits = 0;
-            for (int r = 0; r < p.g.R; ++r)
-              if (hi0 + r >= 0 && hi0 + r < p.g.H) bits |= 1u << r;
-            for (int s = 0; s < p.g.S; ++s)
-              if (wi0 + s >= 0 && wi0 + s < p.g.W) bits |= 1u << (16 + s);
-            inside[it] = bits;
+            // filter rows [r_lo, r_hi) and columns [s_lo, s_hi) fall inside the image (R, S <= 15)
+            const int r_lo = max(0, -hi0), r_hi = min(p.g.R, p.g.H - hi0);
+            const int s_lo = max(0, -wi0), s_hi = min(p.g.S, p.g.W - wi0);
+            const uint32_t rbits = r_hi > r_lo ? ((1u << r_hi) - 1u) & ~((1u << r_lo) - 1u) : 0u;
+            const uint32_t sbits = s_hi > s_lo ? ((1u << s_hi) - 1u) & ~((1u << s_lo) - 1u) : 0u;
+            inside[it] = rbits | (sbits << 16);
           }
         }
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
@@ -1113,8 +1112,8 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
   p.fd_raster = make_fastdiv(p.raster);
   p.fd_split = make_fastdiv(p.split_k);
   p.fd_num_kb = make_fastdiv(p.num_kb);
-  p.fd_howo = make_fastdiv(p.im2col ? p.g.Ho * p.g.Wo : 1);
-  p.fd_wo = make_fastdiv(p.im2col ? p.g.Wo : 1);
+  p.fd_howo = make_fastdiv((conv || p.im2col) ? p.g.Ho * p.g.Wo : 1);
+  p.fd_wo = make_fastdiv((conv || p.im2col) ? p.g.Wo : 1);
   p.fd_cblocks = make_fastdiv(p.im2col ? p.g.C / kBK : 1);
   p.fd_s = make_fastdiv(p.im2col ? p.g.S : 1);
   p.trace = gemm_f16_trace_for_grid(grid);

@@ -52,6 +52,7 @@ sgemm_f32_kernel(const float* __restrict__ A, int64_t lda, const float* __restri
     for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
 
   float4 ra[A4], rb[B4];
+  auto a_swz = [](int kk) { return ((kk >> 2) & 3) << 2; };   // column XOR of sA row kk (multiple of 4)
 
   // ---- global -> registers for slab starting at k0 (zero fill outside the matrix)
   auto load_global = [&](int k0) {
@@ -116,13 +117,17 @@ sgemm_f32_kernel(const float* __restrict__ A, int64_t lda, const float* __restri
       const int f = (v * NT + tid);
       if (TRANS_A) {
         const int kk = f / (BM / 4), mm = (f % (BM / 4)) * 4;
-        *reinterpret_cast<float4*>(&sA[buf][kk][mm]) = ra[v];
+        *reinterpret_cast<float4*>(&sA[buf][kk][mm ^ a_swz(kk)]) = ra[v];
       } else {
+        // the four k values of a float4 go to four rows; rows kk, kk+4, kk+8, kk+12 of one warp's
+        // stores would share banks pairwise, so the column is XOR-ed with a multiple of 4 that
+        // depends on kk / 4 (whole float4 groups move, the later float4 reads stay aligned)
         const int mm = f / (BK / 4), kk = (f % (BK / 4)) * 4;
-        sA[buf][kk + 0][mm] = ra[v].x;
-        sA[buf][kk + 1][mm] = ra[v].y;
-        sA[buf][kk + 2][mm] = ra[v].z;
-        sA[buf][kk + 3][mm] = ra[v].w;
+        const int col = mm ^ a_swz(kk);
+        sA[buf][kk + 0][col] = ra[v].x;
+        sA[buf][kk + 1][col] = ra[v].y;
+        sA[buf][kk + 2][col] = ra[v].z;
+        sA[buf][kk + 3][col] = ra[v].w;
       }
     }
 #pragma unroll
@@ -148,7 +153,7 @@ sgemm_f32_kernel(const float* __restrict__ A, int64_t lda, const float* __restri
       float av[TM], bv[TN];
 #pragma unroll
       for (int q = 0; q < TM / 4; ++q) {
-        const float4 t = *reinterpret_cast<const float4*>(&sA[buf][kk][(q * T::kThreadsM + tm) * 4]);
+        const float4 t = *reinterpret_cast<const float4*>(&sA[buf][kk][((q * T::kThreadsM + tm) * 4) ^ a_swz(kk)]);
         av[q * 4 + 0] = t.x; av[q * 4 + 1] = t.y; av[q * 4 + 2] = t.z; av[q * 4 + 3] = t.w;
       }
 #pragma unroll
