@@ -236,9 +236,9 @@ def extras(peaks):
 #   python bench.py --steps 1 --warmup 3 --no-extras
 # Filled in below only for the kernels that capture listed; the others report null.
 SWEEP_DRAM_BYTES_PER_LAUNCH = {
-    "gemm_f16_tc2_kernel<256>": 15781729, "gemm_f16_tc2_kernel<192>": 34548875,
-    "gemm_f16_tc_kernel<256,0>": 33245932, "gemm_f16_tc_kernel<64,0>": 88540024,
-    "gemm_f16_tc_kernel<128,0>": 21824768,
+    "gemm_f16_tc2_kernel<256>": 15810162, "gemm_f16_tc2_kernel<192>": 34526677,
+    "gemm_f16_tc_kernel<256,0>": 30764491, "gemm_f16_tc_kernel<64,0>": 68126530,
+    "gemm_f16_tc_kernel<128,0>": 14688633, "gemm_f16_tc_kernel<64,1>": 26433792,
 }
 
 

@@ -93,7 +93,7 @@ def gemm_time(prof_dict, key, M, N, K, batch=1, conv=False):
     sms = _param(prof_dict, "sm_count", DEFAULT_SMS)
     pm, pn = (N, M) if swap else (M, N)
     if group == 2:
-        if conv or swap or mode or pm <= tm:
+        if conv or swap or mode or pm <= tm or K < 8 * TILE_K:   # short K is epilogue bound: pairs gain nothing
             return float("inf")
         tm, sms = 2 * tm, sms // 2      # a pair of SMs is one scheduling slot for a 256-row tile
     tiles_m, tiles_n = -(-pm // tm), -(-pn // bn)
@@ -104,9 +104,14 @@ def gemm_time(prof_dict, key, M, N, K, batch=1, conv=False):
         # carries M rows; bounded by the HBM rate reached with wide boxes or by what one CTA takes in
         bytes_ = 2.0 * batch * (M * K + N * K + M * N)
         slab_bytes = (min(M, tm) + bn) * TILE_K * 2.0
-        t_hbm = bytes_ / (_param(prof_dict, "hbm_wide_gbs", 5300.0) * 1e9)
+        # the HBM rate grows a little with the number of streaming CTAs (measured 4.6 TB/s with 16..43, 5.6 with 148)
+        hbm = _param(prof_dict, "hbm_wide_gbs", 5300.0) * 1e9 * (0.8 + 0.2 * min(tiles, sms) / sms)
+        t_hbm = bytes_ / hbm
         t_cta = -(-tiles // sms) * nkb * slab_bytes / (_param(prof_dict, "wide_gbs_per_sm", 400.0) * 1e9)
-        return prof_dict[("skinny_fixed",)] + max(t_hbm, t_cta)
+        # every CTA pulls the same A rows: those lines are a hot spot in L2, which then delivers
+        # only about half of what it gives a square GEMM
+        t_l2 = tiles * nkb * slab_bytes / (_param(prof_dict, "skinny_l2_gbs", 9300.0) * 1e9)
+        return prof_dict[("skinny_fixed",)] + max(t_hbm, t_cta, t_l2)
     rounds, tail = divmod(tiles, sms)
     if mode == 0:
         slabs = (rounds + (1 if tail else 0)) * nkb

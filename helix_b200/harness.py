@@ -145,7 +145,9 @@ def profile_fp16(fast=False, progress=None):
     slab_bytes = (8 + 256) * 64 * 2.0
     d[("wide_gbs_per_sm",)] = float((8192 - 2048) / 64 * slab_bytes / max(t2 - t1, 1e-9) / 1e9)
     per_byte = max(t2 - t1, 1e-9) / (2.0 * 4096 * (8192 - 2048))
-    d[("skinny_fixed",)] = float(max(t1 - 2.0 * 4096 * 2048 * per_byte, 0.0))
+    d[("skinny_fixed",)] = float(max(t1 - 2.0 * 4096 * 2048 * per_byte, 2.5e-6))
+    t = time_gemm_f16(128, 8192, 4096, cfg(64)); tick()      # 128 CTAs, all reading the same 128 rows of A
+    d[("skinny_l2_gbs",)] = float(128 * 64 * (128 + 64) * 64 * 2.0 / max(t - d[("skinny_fixed",)], 1e-9) / 1e9)
     t = time_gemm_f16(16, 256 * sms, 4096, cfg(256)); tick()
     d[("hbm_wide_gbs",)] = float(2.0 * (16 * 4096 + 256 * sms * 4096 + 16 * 256 * sms) /
                                   max(t - d[("skinny_fixed",)], 1e-9) / 1e9)
