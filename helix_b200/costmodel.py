@@ -102,6 +102,8 @@ def gemm_time(prof_dict, key, M, N, K, batch=1, conv=False):
     if not conv and group == 1 and not swap and mode == 0 and M <= tm and ("skinny_fixed",) in prof_dict:
         # one row block of A against a long weight matrix: B streams from HBM once, the A box only
         # carries M rows; bounded by the HBM rate reached with wide boxes or by what one CTA takes in
+        if bn < 128 and N >= 1024:
+            return float("inf")     # narrow boxes stream B at a fraction of the rate (measured 30 us vs 20 at bn 64)
         bytes_ = 2.0 * batch * (M * K + N * K + M * N)
         slab_bytes = (min(M, tm) + bn) * TILE_K * 2.0
         # the HBM rate grows a little with the number of streaming CTAs (measured 4.6 TB/s with 16..43, 5.6 with 148)

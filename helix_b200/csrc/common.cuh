@@ -266,6 +266,25 @@ __device__ __forceinline__ void tma_store_wait_read_1() { asm volatile("cp.async
 // until they have completed altogether
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+// ---------------------------------------------------------------- named barriers (sub-CTA groups)
+// All `nthreads` threads of the group (whole warps) must call these the same number of times.
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+// Barrier that also tells every thread whether `pred` held for all of them.
+__device__ __forceinline__ bool named_bar_and(int id, int nthreads, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %3, 0;\n\t"
+      "bar.red.and.pred p, %1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(id), "r"(nthreads), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return r != 0;
+}
+
 // ---------------------------------------------------------------- programmatic dependent launch
 // launch_dependents: the next kernel on the stream may start being scheduled (when it was launched
 // with the programmatic-serialization attribute).  wait: returns once every kernel this one depends

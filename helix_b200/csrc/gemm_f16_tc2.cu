@@ -34,7 +34,8 @@ constexpr int kBK = 64;
 constexpr int kATileBytes = kBM * kBK * 2;
 constexpr int kPairProducerWarps = 3;   // warp 0 and warps 6, 7 issue TMA loads (slab n: issuer n % load_warps)
 constexpr int kThreads = 32 + 32 + 128 + 64;
-constexpr int kStagingBytes = 4 * 2 * 32 * 128;   // two 32-row x 128-byte boxes per epilogue warp
+constexpr int kStagingBytes = 2 * 128 * 128;     // two 128-row x 128-byte boxes shared by the four epilogue warps
+constexpr int kEpiBarrier = 1;                   // named barrier of the 128 epilogue threads
 
 struct Gemm2Params {
   __half* C;
@@ -130,8 +131,12 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Arrival on a barrier that may live in the other CTA of the pair.  The arrival only has to order
+// this thread's TMEM reads (tcgen05.fence::before_thread_sync precedes it), so it carries the
+// default CTA-scope semantics: a cluster-scope release was measured to hold the thread for about
+// a microsecond per tile.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA load whose completion bytes are credited to a barrier that may live in the other CTA of the pair
 __device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const void* desc, uint32_t bar_cluster_addr, int x,
@@ -316,10 +321,12 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int acc = idx & 1;
       const uint32_t acc_phase = (idx >> 1) & 1;
       ok = mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status);
+      ok = named_bar_and(kEpiBarrier, 128, ok);   // the four warps go on, or give up, together
       if (!ok) break;
       tc_fence_after_sync();
       if (quarter == 0 && lane == 0) trace2_tile(p, idx, 4);
-      const int row0 = w.m_blk * 2 * kBM + (int)rank * kBM + quarter * 32;
+      const int cta_row0 = w.m_blk * 2 * kBM + (int)rank * kBM;
+      const int row0 = cta_row0 + quarter * 32;
       const int row = row0 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
       if (it.slot >= 0) {
@@ -341,17 +348,20 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (quarter == 0 && lane == 0) trace2_tile(p, idx, 5);
         continue;
       }
-      uint8_t* const stage_boxes = sC + (size_t)quarter * (2 * 32 * 128);
       uint32_t ra[32], rb[32], na[32], nb[32];
+      // 64 columns at a time: the four warps put their 32 rows each into one 128-row staging box
+      // and one thread sends the box with a single TMA store (issuing a tensor copy holds its
+      // thread for a few hundred cycles, so one 16 KiB store per chunk instead of four 4 KiB ones);
+      // two boxes alternate so that a store drains while the next box is filled.
       auto emit = [&](const uint32_t (&lo)[32], const uint32_t (&hi)[32], int c0) {
         const int col0 = w.n_blk * BN + c0;
-        if (col0 >= p.PN || row0 >= p.PM) return;   // warp-uniform: nothing but padding
+        if (col0 >= p.PN || cta_row0 >= p.PM) return;   // uniform over the four warps: nothing but padding
         if (p.tma_store) {
-          uint8_t* stage_box = stage_boxes + box * (32 * 128);
-          const uint32_t row_base = smem_u32(stage_box) + lane * 128;
+          uint8_t* stage_box = sC + box * (128 * 128);
+          const uint32_t row_base = smem_u32(stage_box) + (quarter * 32 + lane) * 128;
           box ^= 1;
-          if (lane == 0) tma_store_wait_read_1();   // the store issued two boxes ago has left this buffer
-          __syncwarp();
+          if (quarter == 0 && lane == 0) tma_store_wait_read_1();   // the store issued two boxes ago has left this buffer
+          named_bar_sync(kEpiBarrier, 128);
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch) {
             const uint32_t* src = ch < 4 ? &lo[ch * 8] : &hi[(ch - 4) * 8];
@@ -365,9 +375,9 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                          : "memory");
           }
           fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_3d(&tmap_c, stage_box, col0, row0, w.b);
+          named_bar_sync(kEpiBarrier, 128);
+          if (quarter == 0 && lane == 0) {
+            tma_store_3d(&tmap_c, stage_box, col0, cta_row0, w.b);
             tma_store_commit();
           }
         } else if (row < p.PM) {
@@ -418,7 +428,7 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
       if (quarter == 0 && lane == 0) trace2_tile(p, idx, 5);
     }
-    if (p.tma_store && lane == 0) tma_store_wait_all();
+    if (p.tma_store && quarter == 0 && lane == 0) tma_store_wait_all();
   }
 
   // ------------------------------------------------------------------ teardown
@@ -613,7 +623,7 @@ int gemm_f16_pair_launch(const helix_cfg_t& cfg, const void* A, int64_t lda, con
   tc = tb;
   p.tma_store = 0;
   if ((ldc & 7) == 0 && (sc & 7) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
-      make_map(&tc, C, N, M, batch, ldc, sc, 32) == HELIX_OK)
+      make_map(&tc, C, N, M, batch, ldc, sc, kBM) == HELIX_OK)
     p.tma_store = 1;
   const size_t smem = 1024 + (size_t)p.stages * (kATileBytes + (bn / 2) * kBK * 2) + kStagingBytes + 256;
   const cudaError_t e = bn == 256   ? launch_pair<256>(ta, tb, tc, p, 2 * pairs, smem, stream)
