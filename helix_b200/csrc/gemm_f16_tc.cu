@@ -577,7 +577,9 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
       if (quarter == 0 && lane == 0) trace_mark(p, idx, 5);
     }
-    if (p.tma_store && lane == 0) tma_store_wait_all();   // staged boxes are in global memory before exit
+    // the staging boxes must have been read before the CTA's shared memory goes away; the writes
+    // themselves complete with the grid
+    if (p.tma_store && lane == 0) tma_store_wait_read();
   }
 
   // ------------------------------------------------------------------ teardown
@@ -1219,7 +1221,9 @@ int conv_f16_launch(const helix_cfg_t* cfg_in, const void* x, const void* w, voi
     return gemm_f16_launch(use, x, g.C, w, g.C, y, N, M, N, K, 1, 0, 0, 0, ws, ws_bytes, status_dev, sm_count,
                            independent, stream, launches);
   }
-  const bool gather_forced = cfg_in && cfg_in->tile_m != 0 && cfg_in->conv_gather != 0;
+  if (cfg_in && cfg_in->tile_m != 0 && cfg_in->conv_gather == 3)   // window-resident kernel, on request
+    return conv_f16_halo_launch(cfg_in, x, w, y, g, status_dev, sm_count, independent, stream, launches);
+  const bool gather_forced = cfg_in && cfg_in->tile_m != 0 && cfg_in->conv_gather == 1;
   const bool im2col = !gather_forced && conv_im2col_eligible(g);
   helix_cfg_t cfg;
   if (cfg_in && cfg_in->tile_m != 0) {

@@ -428,7 +428,9 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
       if (quarter == 0 && lane == 0) trace2_tile(p, idx, 5);
     }
-    if (p.tma_store && quarter == 0 && lane == 0) tma_store_wait_all();
+    // the staging boxes must have been read before the CTA's shared memory goes away; the writes
+    // themselves complete with the grid
+    if (p.tma_store && quarter == 0 && lane == 0) tma_store_wait_read();
   }
 
   // ------------------------------------------------------------------ teardown

@@ -56,6 +56,10 @@ int gemm_f16_pair_launch(const helix_cfg_t& cfg, const void* A, int64_t lda, con
                          int64_t ldc, int M, int N, int K, int batch, int64_t sa, int64_t sb, int64_t sc, void* ws,
                          size_t ws_bytes, int* status_dev, int sm_count, bool independent, cudaStream_t stream,
                          int64_t* launches);
+// ---- conv_f16_halo.cu (stride-1 convolution with the input window resident in shared memory)
+bool conv_f16_halo_eligible(const ConvGeom& g, const helix_cfg_t* cfg);
+int conv_f16_halo_launch(const helix_cfg_t* cfg, const void* x, const void* w, void* y, const ConvGeom& g,
+                         int* status_dev, int sm_count, bool independent, cudaStream_t stream, int64_t* launches);
 int conv_f16_launch(const helix_cfg_t* cfg, const void* x, const void* w, void* y, const ConvGeom& g, void* ws,
                     size_t ws_bytes, int* status_dev, int sm_count, bool independent, cudaStream_t stream,
                     int64_t* launches);

@@ -124,6 +124,30 @@ def test_conv_im2col_tensor_map_matches_gather_and_oracle(oracle, geom):
     util.assert_f16_close(auto, y32, f"im2col conv {geom} default configuration")
 
 
+@pytest.mark.parametrize("geom", [
+    (2, 64, 32, 32, 64, 3, 3, 1, 1),      # Wp = 34, three output rows per block, 64-wide tiles
+    (3, 64, 30, 30, 72, 3, 3, 1, 1),      # ragged output channels, odd number of row blocks
+    (2, 128, 28, 28, 128, 3, 3, 1, 1),    # two channel blocks per tap (window ring wraps inside an item)
+    (2, 64, 14, 14, 256, 3, 3, 1, 1),     # Wp = 16: eight rows per block, two output-channel tiles
+    (5, 64, 7, 7, 64, 3, 3, 1, 1),        # one block per image, odd number of blocks: last item has one block
+    (2, 64, 24, 24, 32, 5, 5, 1, 2),      # 5x5 window
+    (2, 64, 20, 20, 64, 3, 3, 1, 0),      # no padding: Wp = W, output smaller than input
+    (1, 64, 40, 40, 64, 1, 3, 1, 1),      # 1x3 filter with padding also on the 1-tap axis
+    (3, 192, 20, 20, 80, 3, 3, 1, 1),     # three channel blocks
+    (1, 64, 56, 56, 64, 3, 3, 1, 1),      # Wp = 58: two rows per block, 116 of 128 accumulator rows used
+])
+def test_conv_window_resident_kernel(oracle, geom):
+    """Stride-1 convolution with the input window resident in shared memory (conv_gather = 3): every
+    filter tap reads the same buffer through a shifted matrix descriptor."""
+    B, C, H, W, OC, kh, kw, stride, pad = geom
+    x, w = datagen.c4_conv(*geom, seed=23)
+    bn = 64 if OC <= 64 else 128
+    got = _run(x, w, stride, pad, ops.make_cfg(OP_CONV_F16, tile_m=128, tile_n=bn, tile_k=64, conv_gather=3))
+    _, y32 = oracle.conv2d_nhwc_f16(x, w, stride, pad)
+    assert got.shape == y32.shape
+    util.assert_f16_close(got, y32, f"window-resident conv {geom}")
+
+
 @pytest.mark.parametrize("geom,bn", [((2, 64, 14, 14, 128, 3, 3, 1, 1), 128), ((5, 32, 9, 9, 72, 3, 3, 2, 1), 64),
                                      ((32, 128, 28, 28, 128, 3, 3, 1, 1), 128)])
 def test_conv_stream_k(oracle, geom, bn):
