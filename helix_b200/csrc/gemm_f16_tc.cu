@@ -49,6 +49,7 @@ constexpr int kConvThreads = kConvProducerWarps * 32 + 32 + 128;  // + MMA warp 
 constexpr int kGemmProducerWarps = 4;      // TMA-issuing warps: K slab n belongs to warp n % load_warps
 constexpr int kGemmThreads = kGemmProducerWarps * 32 + 32 + 128;  // TMA warps + MMA warp + 4 epilogue warps
 constexpr int kStoreStagingBytes = 4 * 2 * 32 * 128;              // two 32-row x 128-byte boxes per epilogue warp
+constexpr int kEpiBarrier = 1;                                    // named barrier of the 128 epilogue threads
 
 enum OutMode { kOutDirect = 0, kOutSplitSlice = 1, kOutStreamSlot = 2 };
 
@@ -75,6 +76,7 @@ struct GemmParams {
   int sk_tiles;    // tiles whose K slabs are dealt out
   int sk_upc;      // K slabs per CTA in the dealt part (<= num_kb, so a range touches <= 2 tiles)
   int tma_store;   // whole tiles leave through shared memory and a TMA store (tmap_c is valid)
+  int swap_fast;   // swap: tiles are transposed through shared memory and leave as 16-byte stores
   int independent; // nothing read or written here is written by the kernel queued just before
   int* status;
   // convolution only
@@ -276,7 +278,8 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           int pix_w = 0, pix_h = 0, pix_n = 0;
           if (p.im2col) {
             int rem, ho, wo;
-            fast_divmod(w.m_blk * kBM, p.fd_howo, pix_n, rem);
+            // pixels run along the 128-row axis, or along the BN axis when the operands are swapped
+            fast_divmod(p.swap ? w.n_blk * BN : w.m_blk * kBM, p.fd_howo, pix_n, rem);
             fast_divmod(rem, p.fd_wo, ho, wo);
             pix_h = ho * p.g.stride - p.g.pad;
             pix_w = wo * p.g.stride - p.g.pad;
@@ -294,13 +297,21 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
               int tap, cb, fr, fs;
               fast_divmod(kb, p.fd_cblocks, tap, cb);
               fast_divmod(tap, p.fd_s, fr, fs);
-              tma_load_im2col_4d(sA + (size_t)stage * kATileBytes, &tmap_a, &full_bar[stage], cb * kBK, pix_w,
-                                 pix_h, pix_n, (uint16_t)fs, (uint16_t)fr);
+              if (p.swap) {   // weights on the 128-row axis, BN pixels per im2col box on the other
+                tma_load_3d(sA + (size_t)stage * kATileBytes, &tmap_a, &full_bar[stage], kb * kBK, w.m_blk * kBM, 0);
+                tma_load_im2col_4d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, &full_bar[stage], cb * kBK, pix_w,
+                                   pix_h, pix_n, (uint16_t)fs, (uint16_t)fr);
+              } else {
+                tma_load_im2col_4d(sA + (size_t)stage * kATileBytes, &tmap_a, &full_bar[stage], cb * kBK, pix_w,
+                                   pix_h, pix_n, (uint16_t)fs, (uint16_t)fr);
+                tma_load_3d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, &full_bar[stage], kb * kBK, w.n_blk * BN,
+                            w.b);
+              }
             } else {
               tma_load_3d(sA + (size_t)stage * kATileBytes, &tmap_a, &full_bar[stage], kb * kBK, w.m_blk * kBM, w.b);
+              tma_load_3d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, &full_bar[stage], kb * kBK, w.n_blk * BN,
+                          w.b);
             }
-            tma_load_3d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, &full_bar[stage], kb * kBK, w.n_blk * BN,
-                        w.b);
             stage += p.load_warps;
             if (stage >= stages) { stage -= stages; phase ^= 1; }
           }
@@ -437,6 +448,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       const int acc = idx & 1;
       const uint32_t acc_phase = (idx >> 1) & 1;
       ok = mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status);
+      ok = named_bar_and(kEpiBarrier, 128, ok);   // the four warps go on, or give up, together
       if (!ok) break;
       tc_fence_after_sync();
       if (quarter == 0 && lane == 0) trace_mark(p, idx, 4);
@@ -498,6 +510,52 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 tmem_ld_32x32b_x32(taddr + c0 + 160, rb);
               }
               emit(na, nb, c0 + 64);
+            }
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+          if (quarter == 0 && lane == 0) trace_mark(p, idx, 5);
+          continue;
+        }
+      }
+      if constexpr (BN >= 32) {
+        if (p.swap && p.swap_fast && w.mode == kOutDirect) {
+          // Swapped operands: TMEM lanes index columns of C's memory rows (C[col][row]).  32 tile
+          // columns at a time are converted and transposed through shared memory ([32 cols][128
+          // rows] fp16, two buffers alternating), then leave as 16-byte stores along the
+          // contiguous axis of C: each thread writes whole 8-element segments.
+          const int m0 = w.m_blk * kBM;
+          __half* cbase = p.C + (int64_t)w.b * p.stride_c;
+          const int t = quarter * 32 + lane;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            const int col0 = w.n_blk * BN + c0;
+            if (col0 >= p.PN) break;   // uniform over the four warps: padding columns only
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(taddr + c0, r);
+            tmem_ld_wait();
+            __half* stg = reinterpret_cast<__half*>(sC + box * 8192);
+            box ^= 1;
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) stg[jj * kBM + trow] = __float2half_rn(__uint_as_float(r[jj]));
+            named_bar_sync(kEpiBarrier, 128);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int q = v * 128 + t;
+              const int cj = q >> 4, seg = q & 15;
+              const int col = col0 + cj, rw = m0 + seg * 8;
+              if (col < p.PN && rw < p.PM) {
+                const uint4 val = *reinterpret_cast<const uint4*>(stg + cj * kBM + seg * 8);
+                __half* dst = cbase + (int64_t)col * p.ldc + rw;
+                if (rw + 8 <= p.PM) {
+                  *reinterpret_cast<uint4*>(dst) = val;
+                } else {
+                  const __half* hv = reinterpret_cast<const __half*>(&val);
+                  for (int e = 0; e < 8; ++e)
+                    if (rw + e < p.PM) dst[e] = hv[e];
+                }
+              }
             }
           }
           tc_fence_before_sync();
@@ -760,25 +818,25 @@ static bool conv_im2col_eligible(const ConvGeom& g) {
 // consecutive output pixels x 64 channels for one filter tap, 128-byte swizzled like a GEMM A tile.
 // The bounding box [-pad, extent - 1 + pad - (filter - 1)] holds the window origins; stepping it
 // with the convolution stride visits exactly Wo x Ho origins per image.
-static int make_tmap_im2col(CUtensorMap* map, const void* x, const ConvGeom& g) {
+static int make_tmap_im2col(CUtensorMap* map, const void* x, const ConvGeom& g, int pixels) {
   EncodeIm2colFn fn = get_encode_im2col_fn();
   if (!fn) return HELIX_ERR_CUDA;
   if (reinterpret_cast<uintptr_t>(x) & 15) return HELIX_ERR_ALIGN;
   struct Key {
     const void* x;
-    int v[8];
+    int v[9];
     bool operator==(const Key& o) const { return x == o.x && std::memcmp(v, o.v, sizeof(v)) == 0; }
   };
   struct KeyHash {
     size_t operator()(const Key& k) const {
       size_t h = reinterpret_cast<size_t>(k.x);
-      for (int i = 0; i < 8; ++i) h ^= (size_t)k.v[i] + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+      for (int i = 0; i < 9; ++i) h ^= (size_t)k.v[i] + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
       return h;
     }
   };
   static std::mutex mu;
   static std::unordered_map<Key, CUtensorMap, KeyHash> cache;
-  const Key key{x, {g.NB, g.H, g.W, g.C, g.R, g.S, g.stride, g.pad}};
+  const Key key{x, {g.NB, g.H, g.W, g.C, g.R, g.S, g.stride, g.pad, pixels}};
   {
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
@@ -793,7 +851,7 @@ static int make_tmap_im2col(CUtensorMap* map, const void* x, const ConvGeom& g) 
   int upper[2] = {g.pad - (g.S - 1), g.pad - (g.R - 1)};
   cuuint32_t estr[4] = {1, (cuuint32_t)g.stride, (cuuint32_t)g.stride, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(x), dims, strides, lower, upper,
-                  (cuuint32_t)kBK, (cuuint32_t)kBM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  (cuuint32_t)kBK, (cuuint32_t)pixels, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return HELIX_ERR_CUDA;
   std::lock_guard<std::mutex> lock(mu);
@@ -957,9 +1015,21 @@ void conv_f16_default_config(const ConvGeom& g, int sm_count, helix_cfg_t* out) 
   const int K = (int)std::min<int64_t>((int64_t)g.R * g.S * g.C, 0x7fffffff);
   if (g.R == 1 && g.S == 1 && g.stride == 1 && g.pad == 0)
     default_config_impl(M, g.KO, K, 1, sm_count, false, true, out);
-  else if (conv_im2col_eligible(g))
+  else if (conv_im2col_eligible(g)) {
     default_config_impl(M, g.KO, K, 1, sm_count, false, false, out);
-  else
+    // A tcgen05.mma step of 128 x N x 16 takes about 130 cycles whatever N <= 256 (measured on
+    // 64-, 128- and 256-wide tiles), so 65..128 output channels are better spent as the 128 rows
+    // with 256 pixels per step: measured 17.1 -> 13.9 us on 3x3, 128 -> 128 channels, 28 x 28 x 32.
+    // With more channels the pixel tiles become too few for the machine, with 64 or fewer half of
+    // every step is padding.
+    if (g.KO > 64 && g.KO <= kBM && M >= 64 * 256) {
+      out->swap_ab = 1;
+      out->stream_k = 0;
+      out->split_k = 1;
+      out->tile_n = 256;
+      out->stages = max_stages(256, false);
+    }
+  } else
     default_config_impl(M, g.KO, K, 1, sm_count, true, false, out);
   out->op = HELIX_OP_CONV_F16;
 }
@@ -1107,6 +1177,8 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
   if (!p.swap && bn >= 64 && (ldc & 7) == 0 && (sc & 7) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
       make_tmap(&tc, C, p.PN, p.PM, p.batch, ldc, sc, 32) == HELIX_OK)
     p.tma_store = 1;
+  // swapped output: 16-byte stores along C's contiguous axis need aligned rows
+  p.swap_fast = (p.swap && bn >= 32 && (ldc & 7) == 0 && (sc & 7) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
   // a launch that shares its workspace with its neighbours on the stream is never independent of them
   p.independent = (independent && !fixup && !reduce) ? 1 : 0;
   p.fd_per_batch = make_fastdiv(p.tiles_m * p.tiles_n);
@@ -1232,7 +1304,26 @@ int conv_f16_launch(const helix_cfg_t* cfg_in, const void* x, const void* w, voi
     conv_f16_default_config(g, sm_count, &cfg);
     if (!ws || ws_bytes < gemm_f16_workspace_bytes(&cfg, M, N, K, 1, sm_count)) cfg.stream_k = 0;
   }
-  if (cfg.tile_m != kBM || cfg.cta_group > 1 || cfg.swap_ab) return HELIX_ERR_UNSUPPORTED;
+  if (cfg.tile_m != kBM || cfg.cta_group > 1) return HELIX_ERR_UNSUPPORTED;
+  if (cfg.swap_ab) {
+    // Output channels on the 128-row axis, pixels on the tile's wide axis: the tensor core takes
+    // about the same time for a 128 x N x 16 step whatever N <= 256, so few output channels are
+    // better spent as rows.  Needs the im2col map (one box = tile_n pixels) and no split of K.
+    if (!im2col || cfg.stream_k || cfg.split_k > 1 || cfg.tile_n < 32) return HELIX_ERR_UNSUPPORTED;
+    GemmParams ps{};
+    ps.PM = N;
+    ps.PN = M;
+    ps.K = K;
+    ps.batch = 1;
+    ps.status = status_dev;
+    ps.g = g;
+    ps.im2col = 1;
+    CUtensorMap tw, tx;
+    int rcs;
+    if ((rcs = make_tmap(&tw, w, K, N, 1, K, 0, kBM)) != HELIX_OK) return rcs;
+    if ((rcs = make_tmap_im2col(&tx, x, g, cfg.tile_n)) != HELIX_OK) return rcs;
+    return launch_common(cfg, false, tw, tx, ps, y, N, 0, ws, ws_bytes, sm_count, independent, stream, launches);
+  }
   GemmParams p{};
   p.PM = M;
   p.PN = N;
@@ -1247,7 +1338,7 @@ int conv_f16_launch(const helix_cfg_t* cfg_in, const void* x, const void* w, voi
   if (im2col) {
     // Same kernel as a GEMM: the one producer thread asks the im2col map for 128 pixels x 64
     // channels of one filter tap per K slab.
-    if ((rc = make_tmap_im2col(&ta, x, g)) != HELIX_OK) return rc;
+    if ((rc = make_tmap_im2col(&ta, x, g, kBM)) != HELIX_OK) return rc;
     p.im2col = 1;
     return launch_common(cfg, false, ta, tb, p, y, N, 0, ws, ws_bytes, sm_count, independent, stream, launches);
   }

@@ -148,6 +148,27 @@ def test_conv_window_resident_kernel(oracle, geom):
     util.assert_f16_close(got, y32, f"window-resident conv {geom}")
 
 
+@pytest.mark.parametrize("geom,bn", [
+    ((2, 64, 32, 32, 64, 3, 3, 1, 1), 256),     # 64 output channels on half of the 128 rows
+    ((3, 64, 30, 30, 72, 3, 3, 1, 1), 256),     # ragged channels (72) and pixels (2700)
+    ((2, 128, 33, 31, 128, 3, 3, 2, 1), 128),   # stride 2, two channel blocks per tap
+    ((2, 64, 40, 40, 136, 1, 1, 2, 0), 256),    # two row tiles of output channels (128 + 8)
+    ((1, 64, 40, 40, 64, 7, 7, 2, 3), 64),
+    ((4, 192, 20, 20, 80, 3, 3, 1, 1), 256),
+])
+def test_conv_pixels_on_wide_axis(oracle, geom, bn):
+    """swap_ab for convolutions: output channels on the 128-row axis of the tile, bn pixels per im2col box
+    on the other; the tile leaves transposed through shared memory."""
+    B, C, H, W, OC, kh, kw, stride, pad = geom
+    x, w = datagen.c4_conv(*geom, seed=29)
+    got = _run(x, w, stride, pad, ops.make_cfg(OP_CONV_F16, tile_m=128, tile_n=bn, tile_k=64, swap_ab=1))
+    _, y32 = oracle.conv2d_nhwc_f16(x, w, stride, pad)
+    assert got.shape == y32.shape
+    util.assert_f16_close(got, y32, f"swapped conv {geom} bn={bn}")
+    plain = _run(x, w, stride, pad, ops.make_cfg(OP_CONV_F16, tile_m=128, tile_n=64, tile_k=64))
+    assert np.array_equal(got, plain)            # same K order per output element: bit-identical
+
+
 @pytest.mark.parametrize("geom,bn", [((2, 64, 14, 14, 128, 3, 3, 1, 1), 128), ((5, 32, 9, 9, 72, 3, 3, 2, 1), 64),
                                      ((32, 128, 28, 28, 128, 3, 3, 1, 1), 128)])
 def test_conv_stream_k(oracle, geom, bn):
