@@ -87,8 +87,11 @@ typedef struct helix_cfg {
                     remaining tiles dealt evenly to all CTAs or CTA pairs (needs a workspace);
                     overrides split_k                                                    */
   int conv_gather; /* CONV_F16: 0 = activations arrive through an im2col tensor map wherever the
-                      geometry allows it (C a multiple of 64, tensor of 128 KiB or more);
-                      1 = always use the gathering (cp.async) producer warps               */
+                      geometry allows it (C a multiple of 64, tensor of 128 KiB or more), else
+                      through gathering producer warps; 1 = always gather (cp.async);
+                      3 = window-resident kernel (stride 1, C a multiple of 64, W + 2*pad <= 128).
+                      With swap_ab = 1 (im2col geometries only) the output channels take the
+                      128-row axis and tile_n pixels the other one                          */
   int reserved[2];
 } helix_cfg_t;
 
