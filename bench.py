@@ -246,8 +246,14 @@ def kernel_breakdown(sw, ops):
     """Time the sweep's launches grouped by the kernel they resolve to (CUDA-graph replay, events on the
     launching stream): launches, seconds and algorithmic flop / bytes per group."""
     from helix_b200 import workloads
+    import ctypes
+    from helix_b200._lib import Launch
     groups = {}
-    for u, l in zip(sw.units, sw.launches):
+    for u, l0 in zip(sw.units, sw.launches):
+        # each kernel is rated on the whole machine, whatever share of it the sweep's lanes give a launch
+        l = Launch()
+        ctypes.memmove(ctypes.byref(l), ctypes.byref(l0), ctypes.sizeof(Launch))
+        ops.limit_ctas(l, 0)
         g = groups.setdefault(ops.kernel_name(l), {"launches": [], "flop": 0.0, "bytes": 0.0})
         g["launches"].append(l)
         g["flop"] += workloads.unit_flops(u)
@@ -277,7 +283,7 @@ def bench_helix(args, rank, world, local_rank):
     peaks = read_peaks()
 
     units = workloads.model_level_sweep()
-    sw = sweep.Sweep(units, seed=4 * 1000 + rank)
+    sw = sweep.Sweep(units, seed=4 * 1000 + rank, lanes=args.lanes)
     # warm-up outside any capture: sets function attributes, fills the tensor-map cache
     launches_per_step = sw.step()
     torch.cuda.synchronize()
@@ -359,7 +365,8 @@ def bench_helix(args, rank, world, local_rank):
         "dtype": "f16 in / f32 accumulate", "data": "synthetic",
         "config": {"workload": WORKLOAD, "units_per_step_per_gpu": len(units), "flop_per_step_per_gpu": sw.flops,
                    "cache": "operands of one step total %.1f GB per GPU (> L2), one buffer set per unit" % (sw.bytes / 1e9),
-                   "cuda_graph": graph is not None, "parallelism": f"independent replicas of the sweep x{world}"},
+                   "cuda_graph": graph is not None, "parallelism": f"independent replicas of the sweep x{world}",
+                   "lanes": "%d concurrent launch chains per GPU, each launch limited to 1/%d of the SMs" % (args.lanes, args.lanes)},
         "roofline": {"bound": "tensor", "achieved": tg["TFLOP/s"], "peak": peak, "unit": "TFLOP/s",
                      "frac": tg["TFLOP/s"] / peak, "traffic": traffic,
                      "kernel": top, "launches_per_step": tg["launches"], "share_of_step": tg["share"],
@@ -399,6 +406,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["helix", "reference"], default="helix")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-configuration table and CPU sample")
+    ap.add_argument("--lanes", type=int, default=2, help="independent shapes of the sweep run in this many concurrent chains")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
     rank = int(os.environ.get("RANK", "0"))

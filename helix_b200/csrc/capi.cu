@@ -79,12 +79,18 @@ int dispatch(const helix_launch_t* l, void* status_dev, cudaStream_t stream) {
   int64_t n = 0;
   int rc;
   const helix_cfg_t* cfg = l->cfg.tile_m != 0 ? &l->cfg : nullptr;
+  // max_ctas (read even from an otherwise zeroed cfg) limits the SMs a launch may spread over
+  auto sms_of = [&](const helix_devinfo_t& di) {
+    int s = di.sm_count;
+    if (l->cfg.max_ctas > 0) s = std::max(2, std::min(s, l->cfg.max_ctas));
+    return s;
+  };
   switch (l->op) {
     case HELIX_OP_GEMM_F16:
       if ((rc = current_device(&info, true)) != HELIX_OK) return rc;
       rc = helix::gemm_f16_launch(cfg, l->a, l->lda, l->b, l->ldb, l->c, l->ldc, l->M, l->N, l->K, l->batch,
                                   l->stride_a, l->stride_b, l->stride_c, l->ws, l->ws_bytes,
-                                  static_cast<int*>(status_dev), info.sm_count,
+                                  static_cast<int*>(status_dev), sms_of(info),
                                   (l->flags & HELIX_LAUNCH_INDEPENDENT) != 0, stream, &n);
       break;
     case HELIX_OP_GEMV_F16:
@@ -99,11 +105,11 @@ int dispatch(const helix_launch_t* l, void* status_dev, cudaStream_t stream) {
           (reinterpret_cast<uintptr_t>(l->a) & 15) == 0 && (reinterpret_cast<uintptr_t>(l->b) & 15) == 0) {
         rc = helix::gemm_f16_launch(nullptr, l->b, l->ldb, l->a, l->lda, l->c, l->ldc == 0 ? l->N : l->ldc, l->M,
                                     l->N, l->K, 1, 0, 0, 0, nullptr, 0, static_cast<int*>(status_dev),
-                                    info.sm_count, (l->flags & HELIX_LAUNCH_INDEPENDENT) != 0, stream, &n);
+                                    sms_of(info), (l->flags & HELIX_LAUNCH_INDEPENDENT) != 0, stream, &n);
         break;
       }
       rc = helix::gemv_f16_launch(cfg, l->a, l->lda, l->b, l->ldb, l->c, l->ldc, l->ldc_inner, l->N, l->K, l->M,
-                                  l->ws, l->ws_bytes, info.sm_count,
+                                  l->ws, l->ws_bytes, sms_of(info),
                                   (l->flags & HELIX_LAUNCH_INDEPENDENT) ? 2 : (l->flags & HELIX_LAUNCH_STATIC_A) ? 1 : 0,
                                   stream, &n);
       break;
@@ -111,14 +117,14 @@ int dispatch(const helix_launch_t* l, void* status_dev, cudaStream_t stream) {
       if ((rc = current_device(&info, true)) != HELIX_OK) return rc;
       const helix::ConvGeom g = conv_geom(l->conv);
       rc = helix::conv_f16_launch(cfg, l->a, l->b, l->c, g, l->ws, l->ws_bytes, static_cast<int*>(status_dev),
-                                  info.sm_count, (l->flags & HELIX_LAUNCH_INDEPENDENT) != 0, stream, &n);
+                                  sms_of(info), (l->flags & HELIX_LAUNCH_INDEPENDENT) != 0, stream, &n);
       break;
     }
     case HELIX_OP_GEMM_F32:
       if ((rc = current_device(&info, false)) != HELIX_OK) return rc;
       rc = helix::sgemm_f32_launch(cfg, static_cast<const float*>(l->a), l->lda, l->trans_a,
                                    static_cast<const float*>(l->b), l->ldb, static_cast<float*>(l->c), l->ldc, l->M,
-                                   l->N, l->K, info.sm_count, stream, &n);
+                                   l->N, l->K, sms_of(info), stream, &n);
       break;
     default:
       return HELIX_ERR_INVALID;
@@ -204,7 +210,8 @@ int helix_get_config(int op, int idx, helix_cfg_t* out) {
 int helix_default_config(const helix_launch_t* l, helix_cfg_t* out) {
   if (!l || !out) return HELIX_ERR_INVALID;
   helix_devinfo_t info;
-  const int sms = (query_device(-1, &info) == HELIX_OK) ? info.sm_count : 148;
+  int sms = (query_device(-1, &info) == HELIX_OK) ? info.sm_count : 148;
+  if (l->cfg.max_ctas > 0) sms = std::max(2, std::min(sms, l->cfg.max_ctas));
   std::memset(out, 0, sizeof(*out));
   switch (l->op) {
     case HELIX_OP_GEMM_F16:
@@ -233,7 +240,8 @@ int helix_default_config(const helix_launch_t* l, helix_cfg_t* out) {
 size_t helix_workspace_bytes(const helix_launch_t* l) {
   if (!l) return 0;
   helix_devinfo_t info;
-  const int sms = (query_device(-1, &info) == HELIX_OK) ? info.sm_count : 148;
+  int sms = (query_device(-1, &info) == HELIX_OK) ? info.sm_count : 148;
+  if (l->cfg.max_ctas > 0) sms = std::max(2, std::min(sms, l->cfg.max_ctas));
   const bool have_cfg = l->cfg.tile_m != 0;
   switch (l->op) {
     case HELIX_OP_GEMM_F16: {

@@ -45,14 +45,32 @@ def check_status(device=None):
         raise _lib.HelixError(v, "device status word")
 
 
-def workspace(nbytes, device=None):
-    """Grow-only scratch buffer per device, reused across calls on the same stream."""
+def workspace(nbytes, device=None, lane=0):
+    """Grow-only scratch buffer per device (and per lane of concurrent launch chains), reused across
+    calls that are ordered on one stream."""
     dev = torch.cuda.current_device() if device is None else torch.device(device).index
-    cur = _workspaces.get(dev)
+    cur = _workspaces.get((dev, lane))
     if cur is None or cur.numel() < nbytes:
         cur = torch.empty(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=f"cuda:{dev}")
-        _workspaces[dev] = cur
+        _workspaces[(dev, lane)] = cur
     return cur
+
+
+def limit_ctas(launch, max_ctas, lane=0):
+    """Let `launch` spread over at most `max_ctas` SMs (so that independent launches on other streams can
+    run beside it) and give it the scratch buffer of its lane; the library re-chooses its configuration
+    for the smaller machine when cfg is left to it."""
+    lib = _lib.load()
+    launch.cfg.max_ctas = int(max_ctas)
+    need = lib.helix_workspace_bytes(ctypes.byref(launch))
+    if need:
+        buf = workspace(need, lane=lane)
+        launch.ws = buf.data_ptr()
+        launch.ws_bytes = buf.numel() * buf.element_size()
+        launch._ws_ref = buf
+    else:
+        launch.ws, launch.ws_bytes = None, 0
+    return launch
 
 
 def device_info(dev=-1):

@@ -47,8 +47,12 @@ def _fill(shape, scale, gen, device, valid_channels=None):
 class Sweep:
     """Device-resident sweep: distinct operand buffers per unit, one prepared launch each."""
 
-    def __init__(self, units, seed=4, device=None, cfg_for=None):
+    def __init__(self, units, seed=4, device=None, cfg_for=None, lanes=1):
+        """lanes > 1: the units are dealt round-robin to that many streams and every launch is limited to
+        1/lanes of the SMs, so independent shapes run side by side with longer-lived CTAs (the set-up and
+        drain of one launch hide behind the steady state of its neighbour)."""
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.lanes = max(1, int(lanes))
         self.units = list(units)
         self.tensors = []
         self.launches = []
@@ -72,6 +76,9 @@ class Sweep:
             l = self._prepare(u, a, b, out, cfg)
             # units of a sweep share no buffers, so a launch need not wait for its predecessor
             l.flags = LAUNCH_INDEPENDENT
+            if self.lanes > 1:
+                sms = ops.device_info().sm_count
+                ops.limit_ctas(l, (sms // self.lanes) & ~1, lane=i % self.lanes)
             self.launches.append(l)
         self.flops = sum(workloads.unit_flops(u) for u in self.units)
         self.bytes = sum(workloads.unit_bytes(u) for u in self.units)
@@ -84,10 +91,27 @@ class Sweep:
         return ops.launch_conv2d_f16(a, b, out, stride, pad, cfg)
 
     def step(self):
-        """Queue every unit once on the current stream; returns the number of library launches."""
+        """Queue every unit once (on the current stream, or dealt to the lanes' streams, which fork from
+        and join back into the current stream); returns the number of library launches."""
         before = ops.launch_count()
-        for l in self.launches:
-            ops.run(l)
+        if self.lanes == 1:
+            for l in self.launches:
+                ops.run(l)
+            return ops.launch_count() - before
+        main = torch.cuda.current_stream()
+        if getattr(self, "_streams", None) is None:
+            self._streams = [torch.cuda.Stream(device=self.device) for _ in range(self.lanes)]
+        fork = torch.cuda.Event()
+        fork.record(main)
+        for s in self._streams:
+            s.wait_event(fork)
+        for i, l in enumerate(self.launches):
+            with torch.cuda.stream(self._streams[i % self.lanes]):
+                ops.run(l)
+        for s in self._streams:
+            done = torch.cuda.Event()
+            done.record(s)
+            main.wait_event(done)
         return ops.launch_count() - before
 
 

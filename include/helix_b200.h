@@ -92,7 +92,10 @@ typedef struct helix_cfg {
                       3 = window-resident kernel (stride 1, C a multiple of 64, W + 2*pad <= 128).
                       With swap_ab = 1 (im2col geometries only) the output channels take the
                       128-row axis and tile_n pixels the other one                          */
-  int reserved[2];
+  int max_ctas;  /* > 0: the launch spreads over at most this many SMs (also honoured when the rest of
+                    the struct is zero, i.e. with the library's own choice): lets two independent
+                    launches on two streams share the machine, each with longer-lived CTAs      */
+  int reserved[1];
 } helix_cfg_t;
 
 /* A fully described launch; the tagged union the timing entry point iterates. */
