@@ -157,6 +157,7 @@ class ClockSampler:
             busy = sm[len(sm) // 2:]
             out["sm_mhz"] = busy[len(busy) // 2]
             out["sm_max_mhz"] = mx
+            out["sm_min_mhz_seen"] = sm[0]
             out["samples"] = len(sm)
         out["reasons"] = sorted(reasons)
         return out
@@ -388,7 +389,11 @@ def bench_helix(args, rank, world, local_rank):
     if world == 1 and not args.no_extras:
         del hs
         torch.cuda.empty_cache()
+        # the per-shape table runs on a GPU the sweep has already heated: record the clocks it saw
+        xs = ClockSampler(local_rank)
+        xs.start()
         line["extras"] = extras(peaks)
+        line["extras"]["clocks"] = xs.stop()
         dt, flops, cores = run_cpu_sample()
         line["cpu_baseline"] = {
             "value": flops / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",

@@ -219,3 +219,73 @@ def test_max_over_ranks_and_aggregate_throughput_world_size_2(tmp_path):
     assert all(p.returncode == 0 for p in procs)
     for rank, (r, slowest, tput) in enumerate(outs):
         assert int(r) == rank and float(slowest) == 2.0 and float(tput) == pytest.approx(10.0)   # 2 x 10 units / 2 s
+
+
+# ----------------------------------------------------------------------------- one GEMM split along N
+def test_nsplit_slabs_tile_n_and_rows_do_not_depend_on_the_split():
+    import numpy as np
+    from helix_b200 import nsplit
+    for N in (0, 1, 255, 256, 1000, 4096, 11008, 65536):
+        for world in (1, 2, 3, 4, 8):
+            bounds = [nsplit.slab_bounds(N, world, r) for r in range(world)]
+            assert bounds[0][0] == 0 and bounds[-1][1] == N
+            for (a0, a1), (b0, b1) in zip(bounds, bounds[1:]):
+                assert a1 == b0 and a0 <= a1
+            assert all(n0 % nsplit.ROW_BLOCK == 0 for n0, _ in bounds)
+            widths = [n1 - n0 for n0, n1 in bounds]
+            assert max(widths) - min(widths) <= nsplit.ROW_BLOCK
+    with pytest.raises(ValueError):
+        nsplit.slab_bounds(1024, 2, 2)
+    whole = nsplit.seeded_rows(5, 0, 1000, 96, 0.1)
+    assert whole.dtype == np.float16 and whole.shape == (1000, 96)
+    for world in (2, 3):
+        parts = []
+        for r in range(world):
+            n0, n1 = nsplit.slab_bounds(1000, world, r)
+            parts.append(nsplit.seeded_rows(5, n0, n1, 96, 0.1))
+        assert np.array_equal(np.concatenate(parts), whole)
+    assert not np.array_equal(nsplit.seeded_rows(6, 0, 256, 96, 0.1), whole[:256])
+    with pytest.raises(ValueError):
+        nsplit.seeded_rows(5, 100, 300, 96, 0.1)
+    a0, b0, _ = nsplit.operands(64, 1000, 96, 9, 2, 0)
+    a1, b1, _ = nsplit.operands(64, 1000, 96, 9, 2, 1)
+    assert np.array_equal(a0, a1) and b0.shape[0] + b1.shape[0] == 1000
+    with pytest.raises(ValueError):
+        nsplit.assemble([np.zeros((4, 3), np.float16)], [(0, 4)], 4, 4)
+
+
+NSPLIT_WORKER = r"""
+import os, sys
+sys.path.insert(0, {root!r})
+import numpy as np, torch
+import torch.distributed as dist
+from helix_b200 import nsplit
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:{port}", rank=int(sys.argv[1]), world_size=2)
+rank = dist.get_rank()
+M, N, K = 48, 700, 64
+a, b, (n0, n1) = nsplit.operands(M, N, K, 3, 2, rank)
+g = object.__new__(nsplit.NSplitGemm)          # host logic only: the slab product is a stand-in computed here
+g.M, g.N, g.K, g.world, g.rank, g.n0, g.n1 = M, N, K, 2, rank, n0, n1
+g.c = torch.from_numpy((a.astype(np.float32) @ b.astype(np.float32).T).astype(np.float16))
+full = g.gather(dist)
+a_all, b_all, _ = nsplit.operands(M, N, K, 3, 1, 0)
+want = (a_all.astype(np.float32) @ b_all.astype(np.float32).T).astype(np.float16)
+print(rank, n0, n1, int(np.array_equal(full, want)))
+dist.destroy_process_group()
+"""
+
+
+def test_nsplit_gather_assembles_the_full_product_world_size_2(tmp_path):
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    script = tmp_path / "n.py"
+    script.write_text(NSPLIT_WORKER.format(root=ROOT, port=port))
+    procs = [subprocess.Popen([sys.executable, str(script), str(r)], stdout=subprocess.PIPE, text=True) for r in (0, 1)]
+    outs = [p.communicate(timeout=120)[0].split() for p in procs]
+    assert all(p.returncode == 0 for p in procs)
+    assert [o[0] for o in outs] == ["0", "1"]
+    assert (outs[0][1], outs[0][2], outs[1][1], outs[1][2]) == ("0", "256", "256", "700")
+    assert outs[0][3] == "1" and outs[1][3] == "1"
