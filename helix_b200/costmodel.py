@@ -28,9 +28,12 @@ GEMV_VARIANTS = ((2, 4), (1, 4), (1, 8), (2, 2))   # (rows per warp, 16-byte loa
 GEMV_SPLITS = (1, 2, 4, 8)
 DEFAULT_SMS = 148
 
-# FP32 SIMT tiles: (BM, BN, BK, TM, TN), the analogue of the reference's
+# FP32 SIMT tiles: (BM, BN, BK, TM, TN, stages), the analogue of the reference's
 # (BM, BN, BK, TM, TN, WARP_ROW_THREAD, COPY_A, COPY_B) keys (build_Ampere_FP32.py:37-63)
-SGEMM_TILES = ((128, 128, 16, 8, 8), (128, 64, 16, 8, 4), (64, 128, 16, 4, 8), (64, 64, 16, 4, 4), (32, 64, 16, 4, 4))
+SGEMM_TILES = ((128, 128, 16, 8, 8, 4), (128, 128, 32, 8, 8, 3), (128, 64, 16, 8, 4, 4), (128, 64, 32, 8, 4, 3),
+               (64, 128, 16, 4, 8, 4),
+               (128, 128, 16, 8, 8, 2), (128, 64, 16, 8, 4, 2), (64, 128, 16, 4, 8, 2), (64, 64, 16, 4, 4, 2),
+               (32, 64, 16, 4, 4, 2))
 
 
 def is_valid_config(tile_n, swap_ab, mode, stages):
@@ -71,7 +74,8 @@ def gemv_keys():
 
 
 def sgemm_keys():
-    return [(bm, bn, bk, tm, tn, 0, 0, 0) for (bm, bn, bk, tm, tn) in SGEMM_TILES]
+    """(BM, BN, BK, TM, TN, stages, 0, 0): stages 2 = register-staged double buffer, >= 3 = cp.async ring."""
+    return [(bm, bn, bk, tm, tn, st, 0, 0) for (bm, bn, bk, tm, tn, st) in SGEMM_TILES]
 
 
 # ----------------------------------------------------------------------------- prediction

@@ -26,6 +26,7 @@ struct SgemmTraits {
   static constexpr int kBElems = BN * BK / kThreads;
   static_assert(TM % 4 == 0 && TN % 4 == 0, "register block is made of 4-wide quads");
   static_assert(kAElems % 4 == 0 && kBElems % 4 == 0, "whole float4s per thread");
+  static_assert(kThreadsM % 4 == 0 && kThreadsN % 8 == 0, "a warp covers 4 x 8 threads of the grid");
 };
 
 template <int BM, int BN, int BK, int TM, int TN, bool TRANS_A, bool VEC>
@@ -39,9 +40,13 @@ sgemm_f32_kernel(const float* __restrict__ A, int64_t lda, const float* __restri
   __shared__ __align__(16) float sA[2][BK][BM + 4];
   __shared__ __align__(16) float sB[2][BK][BN + 4];
 
+  // a warp covers 4 x 8 threads of the kThreadsM x kThreadsN grid, a half-warp 4 x 4: a 128-bit shared
+  // load is served half-warp by half-warp, and 4 distinct float4 per half cost one pass instead of two
   const int tid = threadIdx.x;
-  const int tn = tid % T::kThreadsN;
-  const int tm = tid / T::kThreadsN;
+  const int lane = tid & 31, warp = tid >> 5;
+  constexpr int kWarpsN = T::kThreadsN / 8;
+  const int tn = (warp % kWarpsN) * 8 + (lane & 3) + 4 * (lane >> 4);
+  const int tm = (warp / kWarpsN) * 4 + ((lane >> 2) & 3);
   const int m0 = blockIdx.y * BM;
   const int n0 = blockIdx.x * BN;
 
@@ -193,9 +198,248 @@ sgemm_f32_kernel(const float* __restrict__ A, int64_t lda, const float* __restri
     }
 }
 
-struct SgemmCfg { int bm, bn, bk, tm, tn; };
+// ---------------------------------------------------------------------------------------------
+// Pipelined variant for 16-byte-aligned operands: cp.async straight from global to shared memory
+// through a ring of STAGES slabs (no register staging, one __syncthreads per slab, loads issued
+// STAGES-1 slabs ahead).  Both operands are staged K-major as above.  B and a K x M A (trans_a)
+// arrive as 16-byte copies; a row-major M x K A is transposed by the copy itself, one 4-byte
+// cp.async per element (consecutive threads take consecutive k of one row, so a warp still reads
+// whole 64-byte runs of A), which costs a few more copy instructions per slab and no registers.
+// Rows outside the matrix and the K tail are zero-filled by the copy's source size.
+template <int BM, int BN, int BK, int TM, int TN, int STAGES, bool TRANS_A>
+struct SgemmPipeTraits {
+  static constexpr int kThreadsM = BM / TM;
+  static constexpr int kThreadsN = BN / TN;
+  static constexpr int kThreads = kThreadsM * kThreadsN;
+  static constexpr int kARow = BM + 4;                         // floats per shared row (one k) of A
+  static constexpr int kBRow = BN + 4;
+  static constexpr int kAStage = BK * kARow;                   // floats per stage
+  static constexpr int kBStage = BK * kBRow;
+  static constexpr int kSmemBytes = STAGES * (kAStage + kBStage) * 4;
+  static constexpr int kA4 = BM * BK / 4 / kThreads;           // 16-byte copies of A per thread per slab (K x M A)
+  static constexpr int kA1 = BM * BK / kThreads;               // 4-byte copies of A per thread per slab (M x K A)
+  static constexpr int kB4 = BN * BK / 4 / kThreads;
+  static_assert(TM % 4 == 0 && TN % 4 == 0 && BK % 4 == 0, "4-wide quads");
+  static_assert(kThreadsM % 4 == 0 && kThreadsN % 8 == 0, "a warp covers 4 x 8 threads of the grid");
+  static_assert((BM * BK / 4) % kThreads == 0 && (BN * BK / 4) % kThreads == 0, "whole copies per thread");
+};
+
+__device__ __forceinline__ void cp_async_16_bytes(uint32_t smem_dst, const void* gsrc, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void cp_async_4_bytes(uint32_t smem_dst, const void* gsrc, int src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_bytes)
+               : "memory");
+}
+
+template <int BM, int BN, int BK, int TM, int TN, int STAGES, bool TRANS_A, int MIN_CTAS>
+__global__ void __launch_bounds__(SgemmPipeTraits<BM, BN, BK, TM, TN, STAGES, TRANS_A>::kThreads, MIN_CTAS)
+sgemm_f32_pipe_kernel(const float* __restrict__ A, int64_t lda, const float* __restrict__ B, int64_t ldb,
+                      float* __restrict__ C, int64_t ldc, int M, int N, int K) {
+  using T = SgemmPipeTraits<BM, BN, BK, TM, TN, STAGES, TRANS_A>;
+  constexpr int NT = T::kThreads;
+  extern __shared__ __align__(16) float smem_f[];
+  float* sA = smem_f;
+  float* sB = smem_f + STAGES * T::kAStage;
+  const uint32_t sA_u = smem_u32(sA), sB_u = smem_u32(sB);
+
+  // Thread grid kThreadsM x kThreadsN; a warp covers 4 x 8 of it and each half-warp 4 x 4, so that a
+  // 16-byte shared load touches at most 64 distinct bytes per half-warp: a 128-bit shared load is
+  // served half-warp by half-warp, 128 distinct bytes per pass (measured: 16 lanes reading 16
+  // different float4 cost two passes per half)
+  const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+  constexpr int kWarpsN = T::kThreadsN / 8;
+  const int tn = (warp % kWarpsN) * 8 + (lane & 3) + 4 * (lane >> 4);
+  const int tm = (warp / kWarpsN) * 4 + ((lane >> 2) & 3);
+  auto row_of = [&](int i) { return ((i >> 2) * T::kThreadsM + tm) * 4 + (i & 3); };   // quads of rows
+  const int m0 = blockIdx.y * BM;
+  const int n0 = blockIdx.x * BN;
+
+  float acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+
+  // Copies of an interior tile and a full slab need no bounds work: every thread keeps one running
+  // pointer per operand (advanced once per slab) and its passes are a fixed stride apart.
+  const bool interior = (m0 + BM <= M) && (n0 + BN <= N);
+  constexpr int kAPassRows = TRANS_A ? NT / (BM / 4) : NT / BK;     // k rows (K x M A) or m rows (M x K A) per pass
+  constexpr int kBPassRows = NT / (BN / 4);
+  const int a_r = TRANS_A ? tid / (BM / 4) : tid / BK;               // row of the first pass
+  const int a_c = TRANS_A ? (tid % (BM / 4)) * 4 : tid % BK;         // column (m for K x M, k for M x K)
+  const int b_r = tid / (BN / 4), b_c = (tid % (BN / 4)) * 4;
+  const float* a_run = TRANS_A ? A + (int64_t)a_r * lda + (m0 + a_c) : A + (int64_t)(m0 + a_r) * lda + a_c;
+  const float* b_run = B + (int64_t)b_r * ldb + (n0 + b_c);
+  const int64_t a_pass = (int64_t)kAPassRows * lda;
+  const int64_t b_pass = (int64_t)kBPassRows * ldb;
+  const int64_t a_slab = TRANS_A ? (int64_t)BK * lda : (int64_t)BK;
+  const int64_t b_slab = (int64_t)BK * ldb;
+  const uint32_t a_dst = sA_u + (uint32_t)(TRANS_A ? a_r * T::kARow + a_c : a_c * T::kARow + a_r) * 4u;
+  const uint32_t b_dst = sB_u + (uint32_t)(b_r * T::kBRow + b_c) * 4u;
+  constexpr uint32_t kADstPass = (TRANS_A ? kAPassRows * T::kARow : kAPassRows) * 4u;
+  constexpr uint32_t kBDstPass = kBPassRows * T::kBRow * 4u;
+  int slabs_issued = 0;      // a_run / b_run point at slab `slabs_issued`
+
+  auto issue = [&](int slab, int stage) {
+    const int k0 = slab * BK;
+    if (interior && k0 + BK <= K && slab == slabs_issued) {
+      const uint32_t ad = a_dst + (uint32_t)(stage * T::kAStage) * 4u;
+      const uint32_t bd = b_dst + (uint32_t)(stage * T::kBStage) * 4u;
+      if (TRANS_A) {
+#pragma unroll
+        for (int v = 0; v < T::kA4; ++v)
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ad + v * kADstPass), "l"(a_run + v * a_pass) : "memory");
+      } else {
+#pragma unroll
+        for (int v = 0; v < T::kA1; ++v)
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(ad + v * kADstPass), "l"(a_run + v * a_pass) : "memory");
+      }
+#pragma unroll
+      for (int v = 0; v < T::kB4; ++v)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(bd + v * kBDstPass), "l"(b_run + v * b_pass) : "memory");
+      a_run += a_slab;
+      b_run += b_slab;
+      ++slabs_issued;
+      return;
+    }
+    if (TRANS_A) {
+#pragma unroll
+      for (int v = 0; v < T::kA4; ++v) {
+        const int f = v * NT + tid;
+        const int kk = f / (BM / 4), mm = (f % (BM / 4)) * 4;
+        const int gk = k0 + kk, gm = m0 + mm;
+        const int bytes = gk < K ? max(0, min(4, M - gm)) * 4 : 0;
+        const float* src = bytes ? A + (int64_t)gk * lda + gm : A;
+        cp_async_16_bytes(sA_u + (uint32_t)(stage * T::kAStage + kk * T::kARow + mm) * 4u, src, bytes);
+      }
+    } else {
+#pragma unroll
+      for (int v = 0; v < T::kA1; ++v) {
+        const int f = v * NT + tid;
+        const int mm = f / BK, kk = f % BK;
+        const int gk = k0 + kk, gm = m0 + mm;
+        const int bytes = (gm < M && gk < K) ? 4 : 0;
+        const float* src = bytes ? A + (int64_t)gm * lda + gk : A;
+        cp_async_4_bytes(sA_u + (uint32_t)(stage * T::kAStage + kk * T::kARow + mm) * 4u, src, bytes);
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < T::kB4; ++v) {
+      const int f = v * NT + tid;
+      const int kk = f / (BN / 4), nn = (f % (BN / 4)) * 4;
+      const int gk = k0 + kk, gn = n0 + nn;
+      const int bytes = gk < K ? max(0, min(4, N - gn)) * 4 : 0;
+      const float* src = bytes ? B + (int64_t)gk * ldb + gn : B;
+      cp_async_16_bytes(sB_u + (uint32_t)(stage * T::kBStage + kk * T::kBRow + nn) * 4u, src, bytes);
+    }
+  };
+
+  const int num_slabs = (K + BK - 1) / BK;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < num_slabs) issue(s, s);
+    cp_async_commit();
+  }
+
+  int stage = 0;
+  for (int s = 0; s < num_slabs; ++s) {
+    cp_async_wait<STAGES - 2>();      // slab s has landed (this thread's copies) ...
+    __syncthreads();                  // ... and everyone's; the stage consumed at s-1 is free again
+    {
+      const int ahead = s + STAGES - 1;
+      int st = stage + STAGES - 1;
+      if (st >= STAGES) st -= STAGES;
+      if (ahead < num_slabs) issue(ahead, st);
+      cp_async_commit();
+    }
+    const float* a = sA + stage * T::kAStage;
+    const float* b = sB + stage * T::kBStage;
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float av[TM], bv[TN];
+#pragma unroll
+      for (int q = 0; q < TM / 4; ++q) {
+        const float4 t = *reinterpret_cast<const float4*>(&a[kk * T::kARow + (q * T::kThreadsM + tm) * 4]);
+        av[q * 4 + 0] = t.x; av[q * 4 + 1] = t.y; av[q * 4 + 2] = t.z; av[q * 4 + 3] = t.w;
+      }
+#pragma unroll
+      for (int q = 0; q < TN / 4; ++q) {
+        const float4 t = *reinterpret_cast<const float4*>(&b[kk * T::kBRow + (q * T::kThreadsN + tn) * 4]);
+        bv[q * 4 + 0] = t.x; bv[q * 4 + 1] = t.y; bv[q * 4 + 2] = t.z; bv[q * 4 + 3] = t.w;
+      }
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    if (++stage == STAGES) stage = 0;
+  }
+  cp_async_wait<0>();
+
+#pragma unroll
+  for (int qi = 0; qi < TM / 4; ++qi)
+#pragma unroll
+    for (int ii = 0; ii < 4; ++ii) {
+      const int gm = m0 + row_of(qi * 4 + ii);
+      if (gm >= M) continue;
+#pragma unroll
+      for (int qj = 0; qj < TN / 4; ++qj) {
+        const int gn = n0 + (qj * T::kThreadsN + tn) * 4;
+        float* p = C + (int64_t)gm * ldc + gn;
+        const float* r = &acc[qi * 4 + ii][qj * 4];
+        if (gn + 3 < N) *reinterpret_cast<float4*>(p) = make_float4(r[0], r[1], r[2], r[3]);
+        else {
+          if (gn + 0 < N) p[0] = r[0];
+          if (gn + 1 < N) p[1] = r[1];
+          if (gn + 2 < N) p[2] = r[2];
+        }
+      }
+    }
+}
+
+template <int BM, int BN, int BK, int TM, int TN, int STAGES, int MIN_CTAS>
+static cudaError_t launch_sgemm_pipe(const float* A, int64_t lda, bool trans_a, const float* B, int64_t ldb, float* C,
+                                     int64_t ldc, int M, int N, int K, cudaStream_t stream) {
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  if (trans_a) {
+    using T = SgemmPipeTraits<BM, BN, BK, TM, TN, STAGES, true>;
+    auto kern = sgemm_f32_pipe_kernel<BM, BN, BK, TM, TN, STAGES, true, MIN_CTAS>;
+    static thread_local int attr_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_dev != dev) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);
+      if (e != cudaSuccess) return e;
+      attr_dev = dev;
+    }
+    kern<<<grid, T::kThreads, T::kSmemBytes, stream>>>(A, lda, B, ldb, C, ldc, M, N, K);
+  } else {
+    using T = SgemmPipeTraits<BM, BN, BK, TM, TN, STAGES, false>;
+    auto kern = sgemm_f32_pipe_kernel<BM, BN, BK, TM, TN, STAGES, false, MIN_CTAS>;
+    static thread_local int attr_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_dev != dev) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);
+      if (e != cudaSuccess) return e;
+      attr_dev = dev;
+    }
+    kern<<<grid, T::kThreads, T::kSmemBytes, stream>>>(A, lda, B, ldb, C, ldc, M, N, K);
+  }
+  return cudaSuccess;
+}
+
+// stages == 2: register-staged double buffer (any alignment); stages >= 3: cp.async ring (16-byte-aligned operands,
+// otherwise the launch falls back to the register-staged kernel of the same tile)
+struct SgemmCfg { int bm, bn, bk, tm, tn, stages; };
 static const SgemmCfg kSgemmCfgs[] = {
-    {128, 128, 16, 8, 8}, {128, 64, 16, 8, 4}, {64, 128, 16, 4, 8}, {64, 64, 16, 4, 4}, {32, 64, 16, 4, 4},
+    {128, 128, 16, 8, 8, 4}, {128, 128, 32, 8, 8, 3}, {128, 64, 16, 8, 4, 4}, {128, 64, 32, 8, 4, 3},
+    {64, 128, 16, 4, 8, 4},
+    {128, 128, 16, 8, 8, 2}, {128, 64, 16, 8, 4, 2}, {64, 128, 16, 4, 8, 2}, {64, 64, 16, 4, 4, 2}, {32, 64, 16, 4, 4, 2},
 };
 constexpr int kNumSgemmCfgs = sizeof(kSgemmCfgs) / sizeof(kSgemmCfgs[0]);
 
@@ -208,18 +452,46 @@ void sgemm_f32_get_config(int idx, helix_cfg_t* out) {
   out->tile_k = kSgemmCfgs[idx].bk;
   out->thread_m = kSgemmCfgs[idx].tm;
   out->thread_n = kSgemmCfgs[idx].tn;
-  out->stages = 2;
+  out->stages = kSgemmCfgs[idx].stages;
   out->cta_group = 1;
   out->split_k = 1;
 }
 
-// Largest tile that still yields about two CTAs per SM, else the smallest tile.
+// Relative FFMA-issue efficiency of each configuration when the machine is full (measured on large
+// squares), used to rank configurations by ceil(tiles / resident CTAs) * tile work / efficiency.
+static double sgemm_cfg_rate(const SgemmCfg& c) {
+  if (c.stages >= 3) {
+    if (c.bm == 128 && c.bn == 128) return c.bk == 32 ? 1.0 : 0.93;
+    if (c.bm == 64) return 0.91;
+    return c.bk == 32 ? 0.85 : 0.89;
+  }
+  if (c.bm == 128) return 0.86;
+  if (c.bn == 128) return 0.82;
+  return 0.72;
+}
+static int sgemm_cfg_ctas_per_sm(const SgemmCfg& c) {
+  if (c.stages >= 3) return 2;
+  return (c.bm == 128 && c.bn == 128) ? 2 : (c.bm * c.bn >= 8192 ? 3 : 4);
+}
+
+// The configuration with the smallest estimate of waves * work per tile / rate; a wave holds
+// ctas_per_sm tiles on every SM, and an SM that holds fewer CTAs than it could runs them slower
+// (less latency hiding), which the estimate charges as a 25 % penalty for a single resident CTA.
 void sgemm_f32_default_config(int M, int N, int sm_count, helix_cfg_t* out) {
-  int pick = kNumSgemmCfgs - 1;
+  int pick = 0;
+  double best = 1e300;
   for (int i = 0; i < kNumSgemmCfgs; ++i) {
-    const int64_t tiles = (int64_t)((M + kSgemmCfgs[i].bm - 1) / kSgemmCfgs[i].bm) *
-                          ((N + kSgemmCfgs[i].bn - 1) / kSgemmCfgs[i].bn);
-    if (tiles >= 2 * (int64_t)sm_count) { pick = i; break; }
+    const SgemmCfg& c = kSgemmCfgs[i];
+    const int64_t tiles = (int64_t)((M + c.bm - 1) / c.bm) * ((N + c.bn - 1) / c.bn);
+    const int per_sm = sgemm_cfg_ctas_per_sm(c);
+    const int64_t slots = (int64_t)sm_count * per_sm;
+    const int64_t waves = (tiles + slots - 1) / slots;
+    // CTAs on the busiest SM over the whole run, in units of tile work
+    const int64_t busiest = (waves - 1) * per_sm + ((tiles - (waves - 1) * slots) + sm_count - 1) / sm_count;
+    double rate = sgemm_cfg_rate(c);
+    if (tiles <= sm_count) rate *= 0.75;
+    const double t = (double)busiest * c.bm * c.bn / rate;
+    if (t < best) { best = t; pick = i; }
   }
   sgemm_f32_get_config(pick, out);
 }
@@ -248,17 +520,33 @@ int sgemm_f32_launch(const helix_cfg_t* cfg, const float* A, int64_t lda, int tr
   const bool vec = ((lda & 3) == 0) && ((ldb & 3) == 0) && ((ldc & 3) == 0) &&
                    ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && ((reinterpret_cast<uintptr_t>(B) & 15) == 0) &&
                    ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
-  int bm, bn;
+  int bm, bn, bk, stages;
   if (cfg && cfg->tile_m != 0) {
     bm = cfg->tile_m;
     bn = cfg->tile_n;
+    bk = cfg->tile_k ? cfg->tile_k : 16;
+    stages = cfg->stages ? cfg->stages : 2;
   } else {
     helix_cfg_t def{};
     sgemm_f32_default_config(M, N, sm_count, &def);
     bm = def.tile_m;
     bn = def.tile_n;
+    bk = def.tile_k;
+    stages = def.stages;
   }
   const bool ta = trans_a != 0;
+  if (stages >= 3 && vec) {
+    cudaError_t e = cudaErrorInvalidValue;
+    if (bm == 128 && bn == 128 && bk == 16) e = launch_sgemm_pipe<128, 128, 16, 8, 8, 4, 2>(A, lda, ta, B, ldb, C, ldc, M, N, K, stream);
+    else if (bm == 128 && bn == 128 && bk == 32) e = launch_sgemm_pipe<128, 128, 32, 8, 8, 3, 2>(A, lda, ta, B, ldb, C, ldc, M, N, K, stream);
+    else if (bm == 128 && bn == 64 && bk == 16) e = launch_sgemm_pipe<128, 64, 16, 8, 4, 4, 2>(A, lda, ta, B, ldb, C, ldc, M, N, K, stream);
+    else if (bm == 128 && bn == 64 && bk == 32) e = launch_sgemm_pipe<128, 64, 32, 8, 4, 3, 2>(A, lda, ta, B, ldb, C, ldc, M, N, K, stream);
+    else if (bm == 64 && bn == 128 && bk == 16) e = launch_sgemm_pipe<64, 128, 16, 4, 8, 4, 2>(A, lda, ta, B, ldb, C, ldc, M, N, K, stream);
+    else return HELIX_ERR_UNSUPPORTED;
+    if (e != cudaSuccess) return HELIX_ERR_CUDA;
+    ++*launches;
+    return cudaGetLastError() == cudaSuccess ? HELIX_OK : HELIX_ERR_CUDA;
+  }
   if (bm == 128 && bn == 128) launch_sgemm<128, 128, 16, 8, 8>(A, lda, ta, B, ldb, C, ldc, M, N, K, vec, stream);
   else if (bm == 128 && bn == 64) launch_sgemm<128, 64, 16, 8, 4>(A, lda, ta, B, ldb, C, ldc, M, N, K, vec, stream);
   else if (bm == 64 && bn == 128) launch_sgemm<64, 128, 16, 4, 8>(A, lda, ta, B, ldb, C, ldc, M, N, K, vec, stream);

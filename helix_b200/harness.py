@@ -200,14 +200,21 @@ def profile_fp16(fast=False, progress=None):
     return d
 
 
+def sgemm_key_to_cfg(key):
+    """(BM, BN, BK, TM, TN, stages, 0, 0) -> library configuration (stages 0 reads as the 2-buffer kernel)."""
+    bm, bn, bk, tm, tn = key[:5]
+    return ops.make_cfg(OP_GEMM_F32, tile_m=bm, tile_n=bn, tile_k=bk, thread_m=tm, thread_n=tn,
+                        stages=(key[5] if len(key) > 5 and key[5] else 2))
+
+
 def profile_fp32(fast=False, progress=None):
     require_gpu()
     sms = ops.device_info().sm_count
     d = {("sm_count",): sms}
     size = 1024 if fast else 2048
     for key in costmodel.sgemm_keys():
-        bm, bn, bk, tm, tn = key[:5]
-        c = ops.make_cfg(OP_GEMM_F32, tile_m=bm, tile_n=bn, tile_k=bk, thread_m=tm, thread_n=tn)
+        bm, bn, bk = key[:3]
+        c = sgemm_key_to_cfg(key)
         try:
             t = time_gemm_f32(size, size, size, c)
             tiles = -(-size // bm) * -(-size // bn)
@@ -238,6 +245,40 @@ def gemm_f16_result(prof_dict, M, N, K, batch=None):
     return cost_ms, 2.0 * M * N * K * (batch or 1) / 1e9 / cost_ms
 
 
+def time_key_f16(key, M, N, K):
+    """Seconds of one fp16 GEMM under the dictionary key `key` (a GEMV key runs the GEMV kernel; it needs
+    min(M, N) <= 8).  What the reference's ablation scripts do by spawning one executable per candidate
+    (scripts/Ampere_FP16/candidate_performance_curve.py:22-31)."""
+    require_gpu()
+    Kp = (K + 7) // 8 * 8
+    if key[0] == 0:
+        rows, m, transposed = (N, M, False) if M <= N else (M, N, True)
+        if m > 8:
+            raise ValueError("the GEMV kernel takes at most 8 right-hand sides")
+        return time_gemv_f16(rows, Kp, m, key_to_cfg(key), transposed)
+    return time_gemm_f16(M, N, Kp, key_to_cfg(key))
+
+
+def gemv_passes_time(M, N, K, cfg=None):
+    """Seconds of y[M,N] = x[M,K] W[N,K]^T done by the GEMV kernel alone: ceil(M/8) launches of at most 8
+    right-hand sides each, timed as one chain (the reference's gemv executable loops over M itself,
+    scripts/Ampere_FP16/TensorCore_CUDACore_Adaptive.py:48-54).  Pass a GEMV `cfg` to keep the library
+    from serving 3..8 right-hand sides with the tensor-core kernel."""
+    require_gpu()
+    Kp = (K + 7) // 8 * 8
+    nbuf = int(ROTATE_BYTES // (2.0 * N * Kp)) + 1
+    x = _randn((M, Kp), 1.0)
+    chains = []
+    for _ in range(nbuf):
+        w = _randn((N, Kp), 0.02)
+        y = torch.empty((M, N), device="cuda", dtype=torch.float16)
+        for m0 in range(0, M, 8):
+            m1 = min(M, m0 + 8)
+            chains.append(ops.launch_gemv_f16(w, x[m0:m1], y[m0:m1], cfg))
+    avg, _, _ = ops.time_launches(chains, warmup=3, iters=20, use_graph=True)
+    return avg * (-(-M // 8))
+
+
 def conv_f16_result(prof_dict, batch, IC, H, W, OC, kH, kW, stride, pad):
     """(cost_ms, tflops) of one NHWC convolution as a single implicit GEMM
     (get_Ampere_FP16_conv_Helix_result, Ampere_FP16_conv.py:431-446: im2col time + GEMM time)."""
@@ -258,8 +299,7 @@ def gemm_f32_result(prof_dict, M, N, K):
     key = costmodel.sgemm_cost_model(prof_dict, M, N, K)
     if key is None:
         raise RuntimeError("empty cost-model dictionary: run profile_template.py -b Ampere_FP32 first")
-    bm, bn, bk, tm, tn = key[:5]
-    t = time_gemm_f32(M, N, K, ops.make_cfg(OP_GEMM_F32, tile_m=bm, tile_n=bn, tile_k=bk, thread_m=tm, thread_n=tn))
+    t = time_gemm_f32(M, N, K, sgemm_key_to_cfg(key))
     cost_ms = t * 1e3
     return cost_ms, 2.0 * M * N * K / 1e9 / cost_ms
 

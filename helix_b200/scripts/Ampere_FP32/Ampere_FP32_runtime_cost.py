@@ -19,8 +19,7 @@ def get_Helix_runtime_cost(prof_dict, M, N, K):
     for i in range(100):
         best_config = cost_model(prof_dict, M, N, K)
     T2 = time.perf_counter()
-    bm, bn, bk, tm, tn = best_config[:5]
-    cost = harness.time_gemm_f32(M, N, K, ops.make_cfg(OP_GEMM_F32, tile_m=bm, tile_n=bn, tile_k=bk, thread_m=tm, thread_n=tn))
+    cost = harness.time_gemm_f32(M, N, K, harness.sgemm_key_to_cfg(best_config))
     return (T2 - T1) / 100 / 1000, cost
 
 

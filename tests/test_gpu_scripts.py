@@ -70,3 +70,35 @@ def test_fp32_backend_profile_and_sweep(workdir):
     _run(workdir, "changed_profile.py", "-b", "Ampere_FP32")
     out = _run(workdir, "benchmark_op_level_eval.py", "-o", "GEMM", "-b", "Ampere_FP32", "-s", "Helix", "--limit", "2")
     assert sum("Helix:" in l for l in out.splitlines()) == 2
+
+
+def test_ablation_scripts_run_on_the_profiled_dictionary(workdir):
+    """GEMV <-> tensor-core crossover, candidate curve and Oracle/Default/Static comparison
+    (reference: TensorCore_CUDACore_Adaptive.py:65-76, candidate_performance_curve.py:6-31,
+    benchmark_Ampere_FP16_performance_comparison.py:100-113)."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, SCRIPTS)
+    import importlib
+    from helix_b200 import costmodel
+    adap = importlib.import_module("Ampere_FP16.TensorCore_CUDACore_Adaptive")
+    curve = importlib.import_module("Ampere_FP16.candidate_performance_curve")
+    comp = importlib.import_module("Ampere_FP16.benchmark_Ampere_FP16_performance_comparison")
+    d = costmodel.load(str(workdir / "build" / "prof_dict" / "Ampere_FP16_cost_model.dict"))
+    lines = []
+    rows = adap.adaptive_table(d, [(1, 4096, 1024), (8, 4096, 1024), (16, 4096, 1024)], out=lines.append)
+    assert lines[0].startswith("1x4096x1024: Helix ") and " Gemv " in lines[0] and " GEMM " in lines[0]
+    for M, N, K, helix, gemv, gemm in rows:
+        assert helix > 0 and gemv > 0 and gemm > 0
+        assert helix >= 0.7 * max(gemv, gemm), (M, helix, gemv, gemm)      # the pick is near the better kernel
+    assert rows[0][4] > rows[0][5]                # one right-hand side: the GEMV kernel wins
+    assert rows[2][5] > rows[2][4]                # sixteen: the tensor-core kernel wins
+    lines = []
+    best_id, cand = curve.get_all_candidate_performance(d, 128, 512, 1000, out=lines.append)
+    assert lines[0].startswith("Best candidate id: ") and len(cand) >= 8 and lines[1].startswith("candidate id: ")
+    top = max(c[2] for c in cand)
+    assert dict((c[0], c[2]) for c in cand)[best_id] >= 0.6 * top
+    lines = []
+    (row,) = comp.performance_comparison(d, [(1024, 1024, 1024)], out=lines.append)
+    assert "Helix_Oracle:" in lines[0] and "Helix_Static2:" in lines[0]
+    _, _, _, oracle, default, s1, s2 = row
+    assert oracle >= 0.97 * max(default, s1, s2) and default >= 0.75 * oracle

@@ -289,3 +289,31 @@ def test_nsplit_gather_assembles_the_full_product_world_size_2(tmp_path):
     assert [o[0] for o in outs] == ["0", "1"]
     assert (outs[0][1], outs[0][2], outs[1][1], outs[1][2]) == ("0", "256", "256", "700")
     assert outs[0][3] == "1" and outs[1][3] == "1"
+
+
+# ----------------------------------------------------------------------------- ablation scripts: selection policies
+def test_ablation_selection_policies_on_a_synthetic_dictionary():
+    sys.path.insert(0, SCRIPTS)
+    try:
+        comp = importlib.import_module("Ampere_FP16.benchmark_Ampere_FP16_performance_comparison")
+        adap = importlib.import_module("Ampere_FP16.TensorCore_CUDACore_Adaptive")
+        curve = importlib.import_module("Ampere_FP16.candidate_performance_curve")
+    finally:
+        sys.path.remove(SCRIPTS)
+    d = synthetic_dict()
+    # Static1 never leaves the plain one-CTA kernel; Static2 does not look at the shape
+    for shape in [(4096, 4096, 4096), (16, 11008, 4096), (300, 700, 2048)]:
+        k1 = comp.cost_model_static1(d, *shape)
+        assert k1[0] != 0 and k1[3] == 1 and k1[4] == 0 and k1[5] == 0
+    assert comp.cost_model_static2(d, 4096, 4096, 4096) == comp.cost_model_static2(d, 8192, 8192, 2048)
+    assert comp.cost_model(d, 4096, 4096, 4096) == costmodel.cost_model(d, 4096, 4096, 4096)
+    # GEMV keys are the pick for one right-hand side and never when they are filtered out
+    assert adap.cost_model(d, 1, 4096, 1024)[0] == 0
+    assert adap.cost_model_without_gemv(d, 1, 4096, 1024)[0] != 0
+    assert adap.cost_model_gemv_only(d, 16, 4096, 1024)[0] == 0
+    # candidates: ids count kernel keys in dictionary order; GEMV keys only for M <= 8; the best is the model's pick
+    cand = curve.candidates(d, 476, 1024, 1024)
+    ids = [c[0] for c in cand]
+    assert ids == sorted(ids) and all(c[1][0] != 0 for c in cand)
+    assert min(cand, key=lambda c: c[2])[1] == costmodel.cost_model(d, 476, 1024, 1024)
+    assert any(c[1][0] == 0 for c in curve.candidates(d, 4, 1024, 1024))
