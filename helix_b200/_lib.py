@@ -87,6 +87,7 @@ SIGNATURES = {
     "helix_gemm_f32_host": (_I, [_P, _P, _P, _I, _I, _I]),
     "helix_conv2d_f16_nhwc_host": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I]),
     "helix_gemv_f16_static": (_I, [_P, _L, _P, _L, _P, _L, _L, _I, _I, _I, _I, _P]),
+    "helix_probe_ffma_f32": (_I, [_I, _PD, _P]),
     "helix_launch_count": (_L, []),
     "helix_trace_buffer": (_I, [_P, _Z]),
     "helix_trace_words_per_cta": (_I, []),

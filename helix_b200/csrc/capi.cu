@@ -514,6 +514,16 @@ int helix_gemv_f16_static(const void* W, int64_t ldw, const void* X, int64_t ldx
   return st;
 }
 
+int helix_probe_ffma_f32(int rounds, double* tflops, void* stream) {
+  helix_devinfo_t info;
+  const int rc = current_device(&info, false);
+  if (rc != HELIX_OK) return rc;
+  int64_t n = 0;
+  const int st = helix::ffma_probe(rounds, info.sm_count, tflops, static_cast<cudaStream_t>(stream), &n);
+  g_launches += n;
+  return st;
+}
+
 int64_t helix_launch_count(void) { return g_launches.load(); }
 
 int helix_trace_buffer(void* device_buf, size_t bytes) {

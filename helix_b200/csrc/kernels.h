@@ -20,6 +20,9 @@ int gemv_f16_static_launch(const void* W, int64_t ldw, const void* X, int64_t ld
                            int64_t ldy_inner, int rows, int K, int m, int split_k, int sm_count,
                            cudaStream_t stream, int64_t* launches);
 
+// ---- ffma_probe.cu
+int ffma_probe(int rounds, int sm_count, double* tflops, cudaStream_t stream, int64_t* launches);
+
 // ---- sgemm_f32.cu
 int sgemm_f32_num_configs();
 void sgemm_f32_get_config(int idx, helix_cfg_t* out);

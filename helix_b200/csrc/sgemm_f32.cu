@@ -474,9 +474,8 @@ static int sgemm_cfg_ctas_per_sm(const SgemmCfg& c) {
   return (c.bm == 128 && c.bn == 128) ? 2 : (c.bm * c.bn >= 8192 ? 3 : 4);
 }
 
-// The configuration with the smallest estimate of waves * work per tile / rate; a wave holds
-// ctas_per_sm tiles on every SM, and an SM that holds fewer CTAs than it could runs them slower
-// (less latency hiding), which the estimate charges as a 25 % penalty for a single resident CTA.
+// The configuration with the smallest work on the busiest SM (tiles it runs x tile area / rate); a wave
+// holds ctas_per_sm tiles on every SM.
 void sgemm_f32_default_config(int M, int N, int sm_count, helix_cfg_t* out) {
   int pick = 0;
   double best = 1e300;
@@ -488,9 +487,7 @@ void sgemm_f32_default_config(int M, int N, int sm_count, helix_cfg_t* out) {
     const int64_t waves = (tiles + slots - 1) / slots;
     // CTAs on the busiest SM over the whole run, in units of tile work
     const int64_t busiest = (waves - 1) * per_sm + ((tiles - (waves - 1) * slots) + sm_count - 1) / sm_count;
-    double rate = sgemm_cfg_rate(c);
-    if (tiles <= sm_count) rate *= 0.75;
-    const double t = (double)busiest * c.bm * c.bn / rate;
+    const double t = (double)busiest * c.bm * c.bn / sgemm_cfg_rate(c);
     if (t < best) { best = t; pick = i; }
   }
   sgemm_f32_get_config(pick, out);

@@ -49,7 +49,7 @@ def time_gemm_f16(M, N, K, cfg=None, batch=None, iters=20):
     b = batch or 1
     bytes_ = 2.0 * b * (M * K + N * K + M * N)
     flops = 2.0 * b * M * N * K
-    nbuf = 1 if flops / bytes_ > 300 else int(ROTATE_BYTES // bytes_) + 1
+    nbuf = 1 if flops / bytes_ > costmodel.ROTATE_INTENSITY else int(ROTATE_BYTES // bytes_) + 1
     sa, sb, sc = ((M, K), (N, K), (M, N)) if batch is None else ((b, M, K), (b, N, K), (b, M, N))
     s = 1.0 / math.sqrt(K)
     bufs = [(_randn(sa, s), _randn(sb, s), torch.empty(sc, device="cuda", dtype=torch.float16)) for _ in range(nbuf)]
@@ -274,7 +274,9 @@ def gemv_passes_time(M, N, K, cfg=None):
         y = torch.empty((M, N), device="cuda", dtype=torch.float16)
         for m0 in range(0, M, 8):
             m1 = min(M, m0 + 8)
-            chains.append(ops.launch_gemv_f16(w, x[m0:m1], y[m0:m1], cfg))
+            l = ops.launch_gemv_f16(w, x[m0:m1], y[m0:m1], cfg)
+            l.flags = LAUNCH_INDEPENDENT          # passes write disjoint rows of y and only read W and x
+            chains.append(l)
     avg, _, _ = ops.time_launches(chains, warmup=3, iters=20, use_graph=True)
     return avg * (-(-M // 8))
 

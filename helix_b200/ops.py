@@ -308,5 +308,12 @@ def capture_timeline(launch, warm=2):
     return buf.cpu().numpy()
 
 
+def probe_ffma_f32(rounds=2000):
+    """TFLOP/s of register-resident FFMA in the fp32 GEMM's 8x8 block pattern on the current device."""
+    out = ctypes.c_double(0.0)
+    check(_lib.load().helix_probe_ffma_f32(int(rounds), ctypes.byref(out), _stream()), "helix_probe_ffma_f32")
+    return out.value
+
+
 def launch_count():
     return int(_lib.load().helix_launch_count())

@@ -227,6 +227,14 @@ int helix_gemv_f16_static(const void* W, int64_t ldw, const void* X, int64_t ldx
 int helix_trace_buffer(void* device_buf, size_t bytes);
 int helix_trace_words_per_cta(void);
 
+/* Calibration probe without a reference counterpart (the reference reports TFLOP/s only,
+ * sgemm.cu:655-660): the FFMA rate, in TFLOP/s, that the current device sustains on the register
+ * pattern of the fp32 GEMM's inner loop (8 x 8 outer-product block per thread, two 256-thread CTAs
+ * per SM, no memory traffic), timed with events on `stream` over `rounds` x 1024 FFMA per thread.
+ * Blocks until the probe has run.  The fp32 GEMM is rated against this figure as well as against
+ * SMs x 128 lanes x 2 x clock. */
+int helix_probe_ffma_f32(int rounds, double* tflops, void* stream);
+
 /* Number of kernel launches this process has queued through the library (all ops). */
 int64_t helix_launch_count(void);
 
