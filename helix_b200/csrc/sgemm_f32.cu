@@ -219,7 +219,7 @@ struct SgemmPipeTraits {
   static constexpr int kA4 = BM * BK / 4 / kThreads;           // 16-byte copies of A per thread per slab (K x M A)
   static constexpr int kA1 = BM * BK / kThreads;               // 4-byte copies of A per thread per slab (M x K A)
   static constexpr int kB4 = BN * BK / 4 / kThreads;
-  static_assert(TM % 4 == 0 && TN % 4 == 0 && BK % 4 == 0, "4-wide quads");
+  static_assert(TM % 4 == 0 && TN % 4 == 0 && BK % 8 == 0, "4-wide quads, steps unrolled by eight");
   static_assert(kThreadsM % 4 == 0 && kThreadsN % 8 == 0, "a warp covers 4 x 8 threads of the grid");
   static_assert((BM * BK / 4) % kThreads == 0 && (BN * BK / 4) % kThreads == 0, "whole copies per thread");
 };
@@ -319,8 +319,7 @@ sgemm_f32_pipe_kernel(const float* __restrict__ A, int64_t lda, const float* __r
     } else {
 #pragma unroll
       for (int v = 0; v < T::kA1; ++v) {
-        const int f = v * NT + tid;
-        const int mm = f / BK, kk = f % BK;
+        const int mm = a_r + v * kAPassRows, kk = a_c;
         const int gk = k0 + kk, gm = m0 + mm;
         const int bytes = (gm < M && gk < K) ? 4 : 0;
         const float* src = bytes ? A + (int64_t)gm * lda + gk : A;
@@ -358,23 +357,41 @@ sgemm_f32_pipe_kernel(const float* __restrict__ A, int64_t lda, const float* __r
     }
     const float* a = sA + stage * T::kAStage;
     const float* b = sB + stage * T::kBStage;
-#pragma unroll
-    for (int kk = 0; kk < BK; ++kk) {
-      float av[TM], bv[TN];
+    // fragments of step kk + 1 are fetched into the other half of av / bv before the FFMAs of step kk
+    float av[2][TM], bv[2][TN];
+    auto fetch = [&](int kk, int h) {
 #pragma unroll
       for (int q = 0; q < TM / 4; ++q) {
         const float4 t = *reinterpret_cast<const float4*>(&a[kk * T::kARow + (q * T::kThreadsM + tm) * 4]);
-        av[q * 4 + 0] = t.x; av[q * 4 + 1] = t.y; av[q * 4 + 2] = t.z; av[q * 4 + 3] = t.w;
+        av[h][q * 4 + 0] = t.x; av[h][q * 4 + 1] = t.y; av[h][q * 4 + 2] = t.z; av[h][q * 4 + 3] = t.w;
       }
 #pragma unroll
       for (int q = 0; q < TN / 4; ++q) {
         const float4 t = *reinterpret_cast<const float4*>(&b[kk * T::kBRow + (q * T::kThreadsN + tn) * 4]);
-        bv[q * 4 + 0] = t.x; bv[q * 4 + 1] = t.y; bv[q * 4 + 2] = t.z; bv[q * 4 + 3] = t.w;
+        bv[h][q * 4 + 0] = t.x; bv[h][q * 4 + 1] = t.y; bv[h][q * 4 + 2] = t.z; bv[h][q * 4 + 3] = t.w;
       }
+    };
+    // eight steps are unrolled (512 FFMA of an 8 x 8 block, 8 KB of code): a fully unrolled slab of 32
+    // steps is 32 KB of FFMA and no longer sits in the instruction cache next to the schedulers
+    fetch(0, 0);
 #pragma unroll
-      for (int i = 0; i < TM; ++i)
+    for (int k8 = 0; k8 < BK; k8 += 8) {
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+      for (int u = 0; u < 8; ++u) {
+        const int kk = k8 + u;
+        if (u < 7 || k8 + 8 < BK) fetch(kk + 1, (u + 1) & 1);
+        // zigzag over stripes of two rows: every FFMA shares one operand with its predecessor,
+        // alternately the B and the A value (a0b0 a1b0 a1b1 a0b1 a0b2 ...)
+#pragma unroll
+        for (int i2 = 0; i2 < TM; i2 += 2)
+#pragma unroll
+          for (int jj = 0; jj < TN; ++jj) {
+            const int j = (i2 & 2) ? TN - 1 - jj : jj;
+            const int ia = i2 + (jj & 1), ib = i2 + 1 - (jj & 1);
+            acc[ia][j] = fmaf(av[u & 1][ia], bv[u & 1][j], acc[ia][j]);
+            acc[ib][j] = fmaf(av[u & 1][ib], bv[u & 1][j], acc[ib][j]);
+          }
+      }
     }
     if (++stage == STAGES) stage = 0;
   }
@@ -535,6 +552,8 @@ int sgemm_f32_launch(const helix_cfg_t* cfg, const float* A, int64_t lda, int tr
   if (stages >= 3 && vec) {
     cudaError_t e = cudaErrorInvalidValue;
     if (bm == 128 && bn == 128 && bk == 16) e = launch_sgemm_pipe<128, 128, 16, 8, 8, 4, 2>(A, lda, ta, B, ldb, C, ldc, M, N, K, stream);
+    else if (bm == 128 && bn == 128 && bk == 8 && stages == 4) e = launch_sgemm_pipe<128, 128, 8, 8, 8, 4, 2>(A, lda, ta, B, ldb, C, ldc, M, N, K, stream);
+    else if (bm == 128 && bn == 128 && bk == 8) e = launch_sgemm_pipe<128, 128, 8, 8, 8, 3, 2>(A, lda, ta, B, ldb, C, ldc, M, N, K, stream);
     else if (bm == 128 && bn == 128 && bk == 32) e = launch_sgemm_pipe<128, 128, 32, 8, 8, 3, 2>(A, lda, ta, B, ldb, C, ldc, M, N, K, stream);
     else if (bm == 128 && bn == 64 && bk == 16) e = launch_sgemm_pipe<128, 64, 16, 8, 4, 4, 2>(A, lda, ta, B, ldb, C, ldc, M, N, K, stream);
     else if (bm == 128 && bn == 64 && bk == 32) e = launch_sgemm_pipe<128, 64, 32, 8, 4, 3, 2>(A, lda, ta, B, ldb, C, ldc, M, N, K, stream);
