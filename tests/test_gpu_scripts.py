@@ -103,3 +103,51 @@ def test_ablation_scripts_run_on_the_profiled_dictionary(workdir):
     assert "Helix_Oracle:" in lines[0] and "Helix_Static2:" in lines[0]
     _, _, _, oracle, default, s1, s2 = row
     assert oracle >= 0.97 * max(default, s1, s2) and default >= 0.75 * oracle
+
+
+def test_op_level_list_sampled_parity_with_the_models_pick(workdir):
+    """Every 29th shape of the op-level GEMM list (plus the shapes whose K is no multiple of 8) computed with
+    the configuration the cost model picks -- GEMV keys included -- and checked against the oracle on sampled
+    rows: the sweep reports numbers for results that are right."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, SCRIPTS)
+    import numpy as np
+    import torch
+    from helix_b200 import costmodel, harness, ops
+    from oracle import api as oracle
+    from tests import util
+    from utils.get_benchmark_shape_list import get_gemm_op_MNKList
+    oracle.build()
+    d = costmodel.load(str(workdir / "build" / "prof_dict" / "Ampere_FP16_cost_model.dict"))
+    shapes = get_gemm_op_MNKList()
+    picked = shapes[::29] + [s for s in shapes if s[2] % 8][::7]
+    kinds = set()
+    for idx, (M, N, K) in enumerate(picked):
+        rng = np.random.default_rng(1000 + idx)
+        s = np.float32(1.0 / np.sqrt(K))
+        a = (rng.standard_normal((M, K), dtype=np.float32) * s).astype(np.float16)
+        b = (rng.standard_normal((N, K), dtype=np.float32) * s).astype(np.float16)
+        Kp = (K + 7) // 8 * 8                      # leading dimensions follow the 16-byte rule; zero columns add nothing
+        ad = torch.zeros((M, Kp), dtype=torch.float16, device="cuda")
+        bd = torch.zeros((N, Kp), dtype=torch.float16, device="cuda")
+        ad[:, :K] = torch.from_numpy(a).cuda()
+        bd[:, :K] = torch.from_numpy(b).cuda()
+        key = costmodel.cost_model(d, M, N, K)
+        cfg = harness.key_to_cfg(key)
+        if key[0] == 0:
+            kinds.add("gemv")
+            if M <= N:
+                out = torch.empty((M, N), dtype=torch.float16, device="cuda")
+                ops.run(ops.launch_gemv_f16(bd, ad, out, cfg))
+            else:
+                out = torch.empty((M, N), dtype=torch.float16, device="cuda")
+                ops.run(ops.launch_gemv_f16(ad, bd, out, cfg, out_transposed=True))
+        else:
+            kinds.add("pair" if key[3] == 2 else ("swap" if key[4] else ("streamk" if key[5] else "plain")))
+            out = ops.gemm_f16(ad, bd, cfg=cfg)
+        torch.cuda.synchronize()
+        ops.check_status()
+        rows = sorted({0, M // 3, M // 2, M - 1})
+        _, ref32 = oracle.hgemm_naive(np.ascontiguousarray(a[rows]), b)
+        util.assert_f16_close(out[rows].cpu().numpy(), ref32, f"{M}x{N}x{K} with {key}")
+    assert {"gemv", "pair"} <= kinds and len(kinds) >= 3, kinds
