@@ -151,3 +151,39 @@ def test_op_level_list_sampled_parity_with_the_models_pick(workdir):
         _, ref32 = oracle.hgemm_naive(np.ascontiguousarray(a[rows]), b)
         util.assert_f16_close(out[rows].cpu().numpy(), ref32, f"{M}x{N}x{K} with {key}")
     assert {"gemv", "pair"} <= kinds and len(kinds) >= 3, kinds
+
+
+def test_conv_op_level_list_sampled_parity_with_the_models_pick(workdir):
+    """Every 53rd layer of the op-level convolution list (3, 24, 32 ... 832 input channels, 1x1 to 11x11
+    filters, strides 1, 2, 4) run the way harness.time_conv_f16 runs it -- channels padded to a multiple of
+    8, the cost model's key -- with its first and last image checked against the oracle."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, SCRIPTS)
+    import numpy as np
+    import torch
+    from helix_b200 import costmodel, harness, ops
+    from oracle import api as oracle
+    from tests import util
+    from utils.get_benchmark_shape_list import get_conv_op_shape_list
+    oracle.build()
+    d = costmodel.load(str(workdir / "build" / "prof_dict" / "Ampere_FP16_cost_model.dict"))
+    for idx, (B, IC, H, W, OC, kH, kW, stride, pad) in enumerate(get_conv_op_shape_list()[::53]):
+        rng = np.random.default_rng(2000 + idx)
+        C = (IC + 7) // 8 * 8
+        x = np.zeros((B, H, W, C), np.float16)
+        w = np.zeros((OC, kH, kW, C), np.float16)
+        x[..., :IC] = rng.uniform(-1, 1, (B, H, W, IC)).astype(np.float16)
+        w[..., :IC] = (rng.standard_normal((OC, kH, kW, IC), dtype=np.float32) * np.float32((2.0 / (IC * kH * kW)) ** 0.5)).astype(np.float16)
+        Ho, Wo = ops.conv_out_hw(H, W, kH, kW, stride, pad)
+        M, N, K = B * Ho * Wo, OC, IC * kH * kW
+        as_gemm = kH == 1 and kW == 1 and stride == 1 and pad == 0
+        key = costmodel.cost_model(d, M, N, (K + 7) // 8 * 8, 1, conv=not as_gemm)
+        if key is None or key[0] == 0:
+            key = (costmodel.max_stages(128), 128, 128, 1, 0, 0)       # as harness.conv_f16_result falls back
+        y = ops.conv2d_f16_nhwc(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), stride, pad,
+                                cfg=harness.key_to_cfg(key, conv=True))
+        torch.cuda.synchronize()
+        ops.check_status()
+        for img in sorted({0, B - 1}):
+            _, y32 = oracle.conv2d_nhwc_f16(x[img:img + 1], w, stride, pad)
+            util.assert_f16_close(y[img:img + 1].cpu().numpy(), y32, f"conv {(B, IC, H, W, OC, kH, kW, stride, pad)} image {img} with {key}")
