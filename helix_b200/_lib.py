@@ -9,7 +9,7 @@ import os
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libhelix_b200.so")
 
-OP_GEMM_F16, OP_GEMV_F16, OP_CONV_F16, OP_GEMM_F32 = 0, 1, 2, 3
+OP_GEMM_F16, OP_GEMV_F16, OP_CONV_F16, OP_GEMM_F32, OP_CONV_F32 = 0, 1, 2, 3, 4
 
 STATUS_TEXT = {
     0: "ok", -1: "invalid argument", -2: "pointer or leading dimension not 16-byte aligned",
@@ -81,6 +81,7 @@ SIGNATURES = {
     "helix_gemv_f16": (_I, [ctypes.POINTER(Cfg), _P, _L, _P, _L, _P, _L, _L, _I, _I, _I, _P, _Z, _P, _P]),
     "helix_conv2d_f16_nhwc": (_I, [ctypes.POINTER(Cfg), _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _Z, _P, _P]),
     "helix_gemm_f32": (_I, [ctypes.POINTER(Cfg), _P, _L, _I, _P, _L, _P, _L, _I, _I, _I, _P, _P]),
+    "helix_conv2d_f32_nhwc": (_I, [ctypes.POINTER(Cfg), _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _Z, _P, _P]),
     "helix_time_launches": (_I, [ctypes.POINTER(Launch), _I, _I, _I, _I, _PD, _PD, _PD]),
     "helix_gemm_f16_host": (_I, [_P, _P, _P, _I, _I, _I]),
     "helix_gemv_f16_host": (_I, [_P, _P, _P, _I, _I, _I]),

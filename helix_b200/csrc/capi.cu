@@ -126,6 +126,13 @@ int dispatch(const helix_launch_t* l, void* status_dev, cudaStream_t stream) {
                                    static_cast<const float*>(l->b), l->ldb, static_cast<float*>(l->c), l->ldc, l->M,
                                    l->N, l->K, sms_of(info), stream, &n);
       break;
+    case HELIX_OP_CONV_F32: {
+      if ((rc = current_device(&info, false)) != HELIX_OK) return rc;
+      const helix::ConvGeom g = conv_geom(l->conv);
+      rc = helix::conv_f32_launch(cfg, static_cast<const float*>(l->a), static_cast<const float*>(l->b),
+                                  static_cast<float*>(l->c), g, l->ws, l->ws_bytes, sms_of(info), stream, &n);
+      break;
+    }
     default:
       return HELIX_ERR_INVALID;
   }
@@ -172,7 +179,8 @@ int helix_num_configs(int op) {
     case HELIX_OP_GEMM_F16:
     case HELIX_OP_CONV_F16: return helix::gemm_f16_num_configs();
     case HELIX_OP_GEMV_F16: return 5;  // split-K 1, 2, 4, 8, 16
-    case HELIX_OP_GEMM_F32: return helix::sgemm_f32_num_configs();
+    case HELIX_OP_GEMM_F32:
+    case HELIX_OP_CONV_F32: return helix::sgemm_f32_num_configs();
     default: return HELIX_ERR_INVALID;
   }
 }
@@ -201,7 +209,8 @@ int helix_get_config(int op, int idx, helix_cfg_t* out) {
       out->cta_group = 1;
       break;
     case HELIX_OP_GEMM_F32:
-      helix::sgemm_f32_get_config(idx, out);
+    case HELIX_OP_CONV_F32:
+      helix::sgemm_f32_get_config(idx, out);     // a convolution takes the GEMM's configurations as they are
       break;
   }
   return HELIX_OK;
@@ -232,6 +241,13 @@ int helix_default_config(const helix_launch_t* l, helix_cfg_t* out) {
     case HELIX_OP_GEMM_F32:
       helix::sgemm_f32_default_config(l->M, l->N, sms, out);
       return HELIX_OK;
+    case HELIX_OP_CONV_F32: {
+      const helix::ConvGeom g = conv_geom(l->conv);
+      const int64_t M = (int64_t)g.NB * g.Ho * g.Wo;
+      if (M <= 0 || M > 0x7fffffff || g.KO <= 0) return HELIX_ERR_INVALID;
+      helix::sgemm_f32_default_config((int)M, g.KO, sms, out);
+      return HELIX_OK;
+    }
     default:
       return HELIX_ERR_INVALID;
   }
@@ -261,6 +277,8 @@ size_t helix_workspace_bytes(const helix_launch_t* l) {
       const int split = have_cfg && l->cfg.split_k > 0 ? l->cfg.split_k : helix::gemv_f16_default_split(l->N, l->K, sms);
       return helix::gemv_f16_workspace_bytes(l->N, l->M, split);
     }
+    case HELIX_OP_CONV_F32:
+      return helix::conv_f32_workspace_bytes(conv_geom(l->conv));
     default:
       return 0;
   }
@@ -324,6 +342,21 @@ int helix_gemm_f32(const helix_cfg_t* cfg, const float* A, int64_t lda, int tran
   l.lda = lda; l.ldb = ldb; l.ldc = ldc;
   l.M = M; l.N = N; l.K = K;
   l.trans_a = trans_a;
+  return dispatch(&l, status_dev, static_cast<cudaStream_t>(stream));
+}
+
+int helix_conv2d_f32_nhwc(const helix_cfg_t* cfg, const float* x, const float* w, float* y, int N, int H, int W, int C,
+                          int KO, int R, int S, int stride, int pad, void* ws, size_t ws_bytes, void* status_dev,
+                          void* stream) {
+  helix_launch_t l;
+  std::memset(&l, 0, sizeof(l));
+  l.op = HELIX_OP_CONV_F32;
+  if (cfg) l.cfg = *cfg;
+  l.a = x; l.b = w; l.c = y;
+  const int geom[9] = {N, H, W, C, KO, R, S, stride, pad};
+  std::memcpy(l.conv, geom, sizeof(geom));
+  l.ws = ws;
+  l.ws_bytes = ws_bytes;
   return dispatch(&l, status_dev, static_cast<cudaStream_t>(stream));
 }
 

@@ -40,6 +40,10 @@ void gemm_f16_get_config(int idx, helix_cfg_t* out);
 // Fills *out with the library's default choice for the problem.
 void gemm_f16_default_config(int M, int N, int K, int batch, int sm_count, bool conv, helix_cfg_t* out);
 void conv_f16_default_config(const ConvGeom& g, int sm_count, helix_cfg_t* out);
+// ---- conv_f32.cu (column matrix + FFMA GEMM)
+size_t conv_f32_workspace_bytes(const ConvGeom& g);
+int conv_f32_launch(const helix_cfg_t* cfg, const float* x, const float* w, float* y, const ConvGeom& g, void* ws,
+                    size_t ws_bytes, int sm_count, cudaStream_t stream, int64_t* launches);
 // Per-CTA timeline capture shared by the one-CTA and the CTA-pair kernel (layout: helix_b200.h).
 constexpr int kTraceTiles = 20;   // work items with six stamps each
 constexpr int kTraceSlabs = 32;   // first K slabs of the CTA: request issued, data consumed

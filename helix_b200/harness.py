@@ -306,11 +306,30 @@ def gemm_f32_result(prof_dict, M, N, K):
     return cost_ms, 2.0 * M * N * K / 1e9 / cost_ms
 
 
-def conv_f32_result(prof_dict, batch, IC, H, W, OC, kH, kW, stride, pad):
-    """FP32 convolution = the reference's mapping conv -> GEMM dims (Ampere_FP32_conv.py:101-113); the
-    GEMM is timed on the mapped shape (an explicit fp32 im2col is not part of the tensor-core path)."""
+def time_conv_f32(batch, IC, H, W, OC, kH, kW, stride, pad, cfg=None, iters=10):
+    """Seconds of one true-fp32 NHWC convolution: weight transpose + column matrix + FFMA GEMM."""
+    x = torch.rand((batch, H, W, IC), device="cuda") * 2 - 1
+    w = torch.randn((OC, kH, kW, IC), device="cuda") * math.sqrt(2.0 / (IC * kH * kW))
     Ho, Wo = ops.conv_out_hw(H, W, kH, kW, stride, pad)
-    return gemm_f32_result(prof_dict, batch * Ho * Wo, OC, IC * kH * kW)
+    y = torch.empty((batch, Ho, Wo, OC), device="cuda")
+    l = ops.launch_conv2d_f32(x, w, y, stride, pad, cfg)
+    avg, _, _ = ops.time_launches([l] * 2, warmup=2, iters=iters, use_graph=True)
+    return avg
+
+
+def conv_f32_result(prof_dict, batch, IC, H, W, OC, kH, kW, stride, pad):
+    """(cost_ms, tflops) of one fp32 convolution the reference's way: explicit column matrix, then the GEMM on
+    M = B*Ho*Wo, N = OC, K = IC*kH*kW with the configuration the cost model picks for that shape
+    (Ampere_FP32_conv.py:101-113); the time covers all three kernels."""
+    require_gpu()
+    Ho, Wo = ops.conv_out_hw(H, W, kH, kW, stride, pad)
+    M, N, K = batch * Ho * Wo, OC, IC * kH * kW
+    key = costmodel.sgemm_cost_model(prof_dict, M, N, K)
+    if key is None:
+        raise RuntimeError("empty cost-model dictionary: run profile_template.py -b Ampere_FP32 first")
+    t = time_conv_f32(batch, IC, H, W, OC, kH, kW, stride, pad, sgemm_key_to_cfg(key))
+    cost_ms = t * 1e3
+    return cost_ms, 2.0 * M * N * K / 1e9 / cost_ms
 
 
 # ----------------------------------------------------------------------------- sharded-sweep workers

@@ -210,6 +210,35 @@ def launch_conv2d_f16(x, w, out, stride, pad, cfg=None, ws=None):
     return _finish(l, cfg, ws)
 
 
+def launch_conv2d_f32(x, w, out, stride, pad, cfg=None, ws=None):
+    """x[N,H,W,C], w[KO,R,S,C] -> out[N,Ho,Wo,KO], true fp32 (column matrix + FFMA GEMM in the workspace)."""
+    _require_cuda(x, w, out)
+    assert x.dtype == w.dtype == out.dtype == torch.float32
+    assert x.is_contiguous() and w.is_contiguous() and out.is_contiguous()
+    N, H, W, C = x.shape
+    KO, R, S, C2 = w.shape
+    assert C2 == C
+    Ho, Wo = conv_out_hw(H, W, R, S, stride, pad)
+    assert tuple(out.shape) == (N, Ho, Wo, KO)
+    l = Launch()
+    l.op = _lib.OP_CONV_F32
+    for i, v in enumerate((N, H, W, C, KO, R, S, stride, pad)):
+        l.conv[i] = v
+    l.a, l.b, l.c = x.data_ptr(), w.data_ptr(), out.data_ptr()
+    l._refs = (x, w, out)
+    return _finish(l, cfg, ws)
+
+
+def conv2d_f32_nhwc(x, w, stride=1, pad=0, out=None, cfg=None):
+    N, H, W, _ = x.shape
+    KO, R, S, _ = w.shape
+    Ho, Wo = conv_out_hw(H, W, R, S, stride, pad)
+    if out is None:
+        out = torch.empty((N, Ho, Wo, KO), dtype=torch.float32, device=x.device)
+    run(launch_conv2d_f32(x, w, out, stride, pad, cfg))
+    return out
+
+
 def launch_gemm_f32(a, b, out, trans_a=False, cfg=None):
     """A[M,K] (or [K,M] with trans_a) x B[K,N] -> out[M,N], fp32 FFMA."""
     _require_cuda(a, b, out)

@@ -47,7 +47,8 @@ typedef enum helix_op {
   HELIX_OP_GEMM_F16 = 0, /* tcgen05 tensor-core GEMM, fp16 in, fp32 accumulate, fp16 out  */
   HELIX_OP_GEMV_F16 = 1, /* memory-bound SIMT GEMV for 1..8 right-hand sides              */
   HELIX_OP_CONV_F16 = 2, /* implicit-GEMM NHWC convolution on the same tensor-core path   */
-  HELIX_OP_GEMM_F32 = 3  /* SIMT FFMA GEMM, true fp32                                     */
+  HELIX_OP_GEMM_F32 = 3, /* SIMT FFMA GEMM, true fp32                                     */
+  HELIX_OP_CONV_F32 = 4  /* true-fp32 NHWC convolution: column matrix + the FFMA GEMM      */
 } helix_op_t;
 
 /* Replaces the queried-nowhere literal `108` (A100 SM count) of the reference's
@@ -185,6 +186,18 @@ int helix_conv2d_f16_nhwc(const helix_cfg_t* cfg, const void* x, const void* w, 
 int helix_gemm_f32(const helix_cfg_t* cfg, const float* A, int64_t lda, int trans_a,
                    const float* B, int64_t ldb, float* C, int64_t ldc, int M, int N, int K,
                    void* status_dev, void* stream);
+
+/* y[N,Ho,Wo,KO] = conv2d(x[N,H,W,C], w[KO,R,S,C]) in true fp32, zero padding: a column matrix
+ * col[N*Ho*Wo][R*S*C] and the transposed weights are written into the caller's workspace
+ * (helix_workspace_bytes; 256-byte aligned), then the FFMA GEMM of helix_gemm_f32 runs on them, so
+ * every output is one fmaf chain over (r, s, c) ascending.  Replaces the im2col executable plus
+ * sgemm executable pair of get_Ampere_FP32_conv_Helix_result
+ * (scripts/Ampere_FP32/Ampere_FP32_conv.py:101-113, src_template/Ampere_FP32/im2col.cu:37-97).
+ * A 1x1, stride-1, unpadded convolution needs no column matrix.  cfg: a HELIX_OP_GEMM_F32
+ * configuration or NULL. */
+int helix_conv2d_f32_nhwc(const helix_cfg_t* cfg, const float* x, const float* w, float* y,
+                          int N, int H, int W, int C, int KO, int R, int S, int stride, int pad,
+                          void* ws, size_t ws_bytes, void* status_dev, void* stream);
 
 /* Time `count` launches round-robin: `warmup` untimed rounds, then `iters` timed rounds between
  * two CUDA events on a private stream; *avg_s is seconds per launch.  Distinct buffers per

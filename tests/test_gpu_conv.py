@@ -182,3 +182,47 @@ def test_conv_stream_k(oracle, geom, bn):
     if B > 3:
         _, y32 = oracle.conv2d_nhwc_f16(x[-1:], w, stride, pad)
         util.assert_f16_close(got[-1:], y32, f"stream-K conv {geom} last image")
+
+
+# ----------------------------------------------------------------------------- true-fp32 convolution
+@pytest.mark.parametrize("geom", [
+    (2, 16, 12, 12, 24, 3, 3, 1, 1),       # 3x3 same-size
+    (2, 3, 37, 41, 20, 7, 7, 2, 3),        # 3 input channels: scalar column kernel, K = 147 (unaligned GEMM path)
+    (3, 32, 9, 9, 40, 1, 1, 1, 0),         # 1x1: the activations are the column matrix
+    (2, 8, 15, 17, 12, 5, 5, 2, 2),        # 5x5 stride 2
+    (1, 20, 10, 10, 130, 3, 3, 3, 0),      # stride 3, more output channels than one tile
+    (2, 64, 14, 14, 64, 1, 1, 2, 0),       # strided 1x1 needs the column matrix
+])
+def test_conv_f32_matches_the_fmaf_chain(oracle, geom):
+    """Column matrix + FFMA GEMM: every output is the fmaf chain over (r, s, c) ascending, bit for bit, and
+    within 1e-5 of the multiply-then-add loop."""
+    B, C, H, W, OC, kh, kw, stride, pad = geom
+    rng = np.random.default_rng(sum(geom))
+    x = rng.uniform(-1, 1, (B, H, W, C)).astype(np.float32)
+    w = (rng.standard_normal((OC, kh, kw, C)) * (2.0 / (C * kh * kw)) ** 0.5).astype(np.float32)
+    y = ops.conv2d_f32_nhwc(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), stride, pad)
+    torch.cuda.synchronize()
+    ops.check_status()
+    got = y.cpu().numpy()
+    want = oracle.conv2d_nhwc_f32(x, w, stride, pad, fma=True)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), geom
+    util.assert_f32_close(got, oracle.conv2d_nhwc_f32(x, w, stride, pad, fma=False), f"fp32 conv {geom}")
+
+
+def test_conv_f32_workspace_contract():
+    from helix_b200._lib import HelixError, Launch, OP_CONV_F32, load
+    import ctypes
+    x = torch.rand((2, 10, 10, 8), device="cuda")
+    w = torch.rand((16, 3, 3, 8), device="cuda")
+    y = torch.empty((2, 10, 10, 16), device="cuda")
+    l = ops.launch_conv2d_f32(x, w, y, 1, 1)
+    need = load().helix_workspace_bytes(ctypes.byref(l))
+    M, K = 2 * 10 * 10, 3 * 3 * 8
+    assert need >= (M * K + K * 16) * 4 and need % 256 == 0
+    l.ws_bytes = need - 256
+    with pytest.raises(HelixError) as e:
+        ops.run(l)
+    assert e.value.status == -3                                   # workspace missing or too small
+    l1 = ops.launch_conv2d_f32(torch.rand((1, 6, 6, 8), device="cuda"), torch.rand((4, 1, 1, 8), device="cuda"),
+                               torch.empty((1, 6, 6, 4), device="cuda"), 1, 0)
+    assert load().helix_workspace_bytes(ctypes.byref(l1)) == 256  # 1x1: only the transposed weights (8 x 4 floats)

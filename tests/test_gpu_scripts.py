@@ -70,6 +70,8 @@ def test_fp32_backend_profile_and_sweep(workdir):
     _run(workdir, "changed_profile.py", "-b", "Ampere_FP32")
     out = _run(workdir, "benchmark_op_level_eval.py", "-o", "GEMM", "-b", "Ampere_FP32", "-s", "Helix", "--limit", "2")
     assert sum("Helix:" in l for l in out.splitlines()) == 2
+    out = _run(workdir, "benchmark_op_level_eval.py", "-o", "Conv", "-b", "Ampere_FP32", "-s", "Helix", "--limit", "2")
+    assert sum("Helix:" in l for l in out.splitlines()) == 2      # column matrix + FFMA GEMM, all three kernels timed
 
 
 def test_ablation_scripts_run_on_the_profiled_dictionary(workdir):
