@@ -202,22 +202,31 @@ sgemm_f32_kernel(const float* __restrict__ A, int64_t lda, const float* __restri
 // Pipelined variant for 16-byte-aligned operands: cp.async straight from global to shared memory
 // through a ring of STAGES slabs (no register staging, one __syncthreads per slab, loads issued
 // STAGES-1 slabs ahead).  Both operands are staged K-major as above.  B and a K x M A (trans_a)
-// arrive as 16-byte copies; a row-major M x K A is transposed by the copy itself, one 4-byte
-// cp.async per element (consecutive threads take consecutive k of one row, so a warp still reads
-// whole 64-byte runs of A), which costs a few more copy instructions per slab and no registers.
+// arrive as 16-byte copies.  A row-major M x K A with register blocks of up to 32 accumulators arrives
+// as 8-byte copies of two consecutive k and is staged as k pairs ([BK/2][BM + 2][2]): the eight floats
+// a thread needs for a quad of rows and one k pair are contiguous, so it reads them with two 16-byte
+// loads per pair -- the same number of shared loads per FFMA as the K-major layout, without a
+// transposing copy per element (1024^3, 128 x 64 tile: 66.1 -> 60.1 us).  With 8 x 8 blocks the pair
+// fragments cost 16 more registers and the kernel gets slower (4096^3: 2615 -> 2880 us), so there the
+// copy itself transposes, one 4-byte cp.async per element into the K-major layout.
 // Rows outside the matrix and the K tail are zero-filled by the copy's source size.
 template <int BM, int BN, int BK, int TM, int TN, int STAGES, bool TRANS_A>
 struct SgemmPipeTraits {
   static constexpr int kThreadsM = BM / TM;
   static constexpr int kThreadsN = BN / TN;
   static constexpr int kThreads = kThreadsM * kThreadsN;
-  static constexpr int kARow = BM + 4;                         // floats per shared row (one k) of A
+  // K x M A: staged K-major, one row of BM + 4 floats per k.  M x K A: staged as k pairs, [BK/2][BM + 2][2]
+  // (the two k of an 8-byte copy stay together; BM + 2 = 2 mod 16 spreads the copies of a warp over all banks)
+  static constexpr bool kPair = !TRANS_A && TM * TN <= 32;   // with 64 accumulators the pair fragments cost too many registers (measured slower)
+  static constexpr int kARow = BM + 4;                         // floats per shared row (one k) of A, K-major
+  static constexpr int kARowP = BM + 2;                        // rows (m) per k pair, pair-major
   static constexpr int kBRow = BN + 4;
-  static constexpr int kAStage = BK * kARow;                   // floats per stage
+  static constexpr int kAStage = kPair ? BK * kARowP : BK * kARow;   // floats per stage
   static constexpr int kBStage = BK * kBRow;
   static constexpr int kSmemBytes = STAGES * (kAStage + kBStage) * 4;
   static constexpr int kA4 = BM * BK / 4 / kThreads;           // 16-byte copies of A per thread per slab (K x M A)
-  static constexpr int kA1 = BM * BK / kThreads;               // 4-byte copies of A per thread per slab (M x K A)
+  static constexpr int kA1 = BM * BK / kThreads;               // 4-byte copies of A per thread per slab (M x K A, K-major)
+  static constexpr int kA2 = BM * BK / 2 / kThreads;           // 8-byte copies of A per thread per slab (M x K A)
   static constexpr int kB4 = BN * BK / 4 / kThreads;
   static_assert(TM % 4 == 0 && TN % 4 == 0 && BK % 8 == 0, "4-wide quads, steps unrolled by eight");
   static_assert(kThreadsM % 4 == 0 && kThreadsN % 8 == 0, "a warp covers 4 x 8 threads of the grid");
@@ -231,6 +240,11 @@ __device__ __forceinline__ void cp_async_16_bytes(uint32_t smem_dst, const void*
 
 __device__ __forceinline__ void cp_async_4_bytes(uint32_t smem_dst, const void* gsrc, int src_bytes) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void cp_async_8_bytes(uint32_t smem_dst, const void* gsrc, int src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_bytes)
                : "memory");
 }
 
@@ -267,10 +281,10 @@ sgemm_f32_pipe_kernel(const float* __restrict__ A, int64_t lda, const float* __r
   // Copies of an interior tile and a full slab need no bounds work: every thread keeps one running
   // pointer per operand (advanced once per slab) and its passes are a fixed stride apart.
   const bool interior = (m0 + BM <= M) && (n0 + BN <= N);
-  constexpr int kAPassRows = TRANS_A ? NT / (BM / 4) : NT / BK;     // k rows (K x M A) or m rows (M x K A) per pass
+  constexpr int kAPassRows = TRANS_A ? NT / (BM / 4) : (T::kPair ? NT / (BK / 2) : NT / BK);   // k rows (K x M A) or m rows (M x K A) per pass
   constexpr int kBPassRows = NT / (BN / 4);
-  const int a_r = TRANS_A ? tid / (BM / 4) : tid / BK;               // row of the first pass
-  const int a_c = TRANS_A ? (tid % (BM / 4)) * 4 : tid % BK;         // column (m for K x M, k for M x K)
+  const int a_r = TRANS_A ? tid / (BM / 4) : (T::kPair ? tid / (BK / 2) : tid / BK);               // row of the first pass
+  const int a_c = TRANS_A ? (tid % (BM / 4)) * 4 : (T::kPair ? (tid % (BK / 2)) * 2 : tid % BK);   // column (m for K x M, even k for M x K)
   const int b_r = tid / (BN / 4), b_c = (tid % (BN / 4)) * 4;
   const float* a_run = TRANS_A ? A + (int64_t)a_r * lda + (m0 + a_c) : A + (int64_t)(m0 + a_r) * lda + a_c;
   const float* b_run = B + (int64_t)b_r * ldb + (n0 + b_c);
@@ -278,9 +292,9 @@ sgemm_f32_pipe_kernel(const float* __restrict__ A, int64_t lda, const float* __r
   const int64_t b_pass = (int64_t)kBPassRows * ldb;
   const int64_t a_slab = TRANS_A ? (int64_t)BK * lda : (int64_t)BK;
   const int64_t b_slab = (int64_t)BK * ldb;
-  const uint32_t a_dst = sA_u + (uint32_t)(TRANS_A ? a_r * T::kARow + a_c : a_c * T::kARow + a_r) * 4u;
+  const uint32_t a_dst = sA_u + (uint32_t)(TRANS_A ? a_r * T::kARow + a_c : (T::kPair ? ((a_c >> 1) * T::kARowP + a_r) * 2 : a_c * T::kARow + a_r)) * 4u;
   const uint32_t b_dst = sB_u + (uint32_t)(b_r * T::kBRow + b_c) * 4u;
-  constexpr uint32_t kADstPass = (TRANS_A ? kAPassRows * T::kARow : kAPassRows) * 4u;
+  constexpr uint32_t kADstPass = (TRANS_A ? kAPassRows * T::kARow : (T::kPair ? kAPassRows * 2 : kAPassRows)) * 4u;
   constexpr uint32_t kBDstPass = kBPassRows * T::kBRow * 4u;
   int slabs_issued = 0;      // a_run / b_run point at slab `slabs_issued`
 
@@ -293,6 +307,10 @@ sgemm_f32_pipe_kernel(const float* __restrict__ A, int64_t lda, const float* __r
 #pragma unroll
         for (int v = 0; v < T::kA4; ++v)
           asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ad + v * kADstPass), "l"(a_run + v * a_pass) : "memory");
+      } else if (T::kPair) {
+#pragma unroll
+        for (int v = 0; v < T::kA2; ++v)
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(ad + v * kADstPass), "l"(a_run + v * a_pass) : "memory");
       } else {
 #pragma unroll
         for (int v = 0; v < T::kA1; ++v)
@@ -315,6 +333,15 @@ sgemm_f32_pipe_kernel(const float* __restrict__ A, int64_t lda, const float* __r
         const int bytes = gk < K ? max(0, min(4, M - gm)) * 4 : 0;
         const float* src = bytes ? A + (int64_t)gk * lda + gm : A;
         cp_async_16_bytes(sA_u + (uint32_t)(stage * T::kAStage + kk * T::kARow + mm) * 4u, src, bytes);
+      }
+    } else if (T::kPair) {
+#pragma unroll
+      for (int v = 0; v < T::kA2; ++v) {
+        const int mm = a_r + v * kAPassRows, kk = a_c;
+        const int gk = k0 + kk, gm = m0 + mm;
+        const int bytes = gm < M ? max(0, min(2, K - gk)) * 4 : 0;
+        const float* src = bytes ? A + (int64_t)gm * lda + gk : A;
+        cp_async_8_bytes(sA_u + (uint32_t)(stage * T::kAStage + ((kk >> 1) * T::kARowP + mm) * 2) * 4u, src, bytes);
       }
     } else {
 #pragma unroll
@@ -357,41 +384,56 @@ sgemm_f32_pipe_kernel(const float* __restrict__ A, int64_t lda, const float* __r
     }
     const float* a = sA + stage * T::kAStage;
     const float* b = sB + stage * T::kBStage;
-    // fragments of step kk + 1 are fetched into the other half of av / bv before the FFMAs of step kk
-    float av[2][TM], bv[2][TN];
-    auto fetch = [&](int kk, int h) {
-#pragma unroll
-      for (int q = 0; q < TM / 4; ++q) {
-        const float4 t = *reinterpret_cast<const float4*>(&a[kk * T::kARow + (q * T::kThreadsM + tm) * 4]);
-        av[h][q * 4 + 0] = t.x; av[h][q * 4 + 1] = t.y; av[h][q * 4 + 2] = t.z; av[h][q * 4 + 3] = t.w;
-      }
+    // Fragments are fetched one step ahead of the FFMAs that use them: B (and a K-major A) per step into
+    // the other half of bv / av; a pair-major A per k pair, eight floats per quad of rows holding both k.
+    // Each step's 64 FFMAs run in a zigzag over stripes of two rows, so that every FFMA shares one
+    // register operand with its predecessor, alternately the B and the A value (a0b0 a1b0 a1b1 a0b1 ...).
+    float av[2][TM][T::kPair ? 2 : 1], bv[2][TN];
+    auto fetch_b = [&](int kk, int h) {
 #pragma unroll
       for (int q = 0; q < TN / 4; ++q) {
         const float4 t = *reinterpret_cast<const float4*>(&b[kk * T::kBRow + (q * T::kThreadsN + tn) * 4]);
         bv[h][q * 4 + 0] = t.x; bv[h][q * 4 + 1] = t.y; bv[h][q * 4 + 2] = t.z; bv[h][q * 4 + 3] = t.w;
       }
     };
-    // eight steps are unrolled (512 FFMA of an 8 x 8 block, 8 KB of code): a fully unrolled slab of 32
-    // steps is 32 KB of FFMA and no longer sits in the instruction cache next to the schedulers
-    fetch(0, 0);
+    auto fetch_a = [&](int kk, int h) {      // K-major: step kk; pair-major: the pair starting at even kk
 #pragma unroll
-    for (int k8 = 0; k8 < BK; k8 += 8) {
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int kk = k8 + u;
-        if (u < 7 || k8 + 8 < BK) fetch(kk + 1, (u + 1) & 1);
-        // zigzag over stripes of two rows: every FFMA shares one operand with its predecessor,
-        // alternately the B and the A value (a0b0 a1b0 a1b1 a0b1 a0b2 ...)
-#pragma unroll
-        for (int i2 = 0; i2 < TM; i2 += 2)
-#pragma unroll
-          for (int jj = 0; jj < TN; ++jj) {
-            const int j = (i2 & 2) ? TN - 1 - jj : jj;
-            const int ia = i2 + (jj & 1), ib = i2 + 1 - (jj & 1);
-            acc[ia][j] = fmaf(av[u & 1][ia], bv[u & 1][j], acc[ia][j]);
-            acc[ib][j] = fmaf(av[u & 1][ib], bv[u & 1][j], acc[ib][j]);
-          }
+      for (int q = 0; q < TM / 4; ++q) {
+        if (T::kPair) {
+          const float* src = &a[((kk >> 1) * T::kARowP + (q * T::kThreadsM + tm) * 4) * 2];
+          const float4 t0 = *reinterpret_cast<const float4*>(src);
+          const float4 t1 = *reinterpret_cast<const float4*>(src + 4);
+          av[h][q * 4 + 0][0] = t0.x; av[h][q * 4 + 0][T::kPair] = t0.y;
+          av[h][q * 4 + 1][0] = t0.z; av[h][q * 4 + 1][T::kPair] = t0.w;
+          av[h][q * 4 + 2][0] = t1.x; av[h][q * 4 + 2][T::kPair] = t1.y;
+          av[h][q * 4 + 3][0] = t1.z; av[h][q * 4 + 3][T::kPair] = t1.w;
+        } else {
+          const float4 t = *reinterpret_cast<const float4*>(&a[kk * T::kARow + (q * T::kThreadsM + tm) * 4]);
+          av[h][q * 4 + 0][0] = t.x; av[h][q * 4 + 1][0] = t.y; av[h][q * 4 + 2][0] = t.z; av[h][q * 4 + 3][0] = t.w;
+        }
       }
+    };
+    fetch_a(0, 0);
+    fetch_b(0, 0);
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      if (T::kPair) {
+        if (kk + 1 < BK) fetch_b(kk + 1, (kk + 1) & 1);
+        if ((kk & 1) == 0 && kk + 2 < BK) fetch_a(kk + 2, ((kk >> 1) + 1) & 1);
+      } else if (kk + 1 < BK) {
+        fetch_a(kk + 1, (kk + 1) & 1);
+        fetch_b(kk + 1, (kk + 1) & 1);
+      }
+      const int ha = T::kPair ? (kk >> 1) & 1 : kk & 1, ka = T::kPair ? kk & 1 : 0, hb = kk & 1;
+#pragma unroll
+      for (int i2 = 0; i2 < TM; i2 += 2)
+#pragma unroll
+        for (int jj = 0; jj < TN; ++jj) {
+          const int j = (i2 & 2) ? TN - 1 - jj : jj;
+          const int ia = i2 + (jj & 1), ib = i2 + 1 - (jj & 1);
+          acc[ia][j] = fmaf(av[ha][ia][ka], bv[hb][j], acc[ia][j]);
+          acc[ib][j] = fmaf(av[ha][ib][ka], bv[hb][j], acc[ib][j]);
+        }
     }
     if (++stage == STAGES) stage = 0;
   }
@@ -479,8 +521,8 @@ void sgemm_f32_get_config(int idx, helix_cfg_t* out) {
 static double sgemm_cfg_rate(const SgemmCfg& c) {
   if (c.stages >= 3) {
     if (c.bm == 128 && c.bn == 128) return c.bk == 32 ? 1.0 : 0.93;
-    if (c.bm == 64) return 0.91;
-    return c.bk == 32 ? 0.85 : 0.89;
+    if (c.bm == 64) return 0.89;
+    return c.bk == 32 ? 0.93 : 0.90;
   }
   if (c.bm == 128) return 0.86;
   if (c.bn == 128) return 0.82;
