@@ -210,7 +210,8 @@ int helix_get_config(int op, int idx, helix_cfg_t* out) {
       break;
     case HELIX_OP_GEMM_F32:
     case HELIX_OP_CONV_F32:
-      helix::sgemm_f32_get_config(idx, out);     // a convolution takes the GEMM's configurations as they are
+      helix::sgemm_f32_get_config(idx, out);     // a convolution runs the GEMM's configurations
+      out->op = op;
       break;
   }
   return HELIX_OK;
@@ -246,6 +247,7 @@ int helix_default_config(const helix_launch_t* l, helix_cfg_t* out) {
       const int64_t M = (int64_t)g.NB * g.Ho * g.Wo;
       if (M <= 0 || M > 0x7fffffff || g.KO <= 0) return HELIX_ERR_INVALID;
       helix::sgemm_f32_default_config((int)M, g.KO, sms, out);
+      out->op = HELIX_OP_CONV_F32;
       return HELIX_OK;
     }
     default:

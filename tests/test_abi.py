@@ -39,7 +39,7 @@ def test_version_and_status_strings(lib):
 
 
 def test_config_enumeration(lib):
-    for op in (_lib.OP_GEMM_F16, _lib.OP_GEMV_F16, _lib.OP_CONV_F16, _lib.OP_GEMM_F32):
+    for op in (_lib.OP_GEMM_F16, _lib.OP_GEMV_F16, _lib.OP_CONV_F16, _lib.OP_GEMM_F32, _lib.OP_CONV_F32):
         n = lib.helix_num_configs(op)
         assert n > 0
         seen = set()
@@ -80,3 +80,18 @@ def test_launch_without_device_reports_nodevice_or_runs(lib):
     l.op, l.M, l.N, l.K, l.batch = _lib.OP_GEMM_F16, 128, 128, 64, 1
     assert lib.helix_launch(ctypes.byref(l), None, None) == -7
     assert lib.helix_launch(None, None, None) == -1
+
+
+def test_conv_f32_workspace_is_column_matrix_plus_transposed_weights(lib):
+    l = Launch()
+    l.op = _lib.OP_CONV_F32
+    for i, v in enumerate((2, 10, 10, 8, 16, 3, 3, 1, 1)):      # N H W C KO R S stride pad
+        l.conv[i] = v
+    M, K = 2 * 10 * 10, 3 * 3 * 8
+    need = lib.helix_workspace_bytes(ctypes.byref(l))
+    assert need % 256 == 0 and (M * K + K * 16) * 4 <= need <= (M * K + K * 16) * 4 + 512
+    for i, v in enumerate((1, 6, 6, 8, 4, 1, 1, 1, 0)):          # 1x1: no column matrix
+        l.conv[i] = v
+    assert lib.helix_workspace_bytes(ctypes.byref(l)) == 256
+    c = Cfg()
+    assert lib.helix_default_config(ctypes.byref(l), ctypes.byref(c)) == 0 and c.op == _lib.OP_CONV_F32 and c.tile_m > 0
