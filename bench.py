@@ -294,6 +294,8 @@ def bench_helix(args, rank, world, local_rank):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     from helix_b200 import dist_util, ops, sweep, workloads
     peaks = read_peaks()
+    # one rank per GPU: keep this rank's pinned host buffers on its GPU's NUMA node (matters for e2e at N > 1)
+    numa_cpus = dist_util.bind_to_gpu_numa_node(local_rank) if world > 1 else None
 
     units = workloads.model_level_sweep()
     sw = sweep.Sweep(units, seed=4 * 1000 + rank, lanes=args.lanes)
@@ -379,7 +381,8 @@ def bench_helix(args, rank, world, local_rank):
         "config": {"workload": WORKLOAD, "units_per_step_per_gpu": len(units), "flop_per_step_per_gpu": sw.flops,
                    "cache": "operands of one step total %.1f GB per GPU (> L2), one buffer set per unit" % (sw.bytes / 1e9),
                    "cuda_graph": graph is not None, "parallelism": f"independent replicas of the sweep x{world}",
-                   "lanes": "%d concurrent launch chains per GPU, each launch limited to 1/%d of the SMs" % (args.lanes, args.lanes)},
+                   "lanes": "%d concurrent launch chains per GPU, each launch limited to 1/%d of the SMs" % (args.lanes, args.lanes),
+                   "host_numa_binding": ("rank 0 bound to %d CPUs next to its GPU" % len(numa_cpus)) if numa_cpus else "none"},
         "roofline": {"bound": "tensor", "achieved": tg["TFLOP/s"], "peak": peak, "unit": "TFLOP/s",
                      "frac": tg["TFLOP/s"] / peak, "traffic": traffic,
                      "kernel": top, "launches_per_step": tg["launches"], "share_of_step": tg["share"],

@@ -317,3 +317,12 @@ def test_ablation_selection_policies_on_a_synthetic_dictionary():
     assert ids == sorted(ids) and all(c[1][0] != 0 for c in cand)
     assert min(cand, key=lambda c: c[2])[1] == costmodel.cost_model(d, 476, 1024, 1024)
     assert any(c[1][0] == 0 for c in curve.candidates(d, 4, 1024, 1024))
+
+
+def test_numa_binding_helpers_are_best_effort():
+    from helix_b200 import dist_util
+    assert dist_util._parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert dist_util._parse_cpulist("") == set()
+    before = os.sched_getaffinity(0)
+    assert dist_util.bind_to_gpu_numa_node(0, sysfs="/nonexistent") is None     # unreadable topology: nothing changes
+    assert os.sched_getaffinity(0) == before
