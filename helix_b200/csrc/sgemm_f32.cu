@@ -207,7 +207,8 @@ sgemm_f32_kernel(const float* __restrict__ A, int64_t lda, const float* __restri
 // a thread needs for a quad of rows and one k pair are contiguous, so it reads them with two 16-byte
 // loads per pair -- the same number of shared loads per FFMA as the K-major layout, without a
 // transposing copy per element (1024^3, 128 x 64 tile: 66.1 -> 60.1 us).  With 8 x 8 blocks the pair
-// fragments cost 16 more registers and the kernel gets slower (4096^3: 2615 -> 2880 us), so there the
+// fragments cost 16 more registers and the kernel gets slower (4096^3: 2615 -> 2880 us; 2797 us when the
+// next pair is fetched stripe by stripe into the registers the current pair's last step frees), so there the
 // copy itself transposes, one 4-byte cp.async per element into the K-major layout.
 // Rows outside the matrix and the K tail are zero-filled by the copy's source size.
 template <int BM, int BN, int BK, int TM, int TN, int STAGES, bool TRANS_A>
