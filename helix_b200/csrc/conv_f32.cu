@@ -13,22 +13,37 @@
 
 namespace helix {
 
-// One thread per 4 consecutive channels (VEC) or per element of the column matrix.
-template <bool VEC>
+struct Im2colDivs { FastDiv cq, s, r, wo, ho; };
+
+// One thread per 4 consecutive channels (VEC) or per element of the column matrix.  With fewer than
+// 2^31 work items (SMALL) the index is split with multiply-high reciprocals instead of 64-bit divisions.
+template <bool VEC, bool SMALL>
 __global__ void __launch_bounds__(256) im2col_f32_nhwc_kernel(const float* __restrict__ x, float* __restrict__ col,
                                                               int H, int W, int C, int R, int S, int stride, int pad,
-                                                              int Ho, int Wo, int64_t total) {
+                                                              int Ho, int Wo, int64_t total, Im2colDivs dv) {
   constexpr int E = VEC ? 4 : 1;
   const int cq = C / E;                       // channel groups per tap
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int c = (int)(i % cq) * E;
-    int64_t t = i / cq;
-    const int s = (int)(t % S); t /= S;
-    const int r = (int)(t % R); t /= R;       // t = output pixel index m
-    const int wo = (int)(t % Wo);
-    const int64_t t2 = t / Wo;
-    const int ho = (int)(t2 % Ho);
-    const int64_t n = t2 / Ho;
+    int c, s, r, wo, ho;
+    int64_t t, n;                              // t = output pixel index m
+    if (SMALL) {
+      int q, rem, t32, t2, n32;
+      fast_divmod((int)i, dv.cq, q, rem); c = rem * E;
+      fast_divmod(q, dv.s, q, s);
+      fast_divmod(q, dv.r, t32, r);
+      fast_divmod(t32, dv.wo, t2, wo);
+      fast_divmod(t2, dv.ho, n32, ho);
+      t = t32; n = n32;
+    } else {
+      c = (int)(i % cq) * E;
+      t = i / cq;
+      s = (int)(t % S); t /= S;
+      r = (int)(t % R); t /= R;
+      wo = (int)(t % Wo);
+      const int64_t t2 = t / Wo;
+      ho = (int)(t2 % Ho);
+      n = t2 / Ho;
+    }
     const int h = ho * stride - pad + r, w = wo * stride - pad + s;
     const bool inside = h >= 0 && h < H && w >= 0 && w < W;
     float* dst = col + (t * R * S + (int64_t)r * S + s) * C + c;
@@ -90,12 +105,17 @@ int conv_f32_launch(const helix_cfg_t* cfg, const float* x, const float* w, floa
     const bool vec = (g.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
     const int64_t total = (int64_t)M * g.R * g.S * (vec ? g.C / 4 : g.C);
     const int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)sm_count * 16);
-    if (vec)
-      im2col_f32_nhwc_kernel<true><<<blocks, 256, 0, stream>>>(x, col, g.H, g.W, g.C, g.R, g.S, g.stride, g.pad, g.Ho,
-                                                                g.Wo, total);
-    else
-      im2col_f32_nhwc_kernel<false><<<blocks, 256, 0, stream>>>(x, col, g.H, g.W, g.C, g.R, g.S, g.stride, g.pad, g.Ho,
-                                                                 g.Wo, total);
+    const bool small = total < (int64_t)0x7fffffff;
+    Im2colDivs dv{make_fastdiv(vec ? g.C / 4 : g.C), make_fastdiv(g.S), make_fastdiv(g.R), make_fastdiv(g.Wo),
+                  make_fastdiv(g.Ho)};
+#define HELIX_IM2COL(V, SM)                                                                                        \
+  im2col_f32_nhwc_kernel<V, SM><<<blocks, 256, 0, stream>>>(x, col, g.H, g.W, g.C, g.R, g.S, g.stride, g.pad, g.Ho, \
+                                                            g.Wo, total, dv)
+    if (vec && small) HELIX_IM2COL(true, true);
+    else if (vec) HELIX_IM2COL(true, false);
+    else if (small) HELIX_IM2COL(false, true);
+    else HELIX_IM2COL(false, false);
+#undef HELIX_IM2COL
     ++*launches;
     a = col;
   }
