@@ -241,6 +241,17 @@ def extras(peaks):
         out["gemm_f32_%d" % n] = {"us": avg * 1e6, "TFLOP/s": tf, "frac_ffma_peak_nominal_74.4": tf / 74.4,
                                   "frac_ffma_probe": tf / ffma_measured}
         del a, b, c
+    # true-fp32 convolution (column matrix + weight transpose + FFMA GEMM, all three kernels timed)
+    from helix_b200 import harness
+    c32 = {}
+    for layer in datagen.C4_LAYERS[:2] + datagen.C4_LAYERS[3:4]:
+        B, C, H, W, OC, kh, kw, s, p = layer
+        t = harness.time_conv_f32(*layer)
+        Ho, Wo = ops.conv_out_hw(H, W, kh, kw, s, p)
+        tf = 2.0 * B * Ho * Wo * OC * C * kh * kw / t / 1e12
+        c32["x".join(map(str, layer))] = {"us": t * 1e6, "TFLOP/s": tf, "frac_ffma_peak_nominal_74.4": tf / 74.4,
+                                          "frac_ffma_probe": tf / ffma_measured}
+    out["conv_f32"] = c32
     return out
 
 
