@@ -48,7 +48,7 @@ class Sweep:
     """Device-resident sweep: distinct operand buffers per unit, one prepared launch each."""
 
     def __init__(self, units, seed=4, device=None, cfg_for=None, lanes=1):
-        """lanes > 1: the units are dealt round-robin to that many streams and every launch is limited to
+        """lanes > 1: the units are dealt to that many streams (balanced by estimated time) and every launch is limited to
         1/lanes of the SMs, so independent shapes run side by side with longer-lived CTAs (the set-up and
         drain of one launch hide behind the steady state of its neighbour)."""
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
@@ -56,6 +56,14 @@ class Sweep:
         self.units = list(units)
         self.tensors = []
         self.launches = []
+        # lanes: longest-processing-time-first on a roofline estimate of each unit, so that the chains end a
+        # step together (round-robin puts all the heavy GEMMs of a repeated layer pattern into one chain)
+        est = [max(workloads.unit_flops(u) / 1.0e15, workloads.unit_bytes(u) / 5.0e12) + 4e-6 for u in self.units]
+        self.lane_of = [0] * len(self.units)
+        if self.lanes > 1:
+            for lane, idxs in enumerate(workloads.lpt_partition(est, self.lanes)):
+                for i in idxs:
+                    self.lane_of[i] = lane
         gen = torch.Generator(device=self.device)
         for i, u in enumerate(self.units):
             gen.manual_seed(int(seed) * 1000003 + i)
@@ -78,7 +86,7 @@ class Sweep:
             l.flags = LAUNCH_INDEPENDENT
             if self.lanes > 1:
                 sms = ops.device_info().sm_count
-                ops.limit_ctas(l, (sms // self.lanes) & ~1, lane=i % self.lanes)
+                ops.limit_ctas(l, (sms // self.lanes) & ~1, lane=self.lane_of[i])
             self.launches.append(l)
         self.flops = sum(workloads.unit_flops(u) for u in self.units)
         self.bytes = sum(workloads.unit_bytes(u) for u in self.units)
@@ -106,7 +114,7 @@ class Sweep:
         for s in self._streams:
             s.wait_event(fork)
         for i, l in enumerate(self.launches):
-            with torch.cuda.stream(self._streams[i % self.lanes]):
+            with torch.cuda.stream(self._streams[self.lane_of[i]]):
                 ops.run(l)
         for s in self._streams:
             done = torch.cuda.Event()
