@@ -64,6 +64,12 @@ class Sweep:
             for lane, idxs in enumerate(workloads.lpt_partition(est, self.lanes)):
                 for i in idxs:
                     self.lane_of[i] = lane
+        # odd lanes walk their units backwards: while one chain is in the memory-bound part of the list
+        # (batched attention GEMMs, 1x1 convolutions) its neighbour is in a tensor-bound part
+        per_lane = [[i for i in range(len(self.units)) if self.lane_of[i] == lane] for lane in range(self.lanes)]
+        for lane in range(1, self.lanes, 2):
+            per_lane[lane].reverse()
+        self.issue_order = [lst[j] for j in range(max(map(len, per_lane))) for lst in per_lane if j < len(lst)]
         gen = torch.Generator(device=self.device)
         for i, u in enumerate(self.units):
             gen.manual_seed(int(seed) * 1000003 + i)
@@ -113,9 +119,9 @@ class Sweep:
         fork.record(main)
         for s in self._streams:
             s.wait_event(fork)
-        for i, l in enumerate(self.launches):
+        for i in self.issue_order:
             with torch.cuda.stream(self._streams[self.lane_of[i]]):
-                ops.run(l)
+                ops.run(self.launches[i])
         for s in self._streams:
             done = torch.cuda.Event()
             done.record(s)
