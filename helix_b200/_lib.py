@@ -38,7 +38,7 @@ class Cfg(ctypes.Structure):
                 ("tile_k", ctypes.c_int), ("stages", ctypes.c_int), ("cta_group", ctypes.c_int),
                 ("split_k", ctypes.c_int), ("swap_ab", ctypes.c_int), ("raster", ctypes.c_int),
                 ("thread_m", ctypes.c_int), ("thread_n", ctypes.c_int), ("load_group", ctypes.c_int),
-                ("stream_k", ctypes.c_int), ("conv_gather", ctypes.c_int), ("max_ctas", ctypes.c_int), ("reserved", ctypes.c_int * 1)]
+                ("stream_k", ctypes.c_int), ("conv_gather", ctypes.c_int), ("max_ctas", ctypes.c_int), ("probe", ctypes.c_int)]
 
     def key(self):
         """Hashable identity used as the prof_dict key."""

@@ -64,7 +64,9 @@ int current_device(helix_devinfo_t* info, bool need_sm100) {
 helix::ConvGeom conv_geom(const int* c) {
   helix::ConvGeom g;
   g.NB = c[0]; g.H = c[1]; g.W = c[2]; g.C = c[3]; g.KO = c[4]; g.R = c[5]; g.S = c[6]; g.stride = c[7]; g.pad = c[8];
-  if (g.stride > 0) {
+  // a filter larger than the padded image has no valid window (C division would truncate towards zero
+  // and report one)
+  if (g.stride > 0 && g.H + 2 * g.pad >= g.R && g.W + 2 * g.pad >= g.S) {
     g.Ho = (g.H + 2 * g.pad - g.R) / g.stride + 1;
     g.Wo = (g.W + 2 * g.pad - g.S) / g.stride + 1;
   } else {

@@ -53,6 +53,7 @@ struct HaloParams {
   int b_stages;
   int independent;
   int vec_ok;        // 16-byte output stores are possible
+  int probe;         // tuning instrument (helix_cfg_t.probe): 1 = issue no MMA
   int* status;
   FastDiv fd_tiles_n, fd_rb, fd_wp, fd_s;
   unsigned long long* trace;   // optional per-CTA timeline (null = off), same layout as the GEMM kernels
@@ -246,7 +247,7 @@ conv_f16_halo_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
             const uint32_t shift = (uint32_t)(fr * p.Wp + fs) * 128u;   // first row of this tap's window
             // the two row blocks' accumulators alternate: consecutive MMAs into the same accumulator
             // wait for one another, independent ones overlap
-            if (my_sub < it.nsub) {
+            if (my_sub < it.nsub && !(p.probe & 1)) {
               const uint64_t da = umma_desc_sw128_rows(win0 + (uint32_t)my_sub * p.buf_bytes + shift);
 #pragma unroll
               for (int k = 0; k < kBK / 16; ++k)
@@ -321,6 +322,10 @@ conv_f16_halo_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
   // ------------------------------------------------------------------ teardown
   tc_fence_before_sync();
   __syncthreads();
+  // A launch that did not wait for its predecessor before its work waits for it now, after its last
+  // store: the kernel then cannot complete before everything queued ahead of it has, so completion
+  // order along the stream stays transitive for whatever is queued next.
+  if (p.independent) griddep_wait();
   if (threadIdx.x == 0 && p.trace != nullptr) {
     htrace(p, 3);
     p.trace[(size_t)blockIdx.x * kTraceWords + 4] = global_timer_ns();
@@ -452,6 +457,7 @@ int conv_f16_halo_launch(const helix_cfg_t* cfg, const void* x, const void* w, v
   p.independent = independent ? 1 : 0;
   p.vec_ok = ((g.KO & 7) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0) ? 1 : 0;
   p.status = status_dev;
+  p.probe = (cfg && cfg->tile_m != 0) ? cfg->probe : 0;
   p.fd_tiles_n = make_fastdiv(p.tiles_n);
   p.fd_rb = make_fastdiv(p.RB);
   p.fd_wp = make_fastdiv(p.Wp);

@@ -78,6 +78,9 @@ struct GemmParams {
   int tma_store;   // whole tiles leave through shared memory and a TMA store (tmap_c is valid)
   int swap_fast;   // swap: tiles are transposed through shared memory and leave as 16-byte stores
   int independent; // nothing read or written here is written by the kernel queued just before
+  int probe;       // tuning instrument (helix_cfg_t.probe): 1 = issue no MMA, 2 = no A loads, 4 = no B loads
+  int group;       // ring stages that share one "full" barrier (see the MMA issuer); stages is a multiple of it
+  FastDiv fd_grp;
   int* status;
   // convolution only
   const __half* x;
@@ -220,8 +223,10 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       p.trace[(size_t)cta * kTraceWords + 0] = global_timer_ns();
       p.trace[(size_t)cta * kTraceWords + 1] = (unsigned long long)clock64();
     }
+    // "full" barriers are shared by groups of `group` consecutive stages (one arrival per slab),
+    // "empty" barriers are per stage
     for (int s = 0; s < stages; ++s) {
-      mbar_init(&full_bar[s], CONV ? kConvProducerWarps * 32 + 1 : 1);
+      if (s * p.group < stages) mbar_init(&full_bar[s], CONV ? kConvProducerWarps * 32 + 1 : p.group);
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -291,25 +296,51 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status);
             if (!ok) break;
             trace_slab(p, 0, my_n);
-            mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
-            if (p.im2col) {
+            uint64_t* const fb = &full_bar[fast_div(stage, p.fd_grp)];
+            const bool load_a = !(p.probe & 2), load_b = !(p.probe & 4);
+            if (load_a || load_b)
+              mbar_arrive_expect_tx(fb, (load_a ? kATileBytes : 0) + (load_b ? L::kBTileBytes : 0));
+            else
+              mbar_arrive(fb);
+            if (p.probe & 6) {
+              // probe runs: the same requests minus the operand(s) left out; results are meaningless
+              if (p.im2col) {
+                int tap, cb, fr, fs;
+                fast_divmod(kb, p.fd_cblocks, tap, cb);
+                fast_divmod(tap, p.fd_s, fr, fs);
+                if (p.swap) {
+                  if (load_a) tma_load_3d(sA + (size_t)stage * kATileBytes, &tmap_a, fb, kb * kBK, w.m_blk * kBM, 0);
+                  if (load_b) tma_load_im2col_4d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, fb, cb * kBK,
+                                                 pix_w, pix_h, pix_n, (uint16_t)fs, (uint16_t)fr);
+                } else {
+                  if (load_a) tma_load_im2col_4d(sA + (size_t)stage * kATileBytes, &tmap_a, fb, cb * kBK,
+                                                 pix_w, pix_h, pix_n, (uint16_t)fs, (uint16_t)fr);
+                  if (load_b) tma_load_3d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, fb, kb * kBK,
+                                          w.n_blk * BN, w.b);
+                }
+              } else {
+                if (load_a) tma_load_3d(sA + (size_t)stage * kATileBytes, &tmap_a, fb, kb * kBK, w.m_blk * kBM, w.b);
+                if (load_b) tma_load_3d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, fb, kb * kBK,
+                                        w.n_blk * BN, w.b);
+              }
+            } else if (p.im2col) {
               // K is ordered (r, s, c): slab kb is filter tap kb / cblocks, channels 64 * (kb % cblocks)
               int tap, cb, fr, fs;
               fast_divmod(kb, p.fd_cblocks, tap, cb);
               fast_divmod(tap, p.fd_s, fr, fs);
               if (p.swap) {   // weights on the 128-row axis, BN pixels per im2col box on the other
-                tma_load_3d(sA + (size_t)stage * kATileBytes, &tmap_a, &full_bar[stage], kb * kBK, w.m_blk * kBM, 0);
-                tma_load_im2col_4d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, &full_bar[stage], cb * kBK, pix_w,
+                tma_load_3d(sA + (size_t)stage * kATileBytes, &tmap_a, fb, kb * kBK, w.m_blk * kBM, 0);
+                tma_load_im2col_4d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, fb, cb * kBK, pix_w,
                                    pix_h, pix_n, (uint16_t)fs, (uint16_t)fr);
               } else {
-                tma_load_im2col_4d(sA + (size_t)stage * kATileBytes, &tmap_a, &full_bar[stage], cb * kBK, pix_w,
+                tma_load_im2col_4d(sA + (size_t)stage * kATileBytes, &tmap_a, fb, cb * kBK, pix_w,
                                    pix_h, pix_n, (uint16_t)fs, (uint16_t)fr);
-                tma_load_3d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, &full_bar[stage], kb * kBK, w.n_blk * BN,
+                tma_load_3d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, fb, kb * kBK, w.n_blk * BN,
                             w.b);
               }
             } else {
-              tma_load_3d(sA + (size_t)stage * kATileBytes, &tmap_a, &full_bar[stage], kb * kBK, w.m_blk * kBM, w.b);
-              tma_load_3d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, &full_bar[stage], kb * kBK, w.n_blk * BN,
+              tma_load_3d(sA + (size_t)stage * kATileBytes, &tmap_a, fb, kb * kBK, w.m_blk * kBM, w.b);
+              tma_load_3d(sB + (size_t)stage * L::kBTileBytes, &tmap_b, fb, kb * kBK, w.n_blk * BN,
                           w.b);
             }
             stage += p.load_warps;
@@ -317,6 +348,16 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           }
           n_start += nkb;
           if (warp == 0) trace_mark(p, idx, 1);
+        }
+        // The last group of the CTA's slab sequence may be short: its missing slabs are made up by plain
+        // arrivals, each ordered after the release of its ring stage like a real slab.
+        const int n_pad = (n_start + p.group - 1) / p.group * p.group;
+        for (; ok && my_n < n_pad; my_n += p.load_warps) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status);
+          if (!ok) break;
+          mbar_arrive(&full_bar[fast_div(stage, p.fd_grp)]);
+          stage += p.load_warps;
+          if (stage >= stages) { stage -= stages; phase ^= 1; }
         }
       }
     } else {
@@ -405,6 +446,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       uint32_t phase = 0;
       bool ok = true;
       int nslab = 0;
+      int gpos = 0, gidx = 0;   // position of the next slab inside its group of stages, and the group
       WorkItem w;
       for (int idx = 0; ok && get_item(p, cta, grid, idx, w); ++idx) {
         const int acc = idx & 1;
@@ -415,8 +457,14 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         trace_mark(p, idx, 2);
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
-          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status);
-          if (!ok) break;
+          // One wait per group of stages: reading shared memory (the barrier) costs this thread some 200
+          // cycles on top of the 45 it needs to hand one MMA to the tensor core, more than a 64-deep slab
+          // of a narrow tile keeps the tensor core busy.  The stages are still released one by one.
+          if (gpos == 0) {
+            ok = mbar_wait(&full_bar[gidx], phase, abort_flag, p.status);
+            if (!ok) break;
+          }
+          if (++gpos == p.group) { gpos = 0; ++gidx; }
           trace_slab(p, 1, nslab++);
           // The gathered A tile was written through the generic proxy (cp.async); order those
           // writes, now visible through the barrier, before the tensor core's async-proxy reads.
@@ -424,13 +472,15 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           tc_fence_after_sync();
           const uint64_t da = umma_desc_sw128(smem_u32(sA + (size_t)stage * kATileBytes));
           const uint64_t db = umma_desc_sw128(smem_u32(sB + (size_t)stage * L::kBTileBytes));
+          if (!(p.probe & 1)) {
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) {
-            // advancing 16 halves = 32 bytes along K inside the swizzle atom: +2 in the address field
-            umma_f16_ss(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kb > w.kb0) || (k > 0));
+            for (int k = 0; k < kBK / 16; ++k) {
+              // advancing 16 halves = 32 bytes along K inside the swizzle atom: +2 in the address field
+              umma_f16_ss(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kb > w.kb0) || (k > 0));
+            }
           }
           umma_commit(&empty_bar[stage]);
-          if (++stage == stages) { stage = 0; phase ^= 1; }
+          if (++stage == stages) { stage = 0; phase ^= 1; gidx = 0; }
         }
         if (ok) umma_commit(&tmem_full[acc]);
         trace_mark(p, idx, 3);
@@ -643,6 +693,10 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   // ------------------------------------------------------------------ teardown
   tc_fence_before_sync();
   __syncthreads();
+  // A launch that did not wait for its predecessor before its work waits for it now, after its last
+  // store: the kernel then cannot complete before everything queued ahead of it has, so completion
+  // order along the stream stays transitive for whatever is queued next.
+  if (p.independent) griddep_wait();
   if (threadIdx.x == 0 && p.trace != nullptr) {
     p.trace[(size_t)cta * kTraceWords + 3] = (unsigned long long)clock64();
     p.trace[(size_t)cta * kTraceWords + 4] = global_timer_ns();
@@ -1129,6 +1183,15 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
   const int smax = max_stages(bn, conv);
   p.stages = cfg.stages > 0 ? std::min(cfg.stages, smax) : smax;
   if (p.stages < (conv ? 3 : 2)) return HELIX_ERR_UNSUPPORTED;
+  // stages per "full" barrier: four for narrow tiles (eight stages fit), two otherwise; at least two groups
+  p.group = 1;
+  if (!conv) {
+    p.group = (bn <= 64 && p.stages >= 8) ? 4 : (p.stages >= 6 ? 3 : (p.stages >= 4 ? 2 : 1));
+    if ((cfg.probe >> 4) & 7) p.group = (cfg.probe >> 4) & 7;   // tuning override
+    while (p.group > 1 && p.stages / p.group < 2) --p.group;
+    p.stages = p.stages / p.group * p.group;
+  }
+  p.fd_grp = make_fastdiv(p.group);
   // Never more issuing warps than ring stages: a warp waits on a stage's "empty" barrier by
   // parity, which is only meaningful while it is at most one use of that stage ahead of the
   // consumer; with load_warps <= stages its previous slab guarantees that.
@@ -1191,6 +1254,7 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
   p.fd_cblocks = make_fastdiv(p.im2col ? p.g.C / kBK : 1);
   p.fd_s = make_fastdiv(p.im2col ? p.g.S : 1);
   p.trace = gemm_f16_trace_for_grid(grid);
+  p.probe = conv ? 0 : (cfg.probe & 7);
   cudaError_t e = cudaErrorInvalidValue;
 #define HELIX_BN_CASE(BNV)                                                                 \
   case BNV:                                                                                \

@@ -45,6 +45,9 @@ struct Gemm2Params {
   int raster, stages;
   int load_warps;   // issuing warps per CTA, <= stages (see the one-CTA kernel's producer)
   int tma_store, independent;
+  int probe;        // tuning instrument (helix_cfg_t.probe): 1 = issue no MMA, 2 = no A loads, 4 = no B loads
+  int group;        // ring stages that share one "full" barrier (one wait of the MMA issuer per group)
+  FastDiv fd_grp;
   int* status;
   FastDiv fd_per_batch, fd_group, fd_raster, fd_num_kb;   // reciprocals for the tile decoder
   unsigned long long* trace;                   // optional per-CTA timeline (null = off)
@@ -218,7 +221,7 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       trace2(p, 1);
     }
     for (int s = 0; s < stages; ++s) {
-      mbar_init(&full_bar[s], 1);
+      if (s * p.group < stages) mbar_init(&full_bar[s], p.group);
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -263,17 +266,36 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status);
           if (!ok) break;
           trace2_slab(p, 0, my_n);
-          if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kStageBytes);
-          const uint32_t full_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
-          tma_load_3d_pair(sA + (size_t)stage * kATileBytes, &tmap_a, full_leader, kb * kBK,
-                           w.m_blk * 2 * kBM + (int)rank * kBM, w.b);
-          tma_load_3d_pair(sB + (size_t)stage * kBHalfBytes, &tmap_b, full_leader, kb * kBK,
-                           w.n_blk * BN + (int)rank * (BN / 2), w.b);
+          const bool load_a = !(p.probe & 2), load_b = !(p.probe & 4);
+          uint64_t* const fb = &full_bar[fast_div(stage, p.fd_grp)];
+          if (rank == 0) {
+            if (load_a || load_b)
+              mbar_arrive_expect_tx(fb, 2 * ((load_a ? kATileBytes : 0) + (load_b ? kBHalfBytes : 0)));
+            else
+              mbar_arrive(fb);
+          }
+          const uint32_t full_leader = map_to_cta(smem_u32(fb), 0);
+          if (load_a)
+            tma_load_3d_pair(sA + (size_t)stage * kATileBytes, &tmap_a, full_leader, kb * kBK,
+                             w.m_blk * 2 * kBM + (int)rank * kBM, w.b);
+          if (load_b)
+            tma_load_3d_pair(sB + (size_t)stage * kBHalfBytes, &tmap_b, full_leader, kb * kBK,
+                             w.n_blk * BN + (int)rank * (BN / 2), w.b);
           stage += p.load_warps;
           if (stage >= stages) { stage -= stages; phase ^= 1; }
         }
         n_start += nkb;
         if (issuer == 0) trace2_tile(p, tidx, 1);
+      }
+      // a short last group of the pair's slab sequence is completed by plain arrivals (even CTA: the
+      // barriers live there), each ordered after the release of its ring stage like a real slab
+      const int n_pad = (n_start + p.group - 1) / p.group * p.group;
+      for (; ok && my_n < n_pad; my_n += p.load_warps) {
+        ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status);
+        if (!ok) break;
+        if (rank == 0) mbar_arrive(&full_bar[fast_div(stage, p.fd_grp)]);
+        stage += p.load_warps;
+        if (stage >= stages) { stage -= stages; phase ^= 1; }
       }
     }
   } else if (warp == 1) {
@@ -283,6 +305,7 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t phase = 0;
       bool ok = true;
       int nslab = 0;
+      int gpos = 0, gidx = 0;   // position of the next slab inside its group of stages, and the group
       Item2 it;
       for (int idx = 0; ok && get_item2(p, pair, num_pairs, idx, it); ++idx) {
         const int acc = idx & 1;
@@ -293,17 +316,24 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         trace2_tile(p, idx, 2);
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
-          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status);
-          if (!ok) break;
+          // one wait per group of stages (a shared-memory read costs the issuing thread some 200 cycles);
+          // the stages are still released one by one
+          if (gpos == 0) {
+            ok = mbar_wait(&full_bar[gidx], phase, abort_flag, p.status);
+            if (!ok) break;
+          }
+          if (++gpos == p.group) { gpos = 0; ++gidx; }
           trace2_slab(p, 1, nslab++);
           tc_fence_after_sync();
           const uint64_t da = umma_desc_sw128(smem_u32(sA + (size_t)stage * kATileBytes));
           const uint64_t db = umma_desc_sw128(smem_u32(sB + (size_t)stage * kBHalfBytes));
+          if (!(p.probe & 1)) {
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k)
-            umma_f16_ss_pair(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kb > it.kb0) || (k > 0));
+            for (int k = 0; k < kBK / 16; ++k)
+              umma_f16_ss_pair(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kb > it.kb0) || (k > 0));
+          }
           umma_commit_pair(&empty_bar[stage]);
-          if (++stage == stages) { stage = 0; phase ^= 1; }
+          if (++stage == stages) { stage = 0; phase ^= 1; gidx = 0; }
         }
         if (ok) umma_commit_pair(&tmem_full[acc]);
         trace2_tile(p, idx, 3);
@@ -437,6 +467,10 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   tc_fence_before_sync();
   __syncthreads();
   cluster_sync_all();   // nothing of the pair still refers to this CTA's barriers or shared memory
+  // A launch that did not wait for its predecessor before its work waits for it now, after its last
+  // store: the kernel then cannot complete before everything queued ahead of it has, so completion
+  // order along the stream stays transitive for whatever is queued next.
+  if (p.independent) griddep_wait();
   if (threadIdx.x == 0 && p.trace != nullptr) {
     trace2(p, 3);
     p.trace[(size_t)blockIdx.x * kTraceWords + 4] = global_timer_ns();
@@ -594,6 +628,11 @@ int gemm_f16_pair_launch(const helix_cfg_t& cfg, const void* A, int64_t lda, con
   const int smax = gemm_f16_pair_max_stages(bn);
   p.stages = cfg.stages > 0 ? std::min(cfg.stages, smax) : smax;
   if (p.stages < 2) return HELIX_ERR_UNSUPPORTED;
+  p.group = p.stages >= 6 ? 3 : (p.stages >= 4 ? 2 : 1);
+  if ((cfg.probe >> 4) & 7) p.group = (cfg.probe >> 4) & 7;   // tuning override
+  while (p.group > 1 && p.stages / p.group < 2) --p.group;
+  p.stages = p.stages / p.group * p.group;
+  p.fd_grp = make_fastdiv(p.group);
   p.load_warps = std::max(1, std::min({cfg.load_group > 0 ? cfg.load_group : 2, kPairProducerWarps, p.stages}));
   p.fd_per_batch = make_fastdiv(p.tiles_m * p.tiles_n);
   p.fd_group = make_fastdiv(p.raster * p.tiles_n);
@@ -616,6 +655,7 @@ int gemm_f16_pair_launch(const helix_cfg_t& cfg, const void* A, int64_t lda, con
     fixup = true;
   }
   p.trace = gemm_f16_trace_for_grid(2 * pairs);
+  p.probe = cfg.probe & 7;
   // a launch that shares its workspace with its neighbours on the stream is never independent of them
   p.independent = (independent && !fixup) ? 1 : 0;
   CUtensorMap ta, tb, tc;

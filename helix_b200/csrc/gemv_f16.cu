@@ -28,9 +28,12 @@ gemv_f16_kernel(const __half* __restrict__ W, int64_t ldw, const __half* __restr
   //   1  W is not written by it (weights): the first batch of W loads is issued, THEN the kernel
   //      waits, then reads X and later writes Y -- launch latency and ramp-up hide behind the
   //      predecessor's tail while X may still be its output;
-  //   2  nothing is shared with it: never wait.
+  //   2  nothing is shared with it: no wait before the work.
+  // In modes 1 and 2 every thread that has not waited yet does so just before it exits, after its last
+  // store: this kernel then cannot complete before its predecessor has, so a later kernel that waits
+  // for this one is still ordered after everything queued earlier.
   griddep_launch_dependents();
-  bool waited = order_mode != 1;
+  bool waited = order_mode == 0;
   if (order_mode == 0) griddep_wait();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -63,7 +66,7 @@ gemv_f16_kernel(const __half* __restrict__ W, int64_t ldw, const __half* __restr
           else wv[u][r] = make_uint4(0u, 0u, 0u, 0u);
         }
       }
-      if (!waited) {   // warp-uniform
+      if (!waited && order_mode == 1) {   // warp-uniform
         griddep_wait();
         waited = true;
       }
@@ -101,7 +104,7 @@ gemv_f16_kernel(const __half* __restrict__ W, int64_t ldw, const __half* __restr
         for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
         acc[r][i] = v;
       }
-    if (!waited) {   // empty K range: still order the stores after the predecessor
+    if (!waited && order_mode == 1) {   // empty K range: still order the stores after the predecessor
       griddep_wait();
       waited = true;
     }
@@ -120,6 +123,7 @@ gemv_f16_kernel(const __half* __restrict__ W, int64_t ldw, const __half* __restr
       }
     }
   }
+  if (!waited) griddep_wait();
 }
 
 // Sums the split-K partials in slice order (deterministic) and rounds once.
@@ -281,7 +285,8 @@ int gemv_f16_static_launch(const void* W, int64_t ldw, const void* X, int64_t ld
       (reinterpret_cast<uintptr_t>(X) & 15))
     return HELIX_ERR_ALIGN;
   if (split_k > 1 && (K + split_k - 1) / split_k < 256) split_k = 1;
-  if ((size_t)split_k * (size_t)m * (size_t)rows > kGemvStaticFloats) return HELIX_ERR_CAPACITY;
+  // a single pass over K (split_k = 1, asked for or after the clamp above) never touches the array
+  if (split_k > 1 && (size_t)split_k * (size_t)m * (size_t)rows > kGemvStaticFloats) return HELIX_ERR_CAPACITY;
 
   static std::mutex mu;
   static float* scratch_on_device[64] = {nullptr};

@@ -115,13 +115,14 @@ def kernel_name(launch):
 
 
 def make_cfg(op, tile_m=128, tile_n=128, tile_k=64, stages=0, cta_group=1, split_k=1, swap_ab=0, raster=8,
-             thread_m=0, thread_n=0, load_group=0, stream_k=0, conv_gather=0):
+             thread_m=0, thread_n=0, load_group=0, stream_k=0, conv_gather=0, probe=0):
     c = Cfg()
     c.op, c.tile_m, c.tile_n, c.tile_k, c.stages = op, tile_m, tile_n, tile_k, stages
     c.cta_group, c.split_k, c.swap_ab, c.raster, c.thread_m, c.thread_n = cta_group, split_k, swap_ab, raster, thread_m, thread_n
     c.load_group = load_group
     c.stream_k = stream_k
     c.conv_gather = conv_gather
+    c.probe = probe
     return c
 
 

@@ -96,7 +96,12 @@ typedef struct helix_cfg {
   int max_ctas;  /* > 0: the launch spreads over at most this many SMs (also honoured when the rest of
                     the struct is zero, i.e. with the library's own choice): lets two independent
                     launches on two streams share the machine, each with longer-lived CTAs      */
-  int reserved[1];
+  int probe;     /* tuning instrument, 0 in normal use.  GEMM_F16 / CONV_F16 through a tensor map: bit 0 = the
+                    issuing thread skips its tcgen05.mma instructions, bit 1 = the A-side operand is not
+                    loaded, bit 2 = the B-side operand is not loaded.  Timing such a launch separates
+                    operand delivery from tensor-core time; its output is meaningless.  Bits 4-5, when not
+                    zero, fix how many ring stages share one arrival barrier (1 -> 1, 2 -> 2, 3 -> 4 stages);
+                    results are not affected                                                        */
 } helix_cfg_t;
 
 /* A fully described launch; the tagged union the timing entry point iterates. */
@@ -121,7 +126,9 @@ typedef struct helix_launch {
 /* The caller asserts that nothing this launch reads or writes is written by the kernel queued just
  * before it on the same stream (independent shapes of a sweep).  The kernel then does not wait for
  * that kernel to finish before it loads operands, so consecutive launches overlap at their edges.
- * Without the flag only the set-up phase overlaps.  Ignored for launches that use a workspace. */
+ * Without the flag only the set-up phase overlaps.  Ignored for launches that use a workspace.
+ * A flagged kernel still waits for its predecessor before it exits, so it never completes first: a
+ * later launch that is ordered after the flagged one is ordered after everything queued before it. */
 #define HELIX_LAUNCH_INDEPENDENT 1u
 /* GEMV: the caller asserts that operand `a` (the matrix W: weights) is not written by the kernel
  * queued just before this launch, while X may be.  The kernel issues its first batch of W loads,
@@ -218,7 +225,8 @@ int helix_conv2d_f16_nhwc_host(const void* x, const void* w, void* y, int N, int
 /* Split-K GEMV (same result as helix_gemv_f16 with cfg.split_k = split_k) that never touches the
  * device allocator: the fp32 partial sums go to a 4 MiB array compiled into the library instead
  * of a caller workspace, so split_k * m * rows may not exceed HELIX_GEMV_STATIC_FLOATS, else
- * HELIX_ERR_CAPACITY.  It has no counterpart in the reference.  Meant for callers that cannot
+ * HELIX_ERR_CAPACITY (split_k as used: a split that would leave fewer than 256 elements of K per slice runs
+ * as split_k = 1, and a single-pass GEMV never touches the array, so it is never rejected for size).  It has no counterpart in the reference.  Meant for callers that cannot
  * allocate when they need the product, e.g. a decode loop that has given all HBM to its own
  * pool.  The first call on each device looks up the array's device address (the set-up), so
  * make that first call before any stream capture begins.  The array is shared by all calls and keeps the last call's partials; a call overwrites every slot before

@@ -82,6 +82,54 @@ int oracle_sgemm_f64acc(const float* a, const float* b, float* c, int M, int N, 
   return ORACLE_OK;
 }
 
+/* One (vm2, vn2) cell of either template for one vk2 step: k1 x m1 x n1 multiply-adds into the C
+ * rows at `cl`; B rows are `ldb` floats apart (n1 in the packed panel, N in the plain matrix). */
+__attribute__((target_clones("arch=x86-64-v4", "default")))
+static void micro_kernel(const float* restrict a, size_t lda, int mrows, int kc_valid,
+                         const float* restrict bp, size_t ldb, float* restrict cl, size_t ldcl,
+                         int m1, int k1, int n1, int fma) {
+  /* one (vm2, vn2) cell for one vk2 step: k1 x m1 x n1 */
+  if ((n1 & 15) == 0 && m1 <= 16 && k1 <= 16) {
+    /* Same sums in the same k order per output, with vk1 moved inside vm1/vn1 so the C row
+     * chunk stays in a vector register across the k1 steps (what unrolling vk1 and vm1 and
+     * vectorising vn1 gives the reference's generated code). */
+    typedef float v16 __attribute__((vector_size(64), aligned(4)));
+    float av[16][16];
+    for (int vm1 = 0; vm1 < m1; ++vm1)
+      for (int vk1 = 0; vk1 < k1; ++vk1)
+        av[vm1][vk1] = (vm1 < mrows && vk1 < kc_valid) ? a[(size_t)vm1 * lda + vk1] : 0.0f;
+    for (int c0 = 0; c0 < n1; c0 += 16) {
+      for (int vm1 = 0; vm1 < m1; ++vm1) {
+        float* crow = cl + (size_t)vm1 * ldcl + c0;
+        v16 acc = *(const v16*)crow;
+        for (int vk1 = 0; vk1 < k1; ++vk1) {
+          const v16 bv = *(const v16*)(bp + (size_t)vk1 * ldb + c0);
+          const float s = av[vm1][vk1];
+          if (fma) {
+            for (int i = 0; i < 16; ++i) acc[i] = fmaf(s, bv[i], acc[i]);
+          } else {
+            acc += s * bv;
+          }
+        }
+        *(v16*)crow = acc;
+      }
+    }
+    return;
+  }
+  for (int vk1 = 0; vk1 < k1; ++vk1) {
+    const float* brow = bp + (size_t)vk1 * ldb;
+    for (int vm1 = 0; vm1 < m1; ++vm1) {
+      const float av = (vm1 < mrows && vk1 < kc_valid) ? a[(size_t)vm1 * lda + vk1] : 0.0f;
+      float* crow = cl + (size_t)vm1 * ldcl;
+      if (fma) {
+        for (int vn1 = 0; vn1 < n1; ++vn1) crow[vn1] = fmaf(av, brow[vn1], crow[vn1]);
+      } else {
+        for (int vn1 = 0; vn1 < n1; ++vn1) crow[vn1] += av * brow[vn1];
+      }
+    }
+  }
+}
+
 /* ------------------------------------------------------------------------- */
 /* Single-thread register-blocked template, scripts/x86_CPU/profile_x86_CPU.py */
 /* :40-60.  split vm -> (vm3, m2, m1), vn -> (vn3, n2, n1), vk -> (vk2, k1);   */
@@ -102,23 +150,50 @@ int oracle_sgemm_template(const float* a, const float* b, float* c, int M, int N
       for (int vk2 = 0; vk2 < K / k1; ++vk2)
         for (int vm2 = 0; vm2 < m2; ++vm2)
           for (int vn2 = 0; vn2 < n2; ++vn2)
-            for (int vk1 = 0; vk1 < k1; ++vk1) {
-              const int k = vk2 * k1 + vk1;
-              for (int vm1 = 0; vm1 < m1; ++vm1) {
-                const int m = (vm3 * m2 + vm2) * m1 + vm1;
-                const float av = a[(size_t)m * K + k];
-                float* crow = c + (size_t)m * N + (vn3 * n2 + vn2) * n1;
-                const float* brow = b + (size_t)k * N + (vn3 * n2 + vn2) * n1;
-                if (fma) {
-                  for (int vn1 = 0; vn1 < n1; ++vn1) crow[vn1] = fmaf(av, brow[vn1], crow[vn1]);
-                } else {
-                  for (int vn1 = 0; vn1 < n1; ++vn1) crow[vn1] += av * brow[vn1];
-                }
-              }
+            {
+              const int m0 = (vm3 * m2 + vm2) * m1, n0 = (vn3 * n2 + vn2) * n1, k0 = vk2 * k1;
+              micro_kernel(a + (size_t)m0 * K + k0, (size_t)K, m1, k1, b + (size_t)k0 * N + n0, (size_t)N,
+                           c + (size_t)m0 * N + n0, (size_t)N, m1, k1, n1, fma);
             }
     }
   }
   return ORACLE_OK;
+}
+
+/* Seconds per call of oracle_sgemm_template on seeded operands, timed inside C (the probes of the    */
+/* reference's profile, scripts/x86_CPU/profile_x86_CPU.py:70-91, last microseconds: its evaluator     */
+/* averages 1000 runs).  Runs are repeated until `min_seconds` have gone by, at least 3 times.         */
+#include <time.h>
+static double now_s(void) {
+  struct timespec ts;
+  clock_gettime(CLOCK_MONOTONIC, &ts);
+  return (double)ts.tv_sec + 1e-9 * (double)ts.tv_nsec;
+}
+double oracle_time_sgemm_template(int M, int N, int K, int m1, int m2, int n1, int n2, int k1, int fma,
+                                  double min_seconds) {
+  float* a = (float*)aligned_alloc(64, (((size_t)M * K * 4) + 63) / 64 * 64);
+  float* b = (float*)aligned_alloc(64, (((size_t)K * N * 4) + 63) / 64 * 64);
+  float* c = (float*)aligned_alloc(64, (((size_t)M * N * 4) + 63) / 64 * 64);
+  if (!a || !b || !c) { free(a); free(b); free(c); return -1.0; }
+  uint32_t st = 12345u;
+  for (size_t i = 0; i < (size_t)M * K; ++i) { st = st * 1664525u + 1013904223u; a[i] = (float)(st >> 8) * (1.0f / 16777216.0f); }
+  for (size_t i = 0; i < (size_t)K * N; ++i) { st = st * 1664525u + 1013904223u; b[i] = (float)(st >> 8) * (1.0f / 16777216.0f); }
+  double result = -1.0;
+  if (oracle_sgemm_template(a, b, c, M, N, K, m1, m2, n1, n2, k1, fma) == ORACLE_OK) {
+    long runs = 0;
+    const double t0 = now_s();
+    double t1 = t0;
+    do {
+      for (int r = 0; r < 16; ++r) oracle_sgemm_template(a, b, c, M, N, K, m1, m2, n1, n2, k1, fma);
+      runs += 16;
+      t1 = now_s();
+    } while (t1 - t0 < min_seconds || runs < 3);
+    result = (t1 - t0) / (double)runs;
+  }
+  volatile float sink = c[0];
+  (void)sink;
+  free(a); free(b); free(c);
+  return result;
 }
 
 /* ------------------------------------------------------------------------- */
@@ -131,52 +206,6 @@ int oracle_sgemm_template(const float* a, const float* b, float* c, int M, int N
 /* Inputs need not be padded: out-of-range A/B elements read as zero, which is */
 /* what the reference's padded random buffers amount to for the valid region.  */
 /* ------------------------------------------------------------------------- */
-__attribute__((target_clones("arch=x86-64-v4", "default")))
-static void micro_kernel(const float* restrict a, size_t lda, int mrows, int kc_valid,
-                         const float* restrict bp, float* restrict cl, size_t ldcl,
-                         int m1, int k1, int n1, int fma) {
-  /* one (vm2, vn2) cell for one vk2 step: k1 x m1 x n1 */
-  if ((n1 & 15) == 0 && m1 <= 16 && k1 <= 16) {
-    /* Same sums in the same k order per output, with vk1 moved inside vm1/vn1 so the C row
-     * chunk stays in a vector register across the k1 steps (what unrolling vk1 and vm1 and
-     * vectorising vn1 gives the reference's generated code). */
-    typedef float v16 __attribute__((vector_size(64), aligned(4)));
-    float av[16][16];
-    for (int vm1 = 0; vm1 < m1; ++vm1)
-      for (int vk1 = 0; vk1 < k1; ++vk1)
-        av[vm1][vk1] = (vm1 < mrows && vk1 < kc_valid) ? a[(size_t)vm1 * lda + vk1] : 0.0f;
-    for (int c0 = 0; c0 < n1; c0 += 16) {
-      for (int vm1 = 0; vm1 < m1; ++vm1) {
-        float* crow = cl + (size_t)vm1 * ldcl + c0;
-        v16 acc = *(const v16*)crow;
-        for (int vk1 = 0; vk1 < k1; ++vk1) {
-          const v16 bv = *(const v16*)(bp + (size_t)vk1 * n1 + c0);
-          const float s = av[vm1][vk1];
-          if (fma) {
-            for (int i = 0; i < 16; ++i) acc[i] = fmaf(s, bv[i], acc[i]);
-          } else {
-            acc += s * bv;
-          }
-        }
-        *(v16*)crow = acc;
-      }
-    }
-    return;
-  }
-  for (int vk1 = 0; vk1 < k1; ++vk1) {
-    const float* brow = bp + (size_t)vk1 * n1;
-    for (int vm1 = 0; vm1 < m1; ++vm1) {
-      const float av = (vm1 < mrows && vk1 < kc_valid) ? a[(size_t)vm1 * lda + vk1] : 0.0f;
-      float* crow = cl + (size_t)vm1 * ldcl;
-      if (fma) {
-        for (int vn1 = 0; vn1 < n1; ++vn1) crow[vn1] = fmaf(av, brow[vn1], crow[vn1]);
-      } else {
-        for (int vn1 = 0; vn1 < n1; ++vn1) crow[vn1] += av * brow[vn1];
-      }
-    }
-  }
-}
-
 int oracle_sgemm_parallel(const float* a, const float* b, float* c, int M, int N, int K,
                           int m1, int m2, int m3, int n1, int n2, int n3, int k1,
                           int threads, int fma) {
@@ -228,7 +257,7 @@ int oracle_sgemm_parallel(const float* a, const float* b, float* c, int M, int N
                     int mrows = M - m0; if (mrows > m1) mrows = m1; if (mrows < 0) mrows = 0;
                     int kval = K - k0; if (kval > k1) kval = k1; if (kval < 0) kval = 0;
                     micro_kernel(a + (size_t)(m0 < M ? m0 : 0) * K + (k0 < K ? k0 : 0), (size_t)K, mrows, kval,
-                                 bp + ((((size_t)vn3 * kb + vk2) * n2 + vn2) * k1) * n1,
+                                 bp + ((((size_t)vn3 * kb + vk2) * n2 + vn2) * k1) * n1, (size_t)n1,
                                  cl + (size_t)m0 * nc + (vn3 * n2 + vn2) * n1, (size_t)nc, m1, k1, n1, fma);
                   }
           }

@@ -82,3 +82,73 @@ def test_gemm_split_along_n_matches_the_unsplit_product_and_the_oracle(oracle):
     rows = [0, 127, 128, 383]
     _, ref = oracle.hgemm_naive(np.ascontiguousarray(a[rows]), b)
     assert_f16_close(full[rows], ref, "N-split GEMM")
+
+
+def _check_unit_against_oracle(oracle, u, a, b, out, what):
+    """One unit of the sweep against the CPU oracle: whole output for a plain GEMM, three batch entries of a
+    batched GEMM, first / middle / last image of a convolution."""
+    import numpy as np
+    from tests.util import assert_f16_close
+    s = u["shape"]
+    if u["kind"] == "gemm" and len(s) == 3:
+        _, ref32 = oracle.hgemm_fast(a.cpu().numpy(), b.cpu().numpy())
+        assert_f16_close(out.cpu().numpy(), ref32, what)
+        return 1
+    if u["kind"] == "gemm":
+        batch = s[3]
+        for i in sorted({0, batch // 2, batch - 1}):
+            _, ref32 = oracle.hgemm_naive(a[i].cpu().numpy(), b[i].cpu().numpy())
+            assert_f16_close(out[i].cpu().numpy(), ref32, f"{what} batch entry {i}")
+        return 1
+    stride, pad = s[7], s[8]
+    w = b.cpu().numpy()
+    for img in sorted({0, s[0] // 2, s[0] - 1}):
+        _, y32 = oracle.conv2d_nhwc_f16(np.ascontiguousarray(a[img:img + 1].cpu().numpy()), w, stride, pad)
+        assert_f16_close(out[img:img + 1].cpu().numpy(), y32, f"{what} image {img}")
+    return 1
+
+
+@pytest.mark.parametrize("lanes", [2, 1])
+def test_model_level_sweep_at_full_size_against_the_oracle(oracle, lanes):
+    """The benchmark's own workload and launch configuration: every GEMM of BERT-base at batch 16 / seq 512 and
+    the 53 ResNet-50 convolutions at batch 32, dealt to `lanes` concurrent chains with each launch limited to
+    1 / lanes of the SMs (the library re-chooses its tile for the smaller machine), independent-launch flag set.
+    Every distinct shape (4 linear GEMMs, the two batched attention GEMMs, 23 convolutions, among them the 7x7
+    stem with 3 channels stored as 8, the 7x7-pixel layers and the strided 1x1 projections) is compared with
+    the oracle; then the same step replayed from a CUDA graph, as the benchmark times it, must reproduce the
+    eager outputs bit for bit."""
+    units = workloads.model_level_sweep()
+    sw = sweep.Sweep(units, seed=4000, lanes=lanes)
+    n = sw.step()
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert n >= len(units)
+    seen, checked = set(), 0
+    for u, (a, b, out) in zip(units, sw.tensors):
+        key = (u["kind"], tuple(u["shape"]))
+        if key in seen:
+            continue
+        seen.add(key)
+        checked += _check_unit_against_oracle(oracle, u, a, b, out, f"{u['name']} {u['shape']} lanes={lanes}")
+    assert checked == 4 + 2 + 23
+    # every unit, repeated layers included: a repeated shape must give what its first instance gave on its own data
+    eager = [out.clone() for _, _, out in sw.tensors]
+    for _, _, out in sw.tensors:
+        out.zero_()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        sw.step()
+    g.replay()
+    torch.cuda.synchronize()
+    ops.check_status()
+    for u, want, (_, _, out) in zip(units, eager, sw.tensors):
+        assert torch.equal(want, out), u["name"]
+    # last instance of each repeated shape (other buffers, other position in the chains) against the oracle too
+    last = {}
+    for i, u in enumerate(units):
+        last[(u["kind"], tuple(u["shape"]))] = i
+    for key, i in last.items():
+        u = units[i]
+        if u["kind"] == "gemm" and i >= 6:       # a later BERT layer
+            a, b, out = sw.tensors[i]
+            _check_unit_against_oracle(oracle, u, a, b, out, f"{u['name']} (last instance) lanes={lanes}")

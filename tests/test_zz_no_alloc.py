@@ -34,14 +34,27 @@ def test_static_scratch_gemv_matches_workspace_gemv_twice_in_a_row(lib, oracle):
     for rows, K, m, split in cases:
         wn, xn = datagen.c2_gemv(rows, K, m, seed=21)
         w, x = torch.from_numpy(wn).cuda(), torch.from_numpy(xn).cuda()
-        rc, got = _static(lib, w, x, split)
+        out = torch.full((m, rows), float("nan"), dtype=torch.float16, device="cuda")
+        _static(lib, w, x, split)                     # first call on this device: does the symbol look-up
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        torch_before = torch.cuda.memory_allocated()
+        rc = lib.helix_gemv_f16_static(w.data_ptr(), w.stride(0), x.data_ptr(), x.stride(0), out.data_ptr(),
+                                       out.stride(0), 1, rows, K, m, split,
+                                       ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
         assert rc == 0
+        # the point of the entry point: the call took no device memory, from the driver or from torch
+        assert free_after == free_before and torch.cuda.memory_allocated() == torch_before
+        got = out
         cfg = ops.make_cfg(OP_GEMV_F16, tile_m=1, tile_n=(2 if m <= 2 else 1), tile_k=256, split_k=split,
                            load_group=(4 if m <= 4 else 2))
         want = ops.gemv_f16(w, x, cfg=cfg)            # the existing entry point, caller workspace
         torch.cuda.synchronize()
         got_n, want_n = got.cpu().numpy(), want.cpu().numpy()
-        util.assert_f16_close(got_n, want_n.astype(np.float32), f"static vs workspace GEMV {rows}x{K} m={m}")
+        # same kernel, same slices, same summation order: the two entry points agree bit for bit
+        assert np.array_equal(got_n.view(np.uint16), want_n.view(np.uint16)), f"static vs workspace GEMV {rows}x{K} m={m}"
         _, ref32 = oracle.hgemm_naive(xn, wn)
         util.assert_f16_close(got_n, ref32, f"static GEMV vs oracle {rows}x{K} m={m}")
 
@@ -54,3 +67,16 @@ def test_static_scratch_gemv_rejects_what_does_not_fit(lib):
     rc = lib.helix_gemv_f16_static(w.data_ptr(), K, x.data_ptr(), K, y.data_ptr(), rows, 1, rows, K, m, split, None)
     assert rc == -8
     assert b"capacity" in lib.helix_status_string(rc)
+
+
+def test_static_scratch_gemv_single_pass_is_never_rejected_for_size(lib, oracle):
+    """split_k = 1 (asked for, or what a short K is clamped to) does not use the array: no capacity limit."""
+    rows, K, m = 200000, 256, 8                       # 8 * 200000 floats > 1 Mi floats
+    wn, xn = datagen.c2_gemv(rows, K, m, seed=5)
+    w, x = torch.from_numpy(wn).cuda(), torch.from_numpy(xn).cuda()
+    for split in (1, 4):                              # 4 slices of 64 < 256 elements: runs as one pass
+        rc, got = _static(lib, w, x, split)
+        torch.cuda.synchronize()
+        assert rc == 0
+        _, ref32 = oracle.hgemm_naive(xn[:, :], wn[:4096])
+        util.assert_f16_close(got.cpu().numpy()[:, :4096], ref32, f"single-pass static GEMV split={split}")
