@@ -1,15 +1,17 @@
 #!/usr/bin/env python
 """Benchmark of the Helix hot path on B200: the model-level fp16 GEMM / convolution sweep.
 
-One step = one pass over the model-level sweep (every GEMM of a BERT-base encoder at batch 16,
-seq 512 plus the 53 ResNet-50 convolutions at batch 32, 125 independent units, 1.81 TFLOP).
-Each rank runs the whole sweep on its own GPU with its own data (weak scaling, no collective
-in the data path).  Prints ONE JSON line (rank 0).
+Work list: INSTANCES copies (distinct seeded data) of the model-level sweep -- every GEMM of a BERT-base
+encoder at batch 16 / seq 512 and the 53 ResNet-50 convolutions at batch 32, 125 independent units and
+1.81 TFLOP per copy.  With N GPUs the list is partitioned over the ranks (longest-processing-time-first on
+a roofline estimate, no collective in the data path); the job's time is the slowest rank's, so the figure
+is strong scaling of a fixed list.  One step = PASSES passes over the list, so that the default timed region
+lasts seconds, not milliseconds.  Prints ONE JSON line (rank 0).
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl helix|reference]
 
-`--impl reference` times the CPU restatement of the reference's x86 template (the reference's
-own CPU path is TVM generated and cannot be built here) on a bounded sample of the same sweep.
+`--impl reference` times the CPU restatement of the reference's x86 template (its own CPU path is TVM
+generated and cannot be built here) with all host threads, one pass over one copy of the sweep per step.
 """
 import argparse
 import json
@@ -24,7 +26,10 @@ sys.path.insert(0, ROOT)
 
 METRIC = "fp16_gemm_conv_sweep_tflops"
 UNIT = "TFLOP/s"
-WORKLOAD = "model-level sweep: BERT-base b16 s512 (72 GEMMs incl. batched QK^T/PV) + ResNet-50 b32 224x224 (53 convs)"
+INSTANCES = 8        # copies of the model-level sweep in the work list
+PASSES = 6           # passes over the list per step
+WORKLOAD = ("model-level sweep: BERT-base b16 s512 (72 GEMMs incl. batched QK^T/PV) + ResNet-50 b32 224x224 "
+            "(53 convs), work list = %d seeded copies (%d units)" % (INSTANCES, INSTANCES * 125))
 
 
 def read_peaks():
@@ -37,69 +42,92 @@ def read_peaks():
     return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
 
 
-# ----------------------------------------------------------------------------------------------
-# CPU arm: the oracle's restatement of the x86 template on a bounded sample of the sweep
-# ----------------------------------------------------------------------------------------------
-def cpu_sample_units():
-    """One BERT layer's four linear GEMMs, 8 of its 192 batched attention GEMMs of each kind,
-    and three ResNet-50 convolutions as GEMMs (M = B*Ho*Wo, N = OC, K = IC*kH*kW, batch 4)."""
-    return [
-        ("bert.qkv", (8192, 2304, 768), 1), ("bert.out_proj", (8192, 768, 768), 1),
-        ("bert.ffn_up", (8192, 3072, 768), 1), ("bert.ffn_down", (8192, 768, 3072), 1),
-        ("bert.qk", (512, 512, 64), 8), ("bert.pv", (512, 64, 512), 8),
-        ("resnet.s1.conv2", (4 * 56 * 56, 64, 576), 1), ("resnet.s3.conv2", (4 * 14 * 14, 256, 2304), 1),
-        ("resnet.s4.conv3", (4 * 7 * 7, 2048, 512), 1),
-    ]
+def host_threads():
+    """Threads the CPU arm uses: the CPUs this process may run on.  Passed to the oracle explicitly, so that an
+    OMP_NUM_THREADS=1 inherited from a launcher cannot shrink it."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
 
-def run_cpu_sample(min_seconds=10.0):
-    """Seconds per pass, flops per pass, threads and passes of the sample with all host threads (fp32, as
-    the reference's x86 backend computes); whole passes are repeated until `min_seconds` have gone by."""
-    import numpy as np
-    from oracle import api
-    units = cpu_sample_units()
-    rng = np.random.default_rng(4)
-    mats = []
-    for _, (M, N, K), cnt in units:
-        s = np.float32(1.0 / np.sqrt(K))
-        a = (rng.standard_normal((M, K), dtype=np.float32) * s)
-        b = (rng.standard_normal((K, N), dtype=np.float32) * s)
-        mats.append((a, b, np.empty((M, N), np.float32), cnt))
-    flops = sum(2.0 * M * N * K * cnt for _, (M, N, K), cnt in units)
-    api.sgemm_parallel(mats[1][0], mats[1][1], out=mats[1][2])  # warm the thread pool
-    passes = 0
-    t0 = time.perf_counter()
-    while True:
-        for a, b, c, cnt in mats:
+# ----------------------------------------------------------------------------------------------
+# CPU arm: the oracle's restatement of the x86 template on one copy of the sweep
+# ----------------------------------------------------------------------------------------------
+class CpuSweep:
+    """One copy of the model-level sweep as the reference's x86 backend would run it: every unit an fp32
+    GEMM (a convolution as M = B*Ho*Wo, N = OC, K = IC*kH*kW, the reference's own mapping), the parallel
+    packed schedule with the tiling its profile-driven chooser picks per shape.  Repeated shapes share
+    their operand buffers."""
+
+    def __init__(self, threads):
+        import numpy as np
+        from helix_b200 import workloads
+        from oracle import api, x86_tiling
+        self.api, self.threads = api, threads
+        self.prof, self.prof_info = x86_tiling.profile()
+        self.calls = []       # (a, b, c, tiling, count)
+        self.flops = 0.0
+        shapes = {}
+        for u in workloads.model_level_sweep():
+            s = u["shape"]
+            if u["kind"] == "gemm":
+                M, N, K = s[:3]
+                cnt = s[3] if len(s) > 3 else 1
+            else:
+                B, IC, H, W, OC, kh, kw, stride, pad = s
+                Ho, Wo = (H + 2 * pad - kh) // stride + 1, (W + 2 * pad - kw) // stride + 1
+                M, N, K, cnt = B * Ho * Wo, OC, IC * kh * kw, 1
+            shapes[(M, N, K)] = shapes.get((M, N, K), 0) + cnt
+            self.flops += 2.0 * M * N * K * cnt
+        rng = np.random.default_rng(4)
+        self.tilings = {}
+        for (M, N, K), cnt in shapes.items():
+            s = np.float32(1.0 / np.sqrt(K))
+            a = rng.standard_normal((M, K), dtype=np.float32) * s
+            b = rng.standard_normal((K, N), dtype=np.float32) * s
+            tl = x86_tiling.get_tiling(self.prof, M, N, K, threads)
+            self.tilings[(M, N, K)] = tl
+            self.calls.append((a, b, np.empty((M, N), np.float32), tl, cnt))
+
+    def one_pass(self):
+        t0 = time.perf_counter()
+        for a, b, c, tl, cnt in self.calls:
             for _ in range(cnt):
-                api.sgemm_parallel(a, b, out=c)
-        passes += 1
-        if time.perf_counter() - t0 >= min_seconds:
-            break
-    dt = (time.perf_counter() - t0) / passes
-    return dt, flops, api.max_threads(), passes
+                self.api.sgemm_parallel(a, b, tiling=tl, threads=self.threads, fma=True, out=c)
+        return time.perf_counter() - t0
+
+    def sample_text(self, seconds):
+        return ("one pass over one copy of the sweep: all 125 units (%d distinct GEMM shapes, convolutions as "
+                "M=B*Ho*Wo N=OC K=IC*kH*kW at batch 32), fp32 x86-template restatement with fused multiply-add, "
+                "tiling per shape from the restated profile (%d register blocks kept, best single-thread probe "
+                "%.0f GFLOP/s against the reference's 0.6 x 153), %.2f TFLOP in %.1f s"
+                % (len(self.calls), self.prof_info["register_blocks_kept"], self.prof_info["best_probe_gflops"],
+                   self.flops / 1e12, seconds))
 
 
 def bench_reference(args, rank, world):
     if rank != 0:
         return
+    cores = host_threads()
+    if cores < 2 and (os.cpu_count() or 1) >= 2:
+        raise SystemExit("reference arm: only %d usable CPU of %d" % (cores, os.cpu_count()))
+    cpu = CpuSweep(cores)
     times = []
-    flops = cores = passes = None
     for i in range(args.warmup + args.steps):
-        dt, flops, cores, passes = run_cpu_sample()
+        dt = cpu.one_pass()
         if i >= args.warmup:
             times.append(dt)
     avg = sum(times) / len(times)
-    value = flops / avg / 1e12
-    sample = ("one BERT-base layer (4 linear GEMMs + 8 of 192 QK^T and PV GEMMs) and 3 ResNet-50 convs as "
-              "GEMMs at batch 4, fp32, %.1f GFLOP per pass, %d passes (>= 10 s) per step" % (flops / 1e9, passes))
+    value = cpu.flops / avg / 1e12
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": avg * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "note": "bounded CPU sample of the sweep; a step repeats the sample pass for >= 10 s and ms_per_step "
-                                                  "is the time of one pass; throughput extrapolates"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "step": "one pass over one copy of the sweep (1/%d of the list, every "
+                                                  "distinct unit in its real count)" % INSTANCES},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "gflops_per_core": value * 1e3 / cores, "sample": cpu.sample_text(avg)},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -137,7 +165,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, reasons, mx = [], set(), None
+        sm, reasons, mx, power = [], set(), None, []
         try:
             with open(self.path) as f:
                 for line in f:
@@ -147,6 +175,7 @@ class ClockSampler:
                     try:
                         sm.append(float(p[1]))
                         mx = float(p[2])
+                        power.append(float(p[3]))
                     except ValueError:
                         continue
                     for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
@@ -157,47 +186,77 @@ class ClockSampler:
         except Exception:
             pass
         if sm:
-            sm.sort()
-            # the busy half of the samples: the sampler also sees the idle edges of the region
-            busy = sm[len(sm) // 2:]
+            # the samples taken under load: the sampler also sees the idle edges of the region
+            busy = sorted(s for s, w in zip(sm, power) if w >= 0.5 * max(power)) or sorted(sm)
             out["sm_mhz"] = busy[len(busy) // 2]
             out["sm_max_mhz"] = mx
-            out["sm_min_mhz_seen"] = sm[0]
+            out["sm_min_mhz_seen"] = min(sm)
+            out["power_w_max"] = max(power)
             out["samples"] = len(sm)
         out["reasons"] = sorted(reasons)
         return out
 
 
-def extras(peaks):
-    """Per-configuration figures beside the headline: GEMV GB/s, dense GEMM sweep, convs, fp32 GEMM."""
+def unit_estimate(u):
+    """Roofline estimate (seconds) of one unit, the cost the work list is partitioned by."""
+    from helix_b200 import workloads
+    return max(workloads.unit_flops(u) / 1.0e15, workloads.unit_bytes(u) / 5.0e12) + 4e-6
+
+
+def work_list():
+    from helix_b200 import workloads
+    units = []
+    for inst in range(INSTANCES):
+        for u in workloads.model_level_sweep():
+            v = dict(u)
+            v["name"] = "copy%d.%s" % (inst, u["name"])
+            v["index"] = len(units)
+            units.append(v)
+    return units
+
+
+def per_config_table(peaks):
+    """The configurations the baseline names, one compact row each: [microseconds, rate, fraction of peak]
+    (GB/s against the measured HBM copy rate for memory-bound rows, TFLOP/s against the measured burst tensor
+    peak or the nominal FFMA peak otherwise)."""
     import torch
     from helix_b200 import datagen, ops
     from helix_b200._lib import LAUNCH_INDEPENDENT, LAUNCH_STATIC_A
-    out = {}
     dev = "cuda"
-    # fp16 GEMV 4096 x 4096, m = 1: rotating W buffers (12 x 32 MiB > 2 x L2), CUDA-graph timing
+    out = {}
+    r3 = lambda us, rate, frac: [round(us, 2), round(rate, 1), round(frac, 3)]
+    # C2: fp16 GEMV 4096 x 4096, m = 1: twelve rotating W buffers (12 x 32 MiB > 2 x L2) in three
+    # launch-ordering modes, plus one 268 MB matrix (16384 x 8192) streamed by chains of ordered launches
     rows = K = 4096
     ws = [torch.randn(rows, K, device=dev, dtype=torch.float16) * 0.02 for _ in range(12)]
     x = torch.randn(1, K, device=dev, dtype=torch.float16)
     ys = [torch.empty(1, rows, device=dev, dtype=torch.float16) for _ in ws]
     ls = [ops.launch_gemv_f16(w, x, y) for w, y in zip(ws, ys)]
     gemv_bytes = rows * K * 2 + K * 2 + rows * 2
-    res = {}
-    # twelve distinct W / y pairs sharing only the read-only x: consecutive launches are independent.
-    # Also reported: weights-static ordering (X may come from the previous kernel) and full ordering.
+    g = {}
     for name, flag in (("independent", LAUNCH_INDEPENDENT), ("static_weights", LAUNCH_STATIC_A), ("ordered", 0)):
         for l in ls:
             l.flags = flag
         avg, _, _ = ops.time_launches(ls, warmup=5, iters=50, use_graph=True)
         gb = gemv_bytes / avg / 1e9
-        res[name] = {"us": avg * 1e6, "GB/s": gb, "frac_hbm_peak": gb / peaks["hbm_gbs"]}
-    out["gemv_4096x4096_m1"] = dict(res["independent"], launch_ordering=res)
+        g[name] = r3(avg * 1e6, gb, gb / peaks["hbm_gbs"])
     del ws, ys, ls
-    # fp16 dense GEMM sweep
-    gem = {}
+    big = [torch.randn(16384, 8192, device=dev, dtype=torch.float16) * 0.02 for _ in range(2)]
+    xb = torch.randn(1, 8192, device=dev, dtype=torch.float16)
+    yb = [torch.empty(1, 16384, device=dev, dtype=torch.float16) for _ in big]
+    ls = [ops.launch_gemv_f16(w, xb, y) for w, y in zip(big, yb)]
+    avg, _, _ = ops.time_launches(ls, warmup=3, iters=20, use_graph=True)
+    gb = (16384 * 8192 * 2 + 8192 * 2 + 16384 * 2) / avg / 1e9
+    g["16384x8192_ordered"] = r3(avg * 1e6, gb, gb / peaks["hbm_gbs"])
+    del big, yb, ls
+    out["gemv_4096x4096_m1 [us, GB/s, of_hbm]"] = g
+    # C3: dense fp16 GEMMs; memory-bound shapes rotate through > 2 x L2 of operands
+    c3 = {}
     for (M, N, K) in datagen.C3_SHAPES:
         by = 2.0 * (M * K + N * K + M * N)
-        nbuf = 1 if (2.0 * M * N * K / by) > 300 else int(300e6 // by) + 1
+        fl = 2.0 * M * N * K
+        membound = fl / by <= 300
+        nbuf = int(300e6 // by) + 1 if membound else 1
         bufs = [(torch.randn(M, K, device=dev, dtype=torch.float16) / K ** 0.5,
                  torch.randn(N, K, device=dev, dtype=torch.float16) / K ** 0.5,
                  torch.empty(M, N, device=dev, dtype=torch.float16)) for _ in range(nbuf)]
@@ -206,13 +265,14 @@ def extras(peaks):
             for l in ls:
                 l.flags = LAUNCH_INDEPENDENT
         avg, _, _ = ops.time_launches(ls, warmup=3, iters=20, use_graph=True)
-        tf = 2.0 * M * N * K / avg / 1e12
-        gem[f"{M}x{N}x{K}"] = {"us": avg * 1e6, "TFLOP/s": tf, "frac_tensor_peak": tf / peaks["tflops"],
-                               "GB/s": by / avg / 1e9, "frac_hbm_peak": by / avg / 1e9 / peaks["hbm_gbs"]}
+        tf = fl / avg / 1e12
+        gbs = by / avg / 1e9
+        c3["%dx%dx%d" % (M, N, K)] = (r3(avg * 1e6, gbs, gbs / peaks["hbm_gbs"]) + ["GB/s"]) if membound else \
+            (r3(avg * 1e6, tf, tf / peaks["tflops"]) + ["TFLOP/s"])
         del bufs, ls
-    out["gemm_f16"] = gem
-    # ResNet-style convolutions at batch 32
-    conv = {}
+    out["gemm_f16 [us, rate, of_peak]"] = c3
+    # C4: ResNet-style convolutions at batch 32, each rated against its own floor max(flops/peak, bytes/hbm)
+    c4 = {}
     for layer in datagen.C4_LAYERS:
         B, C, H, W, OC, kh, kw, s, p = layer
         xx = torch.rand(B, H, W, C, device=dev, dtype=torch.float16) * 2 - 1
@@ -223,42 +283,54 @@ def extras(peaks):
         avg, _, _ = ops.time_launches([l] * 4, warmup=3, iters=20, use_graph=True)
         fl = 2.0 * B * Ho * Wo * OC * C * kh * kw
         by = 2.0 * (xx.numel() + ww.numel() + yy.numel())
-        conv["x".join(map(str, layer))] = {"us": avg * 1e6, "TFLOP/s": fl / avg / 1e12,
-                                          "frac_tensor_peak": fl / avg / 1e12 / peaks["tflops"],
-                                          "GB/s": by / avg / 1e9}
-    out["conv_f16"] = conv
-    # fp32 FFMA GEMM: 1024^3 is the configuration the reference's CPU template runs; the larger squares show
-    # the kernel with the machine full.  Rated against the nominal FFMA peak and against the rate a
-    # register-resident FFMA stream of the same 8x8 block pattern reaches on this device.
-    ffma_measured = ops.probe_ffma_f32()
-    out["ffma_probe_tflops"] = ffma_measured
+        floor = max(fl / (peaks["tflops"] * 1e12), by / (peaks["hbm_gbs"] * 1e9))
+        c4["x".join(map(str, layer))] = r3(avg * 1e6, fl / avg / 1e12, floor / avg)
+    out["conv_f16 [us, TFLOP/s, of_roofline]"] = c4
+    # C1: fp32 FFMA GEMM 1024^3 (the configuration the reference's CPU template runs), nominal FFMA peak 74.4
+    c1 = {}
     for n in (1024, 2048, 4096):
         a = torch.rand(n, n, device=dev) * 2 - 1
         b = torch.rand(n, n, device=dev) * 2 - 1
         c = torch.empty(n, n, device=dev)
         avg, _, _ = ops.time_launches([ops.launch_gemm_f32(a, b, c)] * 4, warmup=3, iters=10, use_graph=True)
         tf = 2.0 * n ** 3 / avg / 1e12
-        out["gemm_f32_%d" % n] = {"us": avg * 1e6, "TFLOP/s": tf, "frac_ffma_peak_nominal_74.4": tf / 74.4,
-                                  "frac_ffma_probe": tf / ffma_measured}
+        c1[str(n)] = r3(avg * 1e6, tf, tf / 74.4)
         del a, b, c
-    # true-fp32 convolution (column matrix + weight transpose + FFMA GEMM, all three kernels timed)
-    from helix_b200 import harness
+    out["gemm_f32 [us, TFLOP/s, of_ffma_nominal_74.4]"] = c1
+    return out
+
+
+def extras(peaks):
+    """Further context rows: true-fp32 convolutions and the vendor libraries on the same box."""
+    import torch
+    from helix_b200 import datagen, harness, ops
+    out = {}
     c32 = {}
     for layer in datagen.C4_LAYERS[:2] + datagen.C4_LAYERS[3:4]:
         B, C, H, W, OC, kh, kw, s, p = layer
         t = harness.time_conv_f32(*layer)
         Ho, Wo = ops.conv_out_hw(H, W, kh, kw, s, p)
         tf = 2.0 * B * Ho * Wo * OC * C * kh * kw / t / 1e12
-        c32["x".join(map(str, layer))] = {"us": t * 1e6, "TFLOP/s": tf, "frac_ffma_peak_nominal_74.4": tf / 74.4,
-                                          "frac_ffma_probe": tf / ffma_measured}
+        c32["x".join(map(str, layer))] = {"us": round(t * 1e6, 1), "TFLOP/s": round(tf, 1), "of_ffma_nominal_74.4": round(tf / 74.4, 3)}
     out["conv_f32"] = c32
+    # vendor comparators (context only, never on the product path): cuBLAS fp16 with fp32 accumulate, cuDNN NHWC
+    comp = {}
+    try:
+        for (M, N, K) in datagen.C3_SHAPES:
+            ms, tf = harness.cublas_gemm_result(M, N, K)
+            comp["cublas %dx%dx%d" % (M, N, K)] = {"us": round(ms * 1e3, 1), "TFLOP/s": round(tf, 1)}
+        for layer in datagen.C4_LAYERS:
+            ms, tf = harness.cudnn_conv_result(*layer)
+            comp["cudnn " + "x".join(map(str, layer))] = {"us": round(ms * 1e3, 1), "TFLOP/s": round(tf, 1)}
+    except Exception as exc:     # a comparator that fails does not fail the benchmark
+        comp["error"] = repr(exc)
+    out["comparators"] = comp
     return out
 
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, averaged over the launches of
-# one sweep step) for each kernel of the sweep, from one single-pass ncu capture of
-#   python bench.py --steps 1 --warmup 3 --no-extras
-# Filled in below only for the kernels that capture listed; the others report null.
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, averaged over the launches of one
+# pass over one copy of the sweep) for each kernel, from single-pass ncu captures; the capture commands are
+# in profiles/bench_sweep_launch_list.md.  Kernels that capture did not list report null.
 SWEEP_DRAM_BYTES_PER_LAUNCH = {
     "gemm_f16_tc2_kernel<256>": 15810162, "gemm_f16_tc2_kernel<192>": 34526677,
     "gemm_f16_tc_kernel<256,0>": 30764491, "gemm_f16_tc_kernel<64,0>": 68126530,
@@ -266,15 +338,15 @@ SWEEP_DRAM_BYTES_PER_LAUNCH = {
 }
 
 
-def kernel_breakdown(sw, ops):
-    """Time the sweep's launches grouped by the kernel they resolve to (CUDA-graph replay, events on the
-    launching stream): launches, seconds and algorithmic flop / bytes per group."""
+def kernel_breakdown(sw, ops, limit_units=125):
+    """Time the launches of one copy of the sweep grouped by the kernel they resolve to (CUDA-graph replay,
+    events on the launching stream, each group alone on the whole machine): launches, seconds and algorithmic
+    flop / bytes per group."""
     from helix_b200 import workloads
     import ctypes
     from helix_b200._lib import Launch
     groups = {}
-    for u, l0 in zip(sw.units, sw.launches):
-        # each kernel is rated on the whole machine, whatever share of it the sweep's lanes give a launch
+    for u, l0 in list(zip(sw.units, sw.launches))[:limit_units]:
         l = Launch()
         ctypes.memmove(ctypes.byref(l), ctypes.byref(l0), ctypes.sizeof(Launch))
         ops.limit_ctas(l, 0)
@@ -294,6 +366,34 @@ def kernel_breakdown(sw, ops):
     return out
 
 
+def self_check(sw):
+    """Untimed: a few units of what was just timed (outputs of the last replay) against the CPU oracle.
+    Raises when one is outside the fp16 tolerance (relative Frobenius error 2e-3)."""
+    import numpy as np
+    from oracle import api as oracle
+    want = ["bert.l0.qkv", "bert.l0.qk", "bert.l0.pv", "resnet50.stem", "resnet50.s1b0.conv2", "resnet50.s4b2.conv3"]
+    checked, worst = 0, 0.0
+    for u, (a, b, out) in zip(sw.units, sw.tensors):
+        tag = u["name"].split(".", 1)[1]
+        if tag not in want:
+            continue
+        want.remove(tag)
+        s = u["shape"]
+        if u["kind"] == "gemm" and len(s) == 3:
+            got, (_, ref) = out.cpu().numpy(), oracle.hgemm_fast(a.cpu().numpy(), b.cpu().numpy())
+        elif u["kind"] == "gemm":
+            got, (_, ref) = out[0].cpu().numpy(), oracle.hgemm_naive(a[0].cpu().numpy(), b[0].cpu().numpy())
+        else:
+            got = out[:1].cpu().numpy()
+            _, ref = oracle.conv2d_nhwc_f16(np.ascontiguousarray(a[:1].cpu().numpy()), b.cpu().numpy(), s[7], s[8])
+        err = float(np.linalg.norm(got.astype(np.float64) - ref) / max(np.linalg.norm(ref.astype(np.float64)), 1e-30))
+        if not np.isfinite(err) or err > 2e-3:
+            raise SystemExit("bench self-check failed: %s relative Frobenius error %.3e" % (u["name"], err))
+        worst = max(worst, err)
+        checked += 1
+    return checked, worst
+
+
 def bench_helix(args, rank, world, local_rank):
     import torch
     if not torch.cuda.is_available():
@@ -305,13 +405,15 @@ def bench_helix(args, rank, world, local_rank):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     from helix_b200 import dist_util, ops, sweep, workloads
     peaks = read_peaks()
-    # one rank per GPU: keep this rank's pinned host buffers on its GPU's NUMA node (matters for e2e at N > 1)
     numa_cpus = dist_util.bind_to_gpu_numa_node(local_rank) if world > 1 else None
 
-    units = workloads.model_level_sweep()
-    sw = sweep.Sweep(units, seed=4 * 1000 + rank, lanes=args.lanes)
-    # warm-up outside any capture: sets function attributes, fills the tensor-map cache
-    launches_per_step = sw.step()
+    # this rank's share of the fixed work list
+    units = work_list()
+    total_flops = sum(workloads.unit_flops(u) for u in units)
+    parts = workloads.lpt_partition([unit_estimate(u) for u in units], world)
+    mine = [units[i] for i in parts[rank]]
+    sw = sweep.Sweep(mine, seed=4000, lanes=args.lanes, seeds=[u["index"] for u in mine])
+    launches_per_pass = sw.step()          # outside any capture: sets function attributes, fills the tensor-map cache
     torch.cuda.synchronize()
     ops.check_status()
 
@@ -326,10 +428,11 @@ def bench_helix(args, rank, world, local_rank):
         torch.cuda.synchronize()
 
     def one_step():
-        if graph is not None:
-            graph.replay()
-        else:
-            sw.step()
+        for _ in range(args.passes):
+            if graph is not None:
+                graph.replay()
+            else:
+                sw.step()
 
     for _ in range(args.warmup):
         one_step()
@@ -338,8 +441,7 @@ def bench_helix(args, rank, world, local_rank):
     if rank == 0:
         sampler.start()
         time.sleep(0.25)
-    if dist is not None:
-        dist.barrier()
+    dist_util.barrier(dist)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -347,85 +449,144 @@ def bench_helix(args, rank, world, local_rank):
         one_step()
     e1.record()
     torch.cuda.synchronize()
-    if dist is not None:
-        dist.barrier()
-    ms = e0.elapsed_time(e1)
+    dist_util.barrier(dist)
+    own_ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
     ops.check_status()
-    ms = dist_util.max_over_ranks(ms, dist, "cuda")
+    ms = dist_util.max_over_ranks(own_ms, dist, "cuda")
+    rank_ms = dist_util.gather_floats(own_ms, dist, "cuda")
     ms_per_step = ms / args.steps
-    value = sw.flops * world / (ms_per_step * 1e-3) / 1e12
+    value = total_flops * args.passes / (ms_per_step * 1e-3) / 1e12
 
-    # end to end: pinned host operands in, results out, every step
+    # end to end: this rank's units with pinned host operands in and results out, every pass
     hs = sweep.HostSweep(sw)
-    e2e_steps = max(1, min(args.steps, 3))
+    e2e_passes = max(1, min(args.steps, 3))
     hs.step()
     hs.finish()
-    if dist is not None:
-        dist.barrier()
+    dist_util.barrier(dist)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    for _ in range(e2e_steps):
+    for _ in range(e2e_passes):
         hs.step()
     hs.finish()
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
-    e2e_s = dist_util.max_over_ranks(e2e_s, dist, "cuda")
-    e2e_value = sw.flops * world / e2e_s / 1e12
+    e2e_own = (time.perf_counter() - t0) / e2e_passes
+    e2e_s = dist_util.max_over_ranks(e2e_own, dist, "cuda")
+    e2e_value = total_flops / e2e_s / 1e12
+    h2d_total = dist_util.sum_over_ranks(hs.h2d_bytes, dist, "cuda")
+    d2h_total = dist_util.sum_over_ranks(hs.d2h_bytes, dist, "cuda")
     ops.check_status()
+    del hs
+
+    # secondary figure: every rank runs one whole copy of the sweep (independent replicas)
+    replica = None
+    if world > 1:
+        one_copy = sweep.Sweep(workloads.model_level_sweep(), seed=4000 + rank, lanes=args.lanes)
+        one_copy.step()
+        torch.cuda.synchronize()
+        dist_util.barrier(dist)
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record()
+        for _ in range(10):
+            one_copy.step()
+        r1.record()
+        torch.cuda.synchronize()
+        rep_ms = dist_util.max_over_ranks(r0.elapsed_time(r1) / 10, dist, "cuda")
+        replica = {"value": one_copy.flops * world / (rep_ms * 1e-3) / 1e12, "ms_per_pass": rep_ms,
+                   "what": "every rank one whole copy of the sweep on its own data (weak scaling, eager launches)"}
+        del one_copy
+        ops.check_status()
+
+    # one oversized GEMM split along N (no collective in the timed region), N > 1 only
+    nsplit_row = None
+    if world > 1:
+        from helix_b200 import nsplit
+        import numpy as np
+        M, K = 8192, 8192
+        N = 16384 * world
+        gsp = nsplit.NSplitGemm(M, N, K, 2, world, rank)
+        for _ in range(3):
+            gsp.step()
+        torch.cuda.synchronize()
+        dist_util.barrier(dist)
+        n0e, n1e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n0e.record()
+        for _ in range(10):
+            gsp.step()
+        n1e.record()
+        torch.cuda.synchronize()
+        ns_ms = dist_util.max_over_ranks(n0e.elapsed_time(n1e) / 10, dist, "cuda")
+        digest = float(gsp.c.float().abs().sum().item())
+        nsplit_row = {"M": M, "N": N, "K": K, "ms": ns_ms, "TFLOP/s": 2.0 * M * N * K / (ns_ms * 1e-3) / 1e12,
+                      "checksum_abs_sum_all_slabs": dist_util.sum_over_ranks(digest, dist, "cuda"),
+                      "collectives_in_timed_region": 0}
+        del gsp
+        ops.check_status()
 
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
-    peak = peaks["tflops_sustained"]
     per_gpu = value / world
-    # dominant kernel: the group with the largest share of the step's device time
     groups = kernel_breakdown(sw, ops)
     ops.check_status()
     top = max(groups, key=lambda k: groups[k]["share"])
     tg = groups[top]
-    traffic = SWEEP_DRAM_BYTES_PER_LAUNCH.get(top)
+    checked, worst_err = self_check(sw)
+    pass_ms = ms_per_step / args.passes
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16 in / f32 accumulate", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "units_per_step_per_gpu": len(units), "flop_per_step_per_gpu": sw.flops,
-                   "cache": "operands of one step total %.1f GB per GPU (> L2), one buffer set per unit" % (sw.bytes / 1e9),
-                   "cuda_graph": graph is not None, "parallelism": f"independent replicas of the sweep x{world}",
+        "config": {"workload": WORKLOAD, "step": "%d passes over the work list (%.2f TFLOP per pass)" % (args.passes, total_flops / 1e12),
+                   "units_this_rank": len(mine), "cache": "operands of one pass on rank 0 total %.1f GB (> L2), one buffer set per unit" % (sw.bytes / 1e9),
+                   "cuda_graph": graph is not None,
+                   "parallelism": "fixed work list partitioned over %d GPU(s) by LPT on a roofline estimate; no collective" % world,
                    "lanes": "%d concurrent launch chains per GPU, each launch limited to 1/%d of the SMs" % (args.lanes, args.lanes),
                    "host_numa_binding": ("rank 0 bound to %d CPUs next to its GPU" % len(numa_cpus)) if numa_cpus else "none"},
-        "roofline": {"bound": "tensor", "achieved": tg["TFLOP/s"], "peak": peak, "unit": "TFLOP/s",
-                     "frac": tg["TFLOP/s"] / peak, "traffic": traffic,
-                     "kernel": top, "launches_per_step": tg["launches"], "share_of_step": tg["share"],
+        "ms_per_pass": pass_ms,
+        "rank_idle_frac": [round(1.0 - t / ms, 4) for t in rank_ms],
+        "checked_units": checked, "check_worst_rel_fro": worst_err,
+        "roofline": {"bound": "tensor", "achieved": tg["TFLOP/s"], "peak": peaks["tflops"], "unit": "TFLOP/s",
+                     "frac": tg["TFLOP/s"] / peaks["tflops"],
+                     "traffic": SWEEP_DRAM_BYTES_PER_LAUNCH.get(top),
+                     "traffic_source": "constant from a single-pass ncu capture of one sweep pass (profiles/bench_sweep_launch_list.md), not measured by this run",
+                     "kernel": top, "launches_per_copy": tg["launches"], "share_of_copy": tg["share"],
                      "us_per_launch": tg["us"] / tg["launches"],
                      "algorithmic_flop_per_launch": tg["flop"] / tg["launches"],
                      "algorithmic_bytes_per_launch": tg["bytes"] / tg["launches"],
-                     "peak_source": peaks["source"] + " (sustained bf16 cuBLAS; burst %.0f)" % peaks["tflops"],
-                     "whole_sweep": {"achieved": per_gpu, "frac": per_gpu / peak,
-                                     "hbm_floor_frac": (sw.bytes / (ms_per_step * 1e-3) / 1e9) / peaks["hbm_gbs"]},
+                     "peak_source": peaks["source"] + " burst bf16 cuBLAS (the group is timed alone for ~10 ms); sustained %.0f" % peaks["tflops_sustained"],
+                     "whole_sweep": {"achieved_per_gpu": per_gpu, "frac_of_sustained": per_gpu / peaks["tflops_sustained"],
+                                     "frac_of_burst": per_gpu / peaks["tflops"], "timed_region_s": ms * 1e-3,
+                                     "sm_mhz_median": clocks["sm_mhz"] if clocks else None,
+                                     "hbm_floor_frac": (sw.bytes / (pass_ms * 1e-3) / 1e9) / peaks["hbm_gbs"]},
                      "kernels": {k: {"launches": v["launches"], "us": round(v["us"], 2), "share": round(v["share"], 4),
                                      "TFLOP/s": round(v["TFLOP/s"], 1),
                                      "dram_bytes_per_launch": SWEEP_DRAM_BYTES_PER_LAUNCH.get(k)}
                                  for k, v in sorted(groups.items(), key=lambda kv: -kv[1]["share"])}},
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": hs.h2d_bytes * world,
-                "d2h_bytes_per_step": hs.d2h_bytes * world, "ms_per_step": e2e_s * 1e3},
-        "gpu_launches": launches_per_step * args.steps,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_total, "d2h_bytes_per_step": d2h_total,
+                "ms_per_step": e2e_s * 1e3, "step": "one pass over the work list",
+                "host_gbs_per_gpu": (h2d_total + d2h_total) / world / e2e_s / 1e9},
+        "gpu_launches": launches_per_pass * args.passes * args.steps,
         "clocks": clocks,
     }
+    if replica is not None:
+        line["replicas"] = replica
+    if nsplit_row is not None:
+        line["nsplit_gemm"] = nsplit_row
     if world == 1 and not args.no_extras:
-        del hs
+        del sw
         torch.cuda.empty_cache()
-        # the per-shape table runs on a GPU the sweep has already heated: record the clocks it saw
         xs = ClockSampler(local_rank)
         xs.start()
+        line["roofline"]["configs"] = per_config_table(peaks)
         line["extras"] = extras(peaks)
         line["extras"]["clocks"] = xs.stop()
-        dt, flops, cores, passes = run_cpu_sample()
-        line["cpu_baseline"] = {
-            "value": flops / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": "one BERT-base layer (4 linear GEMMs + 8 of 192 QK^T and PV GEMMs) and 3 ResNet-50 convs as GEMMs "
-                      "at batch 4, fp32 x86-template restatement, %d passes of %.1f GFLOP in %.1f s"
-                      % (passes, flops / 1e9, dt * passes)}
+        cores = host_threads()
+        cpu = CpuSweep(cores)
+        cpu.one_pass()
+        dt = cpu.one_pass()
+        line["cpu_baseline"] = {"value": cpu.flops / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
+                                "gflops_per_core": cpu.flops / dt / 1e9 / cores, "sample": cpu.sample_text(dt)}
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -437,8 +598,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["helix", "reference"], default="helix")
-    ap.add_argument("--no-extras", action="store_true", help="skip the per-configuration table and CPU sample")
-    ap.add_argument("--lanes", type=int, default=2, help="independent shapes of the sweep run in this many concurrent chains")
+    ap.add_argument("--no-extras", action="store_true", help="skip the per-configuration table and the CPU pass")
+    ap.add_argument("--lanes", type=int, default=2, help="independent units run in this many concurrent chains per GPU")
+    ap.add_argument("--passes", type=int, default=PASSES, help="passes over the work list per step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
     rank = int(os.environ.get("RANK", "0"))

@@ -15,6 +15,26 @@ def max_over_ranks(value, dist=None, device="cpu"):
     return float(t.item())
 
 
+def sum_over_ranks(value, dist=None, device="cpu"):
+    """Sum of `value` (a float) over all ranks; identity without a process group."""
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        return float(value)
+    t = torch.tensor([float(value)], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def gather_floats(value, dist=None, device="cpu"):
+    """`value` of every rank, in rank order, on every rank."""
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        return [float(value)]
+    world = dist.get_world_size()
+    t = torch.zeros(world, dtype=torch.float64, device=device)
+    t[dist.get_rank()] = float(value)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return [float(v) for v in t.tolist()]
+
+
 def aggregate_throughput(units_per_rank, seconds, dist=None, device="cpu"):
     """Whole-job units per second: every rank's units over the slowest rank's time."""
     world = dist.get_world_size() if (dist is not None and dist.is_initialized()) else 1

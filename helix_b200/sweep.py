@@ -47,10 +47,12 @@ def _fill(shape, scale, gen, device, valid_channels=None):
 class Sweep:
     """Device-resident sweep: distinct operand buffers per unit, one prepared launch each."""
 
-    def __init__(self, units, seed=4, device=None, cfg_for=None, lanes=1):
+    def __init__(self, units, seed=4, device=None, cfg_for=None, lanes=1, seeds=None):
         """lanes > 1: the units are dealt to that many streams (balanced by estimated time) and every launch is limited to
         1/lanes of the SMs, so independent shapes run side by side with longer-lived CTAs (the set-up and
-        drain of one launch hide behind the steady state of its neighbour)."""
+        drain of one launch hide behind the steady state of its neighbour).
+        seeds: one integer per unit that replaces its position in the data seed, so that a unit of a
+        partitioned list gets the same bytes whichever GPU it lands on."""
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.lanes = max(1, int(lanes))
         self.units = list(units)
@@ -72,7 +74,7 @@ class Sweep:
         self.issue_order = [lst[j] for j in range(max(map(len, per_lane))) for lst in per_lane if j < len(lst)]
         gen = torch.Generator(device=self.device)
         for i, u in enumerate(self.units):
-            gen.manual_seed(int(seed) * 1000003 + i)
+            gen.manual_seed(int(seed) * 1000003 + (int(seeds[i]) if seeds is not None else i))
             sa, sb, so = unit_operand_shapes(u)
             if u["kind"] == "gemm":
                 K = u["shape"][2]

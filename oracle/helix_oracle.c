@@ -130,6 +130,65 @@ static void micro_kernel(const float* restrict a, size_t lda, int mrows, int kc_
   }
 }
 
+/* Register-resident form of the same cell for a whole K range: the m1 x n1 tile of C stays in vector
+ * registers while k runs over every vk2 block of the packed panel (what unrolling vk1 and vm1 and
+ * vectorising vn1 lets the reference's compiler do with the accumulators).  Each output is still one
+ * sum over k ascending, so the result equals the cell-by-cell path bit for bit. */
+typedef float v16f __attribute__((vector_size(64), aligned(4)));
+#define FULLK_BODY(M1, NV)                                                                            \
+  {                                                                                                   \
+    v16f acc[M1][NV];                                                                                 \
+    _Pragma("GCC unroll 9") for (int i = 0; i < M1; ++i)                                              \
+        _Pragma("GCC unroll 4") for (int j = 0; j < NV; ++j) acc[i][j] = (v16f){0};                   \
+    int k = 0;                                                                                        \
+    for (int vk2 = 0; k < K; ++vk2) {                                                                 \
+      const float* bb = bp + (size_t)vk2 * vk2_stride;                                                \
+      for (int vk1 = 0; vk1 < k1 && k < K; ++vk1, ++k) {                                              \
+        v16f bv[NV];                                                                                  \
+        _Pragma("GCC unroll 4") for (int j = 0; j < NV; ++j)                                          \
+            bv[j] = *(const v16f*)(bb + (size_t)vk1 * ldb + 16 * j);                                  \
+        _Pragma("GCC unroll 9") for (int i = 0; i < M1; ++i) {                                        \
+          const float s = a[(size_t)i * lda + k];                                                     \
+          _Pragma("GCC unroll 4") for (int j = 0; j < NV; ++j) acc[i][j] += s * bv[j];                \
+        }                                                                                             \
+      }                                                                                               \
+    }                                                                                                 \
+    _Pragma("GCC unroll 9") for (int i = 0; i < M1; ++i)                                              \
+        _Pragma("GCC unroll 4") for (int j = 0; j < NV; ++j)                                          \
+            *(v16f*)(cl + (size_t)i * ldcl + 16 * j) = acc[i][j];                                     \
+    return 1;                                                                                         \
+  }
+#define FULLK_ROW(M1) case (M1) * 8 + 1: FULLK_BODY(M1, 1) case (M1) * 8 + 2: FULLK_BODY(M1, 2) \
+                      case (M1) * 8 + 3: FULLK_BODY(M1, 3) case (M1) * 8 + 4: FULLK_BODY(M1, 4)
+#define FULLK_SWITCH                                                                                      \
+  if ((n1 & 15) || n1 > 64 || m1 < 1 || m1 > 9) return 0;                                                 \
+  switch (m1 * 8 + (n1 >> 4)) {                                                                           \
+    FULLK_ROW(1) FULLK_ROW(2) FULLK_ROW(3) FULLK_ROW(4) FULLK_ROW(5) FULLK_ROW(6) FULLK_ROW(7) FULLK_ROW(8) \
+    FULLK_ROW(9)                                                                                          \
+  }                                                                                                       \
+  return 0;
+/* s * b + acc as a rounded product and a rounded sum (the file is built with -ffp-contract=off).  Returns 0
+ * when the tile shape has no register-resident kernel (the caller then walks the cells). */
+__attribute__((target_clones("arch=x86-64-v4", "default")))
+static int fullk_kernel_mul(int m1, int n1, const float* restrict a, size_t lda, int K, const float* restrict bp,
+                            size_t ldb, size_t vk2_stride, int k1, float* restrict cl, size_t ldcl) {
+  FULLK_SWITCH
+}
+/* The same text compiled with contraction on: every s * b + acc becomes one fused multiply-add, i.e. what
+ * fmaf() computes (checked bit for bit against the fmaf loop of oracle_sgemm_naive by the tests). */
+__attribute__((target_clones("arch=x86-64-v4", "default"), optimize("fp-contract=fast")))
+static int fullk_kernel_fma(int m1, int n1, const float* restrict a, size_t lda, int K, const float* restrict bp,
+                            size_t ldb, size_t vk2_stride, int k1, float* restrict cl, size_t ldcl) {
+  FULLK_SWITCH
+}
+/* B rows are `ldb` floats apart and consecutive vk2 blocks `vk2_stride` floats (packed panel: n1 and
+ * n2 * k1 * n1; plain matrix: N and k1 * N). */
+static int fullk_kernel(int m1, int n1, const float* a, size_t lda, int K, const float* bp, size_t ldb,
+                        size_t vk2_stride, int k1, float* cl, size_t ldcl, int fma) {
+  return fma ? fullk_kernel_fma(m1, n1, a, lda, K, bp, ldb, vk2_stride, k1, cl, ldcl)
+             : fullk_kernel_mul(m1, n1, a, lda, K, bp, ldb, vk2_stride, k1, cl, ldcl);
+}
+
 /* ------------------------------------------------------------------------- */
 /* Single-thread register-blocked template, scripts/x86_CPU/profile_x86_CPU.py */
 /* :40-60.  split vm -> (vm3, m2, m1), vn -> (vn3, n2, n1), vk -> (vk2, k1);   */
@@ -145,6 +204,15 @@ int oracle_sgemm_template(const float* a, const float* b, float* c, int M, int N
   if (M % mt || N % nt || K % k1) return ORACLE_EINVAL;
   for (int vm3 = 0; vm3 < M / mt; ++vm3) {
     for (int vn3 = 0; vn3 < N / nt; ++vn3) {
+      /* register-resident cells over the whole K range where the tile shape has a kernel */
+      int done = 1;
+      for (int vm2 = 0; vm2 < m2 && done; ++vm2)
+        for (int vn2 = 0; vn2 < n2 && done; ++vn2) {
+          const int m0 = (vm3 * m2 + vm2) * m1, n0 = (vn3 * n2 + vn2) * n1;
+          done = fullk_kernel(m1, n1, a + (size_t)m0 * K, (size_t)K, K, b + n0, (size_t)N, (size_t)k1 * N, k1,
+                              c + (size_t)m0 * N + n0, (size_t)N, fma);
+        }
+      if (done) continue;
       for (int i = 0; i < mt; ++i)
         for (int j = 0; j < nt; ++j) c[(size_t)(vm3 * mt + i) * N + vn3 * nt + j] = 0.0f;
       for (int vk2 = 0; vk2 < K / k1; ++vk2)
@@ -248,7 +316,22 @@ int oracle_sgemm_parallel(const float* a, const float* b, float* c, int M, int N
           for (int vm3 = 0; vm3 < m3; ++vm3) {
             const int mrow0 = (vm4 * m3 + vm3) * m2 * m1;
             memset(cl + (size_t)mrow0 * nc, 0, (size_t)m2 * m1 * nc * sizeof(float));
-            for (int vn3 = 0; vn3 < n3; ++vn3)
+            for (int vn3 = 0; vn3 < n3; ++vn3) {
+              /* whole-K register-resident cells where the tile shape has a kernel and the rows are all valid */
+              int done = 1;
+              for (int vm2 = 0; vm2 < m2 && done; ++vm2)
+                for (int vn2 = 0; vn2 < n2 && done; ++vn2) {
+                  const int m0 = mrow0 + vm2 * m1;
+                  if (m0 + m1 > M) { done = 0; break; }
+                  done = fullk_kernel(m1, n1, a + (size_t)m0 * K, (size_t)K, K,
+                                      bp + (((size_t)vn3 * kb) * n2 + vn2) * k1 * n1, (size_t)n1, (size_t)n2 * k1 * n1, k1,
+                                      cl + (size_t)m0 * nc + (vn3 * n2 + vn2) * n1, (size_t)nc, fma);
+                }
+              if (done) continue;
+              /* the cell-by-cell path accumulates into a zeroed tile (a partly written one is reset) */
+              for (int vm2 = 0; vm2 < m2; ++vm2)
+                for (int r = 0; r < m1; ++r)
+                  memset(cl + (size_t)(mrow0 + vm2 * m1 + r) * nc + (size_t)vn3 * n2 * n1, 0, (size_t)n2 * n1 * sizeof(float));
               for (int vk2 = 0; vk2 < kb; ++vk2)
                 for (int vm2 = 0; vm2 < m2; ++vm2)
                   for (int vn2 = 0; vn2 < n2; ++vn2) {
@@ -260,6 +343,7 @@ int oracle_sgemm_parallel(const float* a, const float* b, float* c, int M, int N
                                  bp + ((((size_t)vn3 * kb + vk2) * n2 + vn2) * k1) * n1, (size_t)n1,
                                  cl + (size_t)m0 * nc + (vn3 * n2 + vn2) * n1, (size_t)nc, m1, k1, n1, fma);
                   }
+            }
           }
         }
         /* write the panel back */

@@ -201,7 +201,19 @@ rank = dist.get_rank()
 dist_util.barrier(dist)
 slowest = dist_util.max_over_ranks(1.0 + rank, dist)
 tput = dist_util.aggregate_throughput(10.0, 1.0 + rank, dist)
-print(f"{{rank}} {{slowest}} {{tput}}")
+total = dist_util.sum_over_ranks(3.0 + rank, dist)
+each = dist_util.gather_floats(5.0 * (rank + 1), dist)
+# the benchmark's partition of a fixed work list: every unit lands on exactly one rank
+import importlib.util
+spec = importlib.util.spec_from_file_location("bench", os.path.join({root!r}, "bench.py"))
+bench = importlib.util.module_from_spec(spec); spec.loader.exec_module(bench)
+from helix_b200 import workloads
+units = bench.work_list()
+parts = workloads.lpt_partition([bench.unit_estimate(u) for u in units], 2)
+mine = sum(bench.unit_estimate(units[i]) for i in parts[rank])
+loads = dist_util.gather_floats(mine, dist)
+covered = dist_util.sum_over_ranks(len(parts[rank]), dist)
+print(f"{{rank}} {{slowest}} {{tput}} {{total}} {{each[0]}} {{each[1]}} {{covered}} {{len(units)}} {{loads[0]}} {{loads[1]}}")
 dist.destroy_process_group()
 """
 
@@ -217,8 +229,11 @@ def test_max_over_ranks_and_aggregate_throughput_world_size_2(tmp_path):
     procs = [subprocess.Popen([sys.executable, str(script), str(r)], stdout=subprocess.PIPE, text=True) for r in (0, 1)]
     outs = [p.communicate(timeout=120)[0].split() for p in procs]
     assert all(p.returncode == 0 for p in procs)
-    for rank, (r, slowest, tput) in enumerate(outs):
+    for rank, (r, slowest, tput, total, e0, e1, covered, n_units, l0, l1) in enumerate(outs):
         assert int(r) == rank and float(slowest) == 2.0 and float(tput) == pytest.approx(10.0)   # 2 x 10 units / 2 s
+        assert float(total) == 7.0 and (float(e0), float(e1)) == (5.0, 10.0)
+        assert float(covered) == float(n_units) == 1000.0
+        assert abs(float(l0) - float(l1)) <= 0.01 * float(l0)        # LPT leaves the two ranks within 1 %
 
 
 # ----------------------------------------------------------------------------- one GEMM split along N
