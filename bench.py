@@ -297,6 +297,14 @@ def per_config_table(peaks):
         c1[str(n)] = r3(avg * 1e6, tf, tf / 74.4)
         del a, b, c
     out["gemm_f32 [us, TFLOP/s, of_ffma_nominal_74.4]"] = c1
+    # fp32 GEMV 8192 x 8192 (268 MB of weights per launch, two buffers)
+    wf = [torch.rand(8192, 8192, device=dev) * 2 - 1 for _ in range(2)]
+    xf = torch.rand(1, 8192, device=dev) * 2 - 1
+    yf = [torch.empty(1, 8192, device=dev) for _ in wf]
+    avg, _, _ = ops.time_launches([ops.launch_gemv_f32(w, xf, y) for w, y in zip(wf, yf)], warmup=3, iters=20, use_graph=True)
+    gb = (8192 * 8192 * 4 + 2 * 8192 * 4) / avg / 1e9
+    out["gemv_f32_8192x8192_m1 [us, GB/s, of_hbm]"] = r3(avg * 1e6, gb, gb / peaks["hbm_gbs"])
+    del wf, yf
     return out
 
 

@@ -9,7 +9,7 @@ import os
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libhelix_b200.so")
 
-OP_GEMM_F16, OP_GEMV_F16, OP_CONV_F16, OP_GEMM_F32, OP_CONV_F32 = 0, 1, 2, 3, 4
+OP_GEMM_F16, OP_GEMV_F16, OP_CONV_F16, OP_GEMM_F32, OP_CONV_F32, OP_GEMV_F32 = 0, 1, 2, 3, 4, 5
 
 STATUS_TEXT = {
     0: "ok", -1: "invalid argument", -2: "pointer or leading dimension not 16-byte aligned",
@@ -79,6 +79,7 @@ SIGNATURES = {
     "helix_launch": (_I, [ctypes.POINTER(Launch), _P, _P]),
     "helix_gemm_f16": (_I, [ctypes.POINTER(Cfg), _P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _L, _L, _L, _P, _Z, _P, _P]),
     "helix_gemv_f16": (_I, [ctypes.POINTER(Cfg), _P, _L, _P, _L, _P, _L, _L, _I, _I, _I, _P, _Z, _P, _P]),
+    "helix_gemv_f32": (_I, [ctypes.POINTER(Cfg), _P, _L, _P, _L, _P, _L, _L, _I, _I, _I, _P, _Z, _P, _P]),
     "helix_conv2d_f16_nhwc": (_I, [ctypes.POINTER(Cfg), _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _Z, _P, _P]),
     "helix_gemm_f32": (_I, [ctypes.POINTER(Cfg), _P, _L, _I, _P, _L, _P, _L, _I, _I, _I, _P, _P]),
     "helix_conv2d_f32_nhwc": (_I, [ctypes.POINTER(Cfg), _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _Z, _P, _P]),
@@ -88,7 +89,7 @@ SIGNATURES = {
     "helix_gemm_f32_host": (_I, [_P, _P, _P, _I, _I, _I]),
     "helix_conv2d_f16_nhwc_host": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I]),
     "helix_gemv_f16_static": (_I, [_P, _L, _P, _L, _P, _L, _L, _I, _I, _I, _I, _P]),
-    "helix_probe_ffma_f32": (_I, [_I, _PD, _P]),
+    "helix_selftest_bounded_wait": (_I, [ctypes.c_uint64, _P, _P]),
     "helix_launch_count": (_L, []),
     "helix_trace_buffer": (_I, [_P, _Z]),
     "helix_trace_words_per_cta": (_I, []),

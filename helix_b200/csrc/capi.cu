@@ -5,9 +5,24 @@
 #include <mutex>
 #include <vector>
 
+#include "common.cuh"
 #include "kernels.h"
 
 namespace {
+
+// One thread waits, with the bounded wait every kernel of the library uses, on a barrier that nothing will
+// ever arrive at.  The wait gives up after `limit_ns`, records HELIX_ERR_TIMEOUT in the status word and the
+// kernel returns normally: the path a stalled pipeline takes, exercised without stalling one.
+__global__ void selftest_wait_kernel(unsigned long long limit_ns, int* status_dev) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    helix::mbar_init(&bar, 1);
+    abort_flag = 0;
+    helix::mbar_fence_init();
+    (void)helix::mbar_wait_limit(&bar, 0, &abort_flag, status_dev, limit_ns);
+  }
+}
 
 std::atomic<int64_t> g_launches{0};
 
@@ -128,6 +143,12 @@ int dispatch(const helix_launch_t* l, void* status_dev, cudaStream_t stream) {
                                    static_cast<const float*>(l->b), l->ldb, static_cast<float*>(l->c), l->ldc, l->M,
                                    l->N, l->K, sms_of(info), stream, &n);
       break;
+    case HELIX_OP_GEMV_F32:
+      if ((rc = current_device(&info, false)) != HELIX_OK) return rc;
+      rc = helix::gemv_f32_launch(cfg, static_cast<const float*>(l->a), l->lda, static_cast<const float*>(l->b), l->ldb,
+                                  static_cast<float*>(l->c), l->ldc, l->ldc_inner, l->N, l->K, l->M, l->ws,
+                                  l->ws_bytes, sms_of(info), stream, &n);
+      break;
     case HELIX_OP_CONV_F32: {
       if ((rc = current_device(&info, false)) != HELIX_OK) return rc;
       const helix::ConvGeom g = conv_geom(l->conv);
@@ -180,7 +201,8 @@ int helix_num_configs(int op) {
   switch (op) {
     case HELIX_OP_GEMM_F16:
     case HELIX_OP_CONV_F16: return helix::gemm_f16_num_configs();
-    case HELIX_OP_GEMV_F16: return 5;  // split-K 1, 2, 4, 8, 16
+    case HELIX_OP_GEMV_F16:
+    case HELIX_OP_GEMV_F32: return 5;  // split-K 1, 2, 4, 8, 16
     case HELIX_OP_GEMM_F32:
     case HELIX_OP_CONV_F32: return helix::sgemm_f32_num_configs();
     default: return HELIX_ERR_INVALID;
@@ -203,10 +225,11 @@ int helix_get_config(int op, int idx, helix_cfg_t* out) {
       if (out->swap_ab || out->cta_group != 1) return HELIX_ERR_UNSUPPORTED;
       break;
     case HELIX_OP_GEMV_F16:
-      out->op = HELIX_OP_GEMV_F16;
+    case HELIX_OP_GEMV_F32:
+      out->op = op;
       out->tile_m = 1;
       out->tile_n = 2;
-      out->tile_k = 256;
+      out->tile_k = op == HELIX_OP_GEMV_F16 ? 256 : 128;
       out->split_k = 1 << idx;
       out->cta_group = 1;
       break;
@@ -240,6 +263,12 @@ int helix_default_config(const helix_launch_t* l, helix_cfg_t* out) {
       out->op = HELIX_OP_GEMV_F16;
       out->tile_m = 1; out->tile_n = 2; out->tile_k = 256; out->cta_group = 1;
       out->split_k = helix::gemv_f16_default_split(l->N, l->K, sms);
+      return HELIX_OK;
+    case HELIX_OP_GEMV_F32:
+      out->op = HELIX_OP_GEMV_F32;
+      out->tile_m = 1; out->tile_n = l->M <= 2 ? 2 : 1; out->tile_k = 128; out->cta_group = 1;
+      out->load_group = l->M <= 4 ? 4 : 2;
+      out->split_k = helix::gemv_f32_default_split(l->N, l->K, sms);
       return HELIX_OK;
     case HELIX_OP_GEMM_F32:
       helix::sgemm_f32_default_config(l->M, l->N, sms, out);
@@ -281,6 +310,10 @@ size_t helix_workspace_bytes(const helix_launch_t* l) {
       const int split = have_cfg && l->cfg.split_k > 0 ? l->cfg.split_k : helix::gemv_f16_default_split(l->N, l->K, sms);
       return helix::gemv_f16_workspace_bytes(l->N, l->M, split);
     }
+    case HELIX_OP_GEMV_F32: {
+      const int split = have_cfg && l->cfg.split_k > 0 ? l->cfg.split_k : helix::gemv_f32_default_split(l->N, l->K, sms);
+      return helix::gemv_f32_workspace_bytes(l->N, l->M, split);
+    }
     case HELIX_OP_CONV_F32:
       return helix::conv_f32_workspace_bytes(conv_geom(l->conv));
     default:
@@ -314,6 +347,20 @@ int helix_gemv_f16(const helix_cfg_t* cfg, const void* W, int64_t ldw, const voi
   helix_launch_t l;
   std::memset(&l, 0, sizeof(l));
   l.op = HELIX_OP_GEMV_F16;
+  if (cfg) l.cfg = *cfg;
+  l.a = W; l.b = X; l.c = Y;
+  l.lda = ldw; l.ldb = ldx; l.ldc = ldy; l.ldc_inner = ldy_inner;
+  l.M = m; l.N = rows; l.K = K;
+  l.ws = ws; l.ws_bytes = ws_bytes;
+  return dispatch(&l, status_dev, static_cast<cudaStream_t>(stream));
+}
+
+int helix_gemv_f32(const helix_cfg_t* cfg, const float* W, int64_t ldw, const float* X, int64_t ldx, float* Y,
+                   int64_t ldy, int64_t ldy_inner, int rows, int K, int m, void* ws, size_t ws_bytes,
+                   void* status_dev, void* stream) {
+  helix_launch_t l;
+  std::memset(&l, 0, sizeof(l));
+  l.op = HELIX_OP_GEMV_F32;
   if (cfg) l.cfg = *cfg;
   l.a = W; l.b = X; l.c = Y;
   l.lda = ldw; l.ldb = ldx; l.ldc = ldy; l.ldc_inner = ldy_inner;
@@ -551,14 +598,14 @@ int helix_gemv_f16_static(const void* W, int64_t ldw, const void* X, int64_t ldx
   return st;
 }
 
-int helix_probe_ffma_f32(int rounds, double* tflops, void* stream) {
+int helix_selftest_bounded_wait(uint64_t limit_ns, void* status_dev, void* stream) {
+  if (!status_dev || limit_ns == 0 || limit_ns > 1000000000ull) return HELIX_ERR_INVALID;
   helix_devinfo_t info;
   const int rc = current_device(&info, false);
   if (rc != HELIX_OK) return rc;
-  int64_t n = 0;
-  const int st = helix::ffma_probe(rounds, info.sm_count, tflops, static_cast<cudaStream_t>(stream), &n);
-  g_launches += n;
-  return st;
+  selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(limit_ns, static_cast<int*>(status_dev));
+  g_launches += 1;
+  return cudaGetLastError() == cudaSuccess ? HELIX_OK : HELIX_ERR_CUDA;
 }
 
 int64_t helix_launch_count(void) { return g_launches.load(); }

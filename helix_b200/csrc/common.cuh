@@ -84,8 +84,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (after recording the failure) when the limit ran out
 // or another role of this CTA already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status_dev) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                int* status_dev, unsigned long long limit_ns) {
   for (int i = 0; i < 2048; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
@@ -93,12 +93,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (global_timer_ns() - t0 > kWaitLimitNs) {
+    if (global_timer_ns() - t0 > limit_ns) {
       *abort_flag = 1;
       if (status_dev) atomicExch(status_dev, (int)HELIX_ERR_TIMEOUT);
       return false;
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status_dev) {
+  return mbar_wait_limit(bar, parity, abort_flag, status_dev, kWaitLimitNs);
 }
 
 // ---------------------------------------------------------------- proxies / fences

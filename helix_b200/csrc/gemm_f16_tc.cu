@@ -385,12 +385,13 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       WorkItem w;
       for (int idx = 0; ok && get_item(p, cta, grid, idx, w); ++idx) {
         int64_t base_off[kConvRowsPerThread];  // element offset of the (possibly padded) window origin
-        uint32_t inside[kConvRowsPerThread];   // bit r: row r of the window is inside; bit 16+s: column s
+        uint32_t in_r[kConvRowsPerThread];     // bit r: filter row r of the window falls inside the image
+        uint32_t in_s[kConvRowsPerThread];     // bit s: filter column s does
 #pragma unroll
         for (int it = 0; it < kConvRowsPerThread; ++it) {
           const int m = w.m_blk * kBM + pw * 16 + it * 4 + sub;
           base_off[it] = 0;
-          inside[it] = 0;
+          in_r[it] = in_s[it] = 0;
           if (m < p.PM) {
             int n_img, rem, ho, wo;
             fast_divmod(m, p.fd_howo, n_img, rem);
@@ -398,12 +399,11 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             const int hi0 = ho * p.g.stride - p.g.pad;
             const int wi0 = wo * p.g.stride - p.g.pad;
             base_off[it] = ((int64_t)n_img * p.g.H + hi0) * p.g.W * p.g.C + (int64_t)wi0 * p.g.C;
-            // filter rows [r_lo, r_hi) and columns [s_lo, s_hi) fall inside the image (R, S <= 15)
+            // filter rows [r_lo, r_hi) and columns [s_lo, s_hi) fall inside the image (R, S <= 32)
             const int r_lo = max(0, -hi0), r_hi = min(p.g.R, p.g.H - hi0);
             const int s_lo = max(0, -wi0), s_hi = min(p.g.S, p.g.W - wi0);
-            const uint32_t rbits = r_hi > r_lo ? ((1u << r_hi) - 1u) & ~((1u << r_lo) - 1u) : 0u;
-            const uint32_t sbits = s_hi > s_lo ? ((1u << s_hi) - 1u) & ~((1u << s_lo) - 1u) : 0u;
-            inside[it] = rbits | (sbits << 16);
+            in_r[it] = r_hi > r_lo ? (uint32_t)((1ull << r_hi) - 1ull) & ~(uint32_t)((1ull << r_lo) - 1ull) : 0u;
+            in_s[it] = s_hi > s_lo ? (uint32_t)((1ull << s_hi) - 1ull) & ~(uint32_t)((1ull << s_lo) - 1ull) : 0u;
           }
         }
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
@@ -420,12 +420,12 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           const uint32_t e = k_ok ? conv_tab[kc] : 0u;
           const int dr = (int)(e >> 24), ds = (int)((e >> 16) & 0xFF), c0 = (int)(e & 0xFFFF);
           const int tap_off = (dr * p.g.W + ds) * p.g.C + c0;
-          const uint32_t need = k_ok ? ((1u << dr) | (1u << (16 + ds))) : 0xFFFFFFFFu;
+
           const __half* tap_ptr = p.x + tap_off;
           const uint32_t tile_base = smem_u32(sA + (size_t)stage * kATileBytes);
 #pragma unroll
           for (int it = 0; it < kConvRowsPerThread; ++it) {
-            const bool valid = (inside[it] & need) == need;
+            const bool valid = k_ok && (((in_r[it] >> dr) & (in_s[it] >> ds) & 1u) != 0u);
             const __half* src = valid ? tap_ptr + base_off[it] : p.x;
             cp_async_16_zfill(tile_base + dst_off[it], src, valid);
           }
@@ -1342,7 +1342,7 @@ int conv_f16_launch(const helix_cfg_t* cfg_in, const void* x, const void* w, voi
   if ((g.C & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return HELIX_ERR_ALIGN;
   const int64_t M64 = (int64_t)g.NB * g.Ho * g.Wo;
   const int64_t K64 = (int64_t)g.R * g.S * g.C;
-  if (M64 > 0x7fffffff || K64 > (int64_t)kConvTableEntries * 8 || g.R > 15 || g.S > 15 || g.C > 65535)
+  if (M64 > 0x7fffffff || K64 > (int64_t)kConvTableEntries * 8 || g.R > 32 || g.S > 32 || g.C > 65535)
     return HELIX_ERR_UNSUPPORTED;
   const int M = (int)M64, K = (int)K64, N = g.KO;
   // A 1x1, stride-1, unpadded convolution is exactly a GEMM over the pixel list.

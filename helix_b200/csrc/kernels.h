@@ -20,8 +20,13 @@ int gemv_f16_static_launch(const void* W, int64_t ldw, const void* X, int64_t ld
                            int64_t ldy_inner, int rows, int K, int m, int split_k, int sm_count,
                            cudaStream_t stream, int64_t* launches);
 
-// ---- ffma_probe.cu
-int ffma_probe(int rounds, int sm_count, double* tflops, cudaStream_t stream, int64_t* launches);
+// ---- gemv_f32.cu (true-fp32 GEMV)
+size_t gemv_f32_workspace_bytes(int rows, int m, int split_k);
+int gemv_f32_default_split(int rows, int K, int sm_count);
+int gemv_f32_launch(const helix_cfg_t* cfg, const float* W, int64_t ldw, const float* X, int64_t ldx, float* Y,
+                    int64_t ldy, int64_t ldy_inner, int rows, int K, int m, void* ws, size_t ws_bytes, int sm_count,
+                    cudaStream_t stream, int64_t* launches);
+
 
 // ---- sgemm_f32.cu
 int sgemm_f32_num_configs();

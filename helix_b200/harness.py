@@ -92,6 +92,20 @@ def time_conv_f16(batch, IC, H, W, OC, kH, kW, stride, pad, cfg=None, iters=20):
     return avg
 
 
+def time_gemv_f32(rows, K, m, cfg=None, transposed=False, iters=30):
+    """Seconds per launch of the fp32 GEMV with W rotating through > 2x L2."""
+    bytes_ = 4.0 * (rows * K + m * K + m * rows)
+    nbuf = int(ROTATE_BYTES // bytes_) + 1
+    x = torch.rand((m, K), device="cuda") * 2 - 1
+    ws = [torch.rand((rows, K), device="cuda") * 2 - 1 for _ in range(nbuf)]
+    oshape = (rows, m) if transposed else (m, rows)
+    ys = [torch.empty(oshape, device="cuda") for _ in range(nbuf)]
+    ls = [ops.launch_gemv_f32(w, x, y, cfg, out_transposed=transposed) for w, y in zip(ws, ys)]
+    reps = max(1, 4 // len(ls))
+    avg, _, _ = ops.time_launches(ls * reps, warmup=3, iters=iters, use_graph=True)
+    return avg
+
+
 def time_gemm_f32(M, N, K, cfg=None, iters=10):
     a = torch.rand((M, K), device="cuda") * 2 - 1
     b = torch.rand((K, N), device="cuda") * 2 - 1
@@ -298,6 +312,13 @@ def conv_f16_result(prof_dict, batch, IC, H, W, OC, kH, kW, stride, pad):
 
 def gemm_f32_result(prof_dict, M, N, K):
     require_gpu()
+    if min(M, N) <= 8 and max(M, N) >= 64:
+        # up to eight rows or columns: the weight matrix is streamed once by the fp32 GEMV (the reference keeps
+        # a GEMV template for this case, src_template/Ampere_FP32/gemv_template_fp32.cu, but never builds it)
+        Kp = (K + 3) // 4 * 4
+        rows, m, transposed = (N, M, False) if M <= N else (M, N, True)
+        t = time_gemv_f32(rows, Kp, m, None, transposed)
+        return t * 1e3, 2.0 * M * N * K / 1e9 / (t * 1e3)
     key = costmodel.sgemm_cost_model(prof_dict, M, N, K)
     if key is None:
         raise RuntimeError("empty cost-model dictionary: run profile_template.py -b Ampere_FP32 first")

@@ -101,6 +101,8 @@ def kernel_name(launch):
     c = launch.cfg if launch.cfg.tile_n or launch.cfg.tile_m else default_config(launch)
     if launch.op == _lib.OP_GEMV_F16:
         return "gemv_f16_kernel"
+    if launch.op == _lib.OP_GEMV_F32:
+        return "gemv_f32_kernel"
     if launch.op == _lib.OP_GEMM_F32:
         return "sgemm_f32_kernel<%d,%d>" % (c.tile_m, c.tile_n)
     if c.cta_group == 2:
@@ -186,6 +188,35 @@ def launch_gemv_f16(w, x, out, cfg=None, ws=None, out_transposed=False):
     l.a, l.b, l.c = w.data_ptr(), x.data_ptr(), out.data_ptr()
     l._refs = (w, x, out)
     return _finish(l, cfg, ws)
+
+
+def launch_gemv_f32(w, x, out, cfg=None, ws=None, out_transposed=False):
+    """W[rows,K], X[m,K] (m <= 8), fp32 -> out[m,rows]; or out[rows,m] when ``out_transposed``."""
+    _require_cuda(w, x, out)
+    assert w.dtype == x.dtype == out.dtype == torch.float32
+    assert w.stride(1) == 1 and x.stride(1) == 1
+    l = Launch()
+    l.op = _lib.OP_GEMV_F32
+    l.N, l.K = w.shape
+    l.M = x.shape[0]
+    assert x.shape[1] == l.K
+    l.lda, l.ldb = w.stride(0), x.stride(0)
+    if out_transposed:
+        assert tuple(out.shape) == (l.N, l.M)
+        l.ldc, l.ldc_inner = out.stride(1), out.stride(0)
+    else:
+        assert tuple(out.shape) == (l.M, l.N)
+        l.ldc, l.ldc_inner = out.stride(0), out.stride(1)
+    l.a, l.b, l.c = w.data_ptr(), x.data_ptr(), out.data_ptr()
+    l._refs = (w, x, out)
+    return _finish(l, cfg, ws)
+
+
+def gemv_f32(w, x, out=None, cfg=None):
+    if out is None:
+        out = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float32, device=w.device)
+    run(launch_gemv_f32(w, x, out, cfg))
+    return out
 
 
 def conv_out_hw(H, W, R, S, stride, pad):
@@ -338,11 +369,11 @@ def capture_timeline(launch, warm=2):
     return buf.cpu().numpy()
 
 
-def probe_ffma_f32(rounds=2000):
-    """TFLOP/s of register-resident FFMA in the fp32 GEMM's 8x8 block pattern on the current device."""
-    out = ctypes.c_double(0.0)
-    check(_lib.load().helix_probe_ffma_f32(int(rounds), ctypes.byref(out), _stream()), "helix_probe_ffma_f32")
-    return out.value
+def selftest_bounded_wait(limit_ns=2_000_000):
+    """Launch the library's wait self-test on the current stream: a wait nothing satisfies gives up after
+    `limit_ns` and leaves HELIX_ERR_TIMEOUT in the status word (read it with check_status)."""
+    check(_lib.load().helix_selftest_bounded_wait(int(limit_ns), ctypes.c_void_p(status_word().data_ptr()), _stream()),
+          "helix_selftest_bounded_wait")
 
 
 def launch_count():

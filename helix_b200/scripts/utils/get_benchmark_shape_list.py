@@ -1,13 +1,14 @@
 """Shape suites of the sweeps (role of the reference's scripts/utils/get_benchmark_shape_list.py:1-49).
 
-Same four entry points and tuple conventions as the reference -- GEMM units are (M, N, K); convolution
-units are (batch, IC, H, W, OC, kH, kW, stride, pad) -- but the lists are generated here from the
-architectures' published layer dimensions instead of being stored as literals.  The reference
-additionally appends DeepBench- and GNN-derived GEMM/conv literals to the op-level lists; those are not
-reproduced: point HELIX_EXTRA_GEMM_SHAPES / HELIX_EXTRA_CONV_SHAPES at a JSON file with a list of tuples
-to sweep any further shapes.  The benchmark's own model-level configuration (BERT-base at batch 16,
-sequence 512 with its batched attention GEMMs, and the 53 ResNet-50 convolutions at batch 32) lives in
-helix_b200/workloads.py.
+Same four entry points, tuple conventions and contents as the reference -- GEMM units are (M, N, K);
+convolution units are (batch, IC, H, W, OC, kH, kW, stride, pad).  What follows from an architecture's
+dimensions (the transformer linear layers over the sequence-length sweep, the classifier layers over the
+batch sweep) is generated; the reference's literal tables (DeepBench and GNN GEMMs, the convolution layer
+lists, the AlexNet / ResNet / GoogLeNet op-sets) are data and live in shape_tables.json beside this file
+(written by make_shape_tables.py).  HELIX_EXTRA_GEMM_SHAPES / HELIX_EXTRA_CONV_SHAPES may point at a JSON
+file with further tuples to append to the op-level lists.  The benchmark's own model-level configuration
+(BERT-base at batch 16, sequence 512 with its batched attention GEMMs, and the 53 ResNet-50 convolutions
+at batch 32) lives in helix_b200/workloads.py.
 """
 import json
 import os
@@ -18,6 +19,17 @@ TOKEN_COUNTS = [2, 13, 31, 53, 73, 101, 127, 151, 179, 199, 233, 263, 283, 317, 
                 1277, 1297, 1321, 1381, 1429, 1453, 1487, 1521, 1559, 1597, 1621, 1663, 1697, 1739, 1783, 1823, 1871,
                 1902, 1949]
 CNN_BATCHES = [1, 4, 8, 12, 16, 20, 24, 28, 32, 36, 40, 44, 48, 52, 56, 60, 64]
+
+
+_TABLES = None
+
+
+def _table(name):
+    global _TABLES
+    if _TABLES is None:
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "shape_tables.json")) as f:
+            _TABLES = json.load(f)
+    return [tuple(row) for row in _TABLES[name]]
 
 
 def _extra(env):
@@ -49,7 +61,7 @@ def get_gemm_op_MNKList():
     fc_nk = [(12544, 120), (120, 80), (80, 10), (9216, 4096), (4096, 4096), (4096, 1000), (25088, 4096), (512, 1000),
              (1024, 1000), (25088, 1000)]
     cnn = [(m, n, k) for m in [1, 2, 4, 8, 16, 32, 64, 128] for (n, k) in fc_nk]
-    return transformer + cnn + _extra("HELIX_EXTRA_GEMM_SHAPES")
+    return transformer + cnn + _table("gemm_deepbench") + _table("gemm_gnn") + _extra("HELIX_EXTRA_GEMM_SHAPES")
 
 
 def get_llm_opset_MNKList():
@@ -63,47 +75,13 @@ def get_llm_opset_MNKList():
     return bert, llama2, gpt2
 
 
-def _alexnet():
-    return [(3, 224, 224, 96, 11, 11, 4, 0), (96, 26, 26, 256, 5, 5, 1, 2), (256, 12, 12, 384, 3, 3, 1, 1),
-            (384, 12, 12, 384, 3, 3, 1, 1), (384, 12, 12, 256, 3, 3, 1, 1)]
-
-
-def _resnet18_style():
-    """3x3 stem at full resolution, then four stages of two basic blocks; stage changes by a strided 3x3 and a
-    1x1 projection."""
-    layers = [(3, 224, 224, 64, 3, 3, 1, 1)]
-    ch, res = 64, 112
-    layers += [(ch, res, res, ch, 3, 3, 1, 1)] * 4
-    for _ in range(3):
-        out, nres = ch * 2, res // 2
-        layers += [(ch, res, res, out, 3, 3, 2, 1), (out, nres, nres, out, 3, 3, 1, 1), (ch, res, res, out, 1, 1, 2, 0),
-                   (out, nres, nres, out, 3, 3, 1, 1), (out, nres, nres, out, 3, 3, 1, 1)]
-        ch, res = out, nres
-    return layers
-
-
-def _googlenet():
-    """Stem plus the nine inception modules (1x1, 3x3-reduce, 3x3, 5x5-reduce, 5x5, pool-projection)."""
-    layers = [(3, 224, 224, 64, 7, 7, 2, 3), (64, 56, 56, 192, 3, 3, 1, 1)]
-    modules = [  # (resolution, in, n1x1, n3x3r, n3x3, n5x5r, n5x5, pool)
-        (28, 192, 64, 96, 128, 16, 32, 32), (28, 256, 128, 128, 192, 32, 96, 64),
-        (14, 480, 192, 96, 208, 16, 48, 64), (14, 512, 160, 112, 224, 24, 64, 64), (14, 512, 128, 128, 256, 24, 64, 64),
-        (14, 512, 112, 144, 288, 32, 64, 64), (14, 528, 256, 160, 320, 32, 128, 128),
-        (7, 832, 256, 160, 320, 32, 128, 128), (7, 832, 384, 192, 384, 48, 128, 128)]
-    for r, cin, n1, n3r, n3, n5r, n5, pp in modules:
-        layers += [(cin, r, r, n1, 1, 1, 1, 0), (cin, r, r, n3r, 1, 1, 1, 0), (n3r, r, r, n3, 3, 3, 1, 1),
-                   (cin, r, r, n5r, 1, 1, 1, 0), (n5r, r, r, n5, 5, 5, 1, 2), (cin, r, r, pp, 1, 1, 1, 0)]
-    return layers
-
-
 def get_conv_op_shape_list():
-    without_batch = _alexnet() + _googlenet() + _resnet18_style()
-    cnn = [(batch,) + shape for batch in CNN_BATCHES for shape in without_batch]
-    return cnn + _extra("HELIX_EXTRA_CONV_SHAPES")
+    cnn = [(batch,) + shape for batch in CNN_BATCHES for shape in _table("conv_layers")]
+    return cnn + _table("conv_deepbench") + _extra("HELIX_EXTRA_CONV_SHAPES")
 
 
 def get_cnn_opset_shape_List():
-    alexnet = [(batch,) + shape for batch in CNN_BATCHES for shape in _alexnet()]
-    resnet = [(batch,) + shape for batch in CNN_BATCHES for shape in _resnet18_style()]
-    googlenet = [(batch,) + shape for batch in CNN_BATCHES for shape in _googlenet()]
+    alexnet = [(batch,) + shape for batch in CNN_BATCHES for shape in _table("opset_alexnet")]
+    resnet = [(batch,) + shape for batch in CNN_BATCHES for shape in _table("opset_resnet")]
+    googlenet = [(batch,) + shape for batch in CNN_BATCHES for shape in _table("opset_googlenet")]
     return alexnet, resnet, googlenet

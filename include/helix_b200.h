@@ -48,7 +48,8 @@ typedef enum helix_op {
   HELIX_OP_GEMV_F16 = 1, /* memory-bound SIMT GEMV for 1..8 right-hand sides              */
   HELIX_OP_CONV_F16 = 2, /* implicit-GEMM NHWC convolution on the same tensor-core path   */
   HELIX_OP_GEMM_F32 = 3, /* SIMT FFMA GEMM, true fp32                                     */
-  HELIX_OP_CONV_F32 = 4  /* true-fp32 NHWC convolution: column matrix + the FFMA GEMM      */
+  HELIX_OP_CONV_F32 = 4, /* true-fp32 NHWC convolution: column matrix + the FFMA GEMM      */
+  HELIX_OP_GEMV_F32 = 5  /* true-fp32 memory-bound GEMV for 1..8 right-hand sides          */
 } helix_op_t;
 
 /* Replaces the queried-nowhere literal `108` (A100 SM count) of the reference's
@@ -108,7 +109,7 @@ typedef struct helix_cfg {
 typedef struct helix_launch {
   int op;            /* helix_op_t */
   helix_cfg_t cfg;   /* cfg.tile_m == 0: library default */
-  const void* a;     /* GEMM: A[M,K]   GEMV: W[rows=N,K]   CONV: x[N,H,W,C]   */
+  const void* a;     /* GEMM: A[M,K]   GEMV (f16 and f32): W[rows=N,K]   CONV: x[N,H,W,C]   */
   const void* b;     /* GEMM: B[N,K] (f16) / B[K,N] (f32)  GEMV: X[m=M,K]  CONV: w[KO,R,S,C] */
   void* c;           /* GEMM: C[M,N]   GEMV: Y             CONV: y[N,Ho,Wo,KO] */
   int64_t lda, ldb, ldc; /* leading dimensions in elements (0 = packed)        */
@@ -194,6 +195,17 @@ int helix_gemm_f32(const helix_cfg_t* cfg, const float* A, int64_t lda, int tran
                    const float* B, int64_t ldb, float* C, int64_t ldc, int M, int N, int K,
                    void* status_dev, void* stream);
 
+/* Y[i,r] = sum_k W[r,k] * X[i,k] in true fp32 (FFMA only), i < m <= 8; element (i,r) is stored at
+ * Y[i*ldy + r*ldy_inner].  K and the leading dimensions are multiples of 4 floats, bases 16-byte aligned.
+ * Each output is the shuffle-tree sum (xor 16, 8, 4, 2, 1) of 32 lane chains, lane l adding the elements
+ * 4l..4l+3 of every 128-element stretch of K in ascending order: a fixed order, so results repeat bit for
+ * bit.  cfg: tile_n = rows per warp (1, 2), load_group = loads in flight (2, 4, 8), split_k; NULL = library
+ * choice.  Stands in for the reference's fp32 GEMV template, which none of its scripts builds
+ * (src_template/Ampere_FP32/gemv_template_fp32.cu:153-218). */
+int helix_gemv_f32(const helix_cfg_t* cfg, const float* W, int64_t ldw, const float* X, int64_t ldx, float* Y,
+                   int64_t ldy, int64_t ldy_inner, int rows, int K, int m, void* ws, size_t ws_bytes,
+                   void* status_dev, void* stream);
+
 /* y[N,Ho,Wo,KO] = conv2d(x[N,H,W,C], w[KO,R,S,C]) in true fp32, zero padding: a column matrix
  * col[N*Ho*Wo][R*S*C] and the transposed weights are written into the caller's workspace
  * (helix_workspace_bytes; 256-byte aligned), then the FFMA GEMM of helix_gemm_f32 runs on them, so
@@ -248,13 +260,12 @@ int helix_gemv_f16_static(const void* W, int64_t ldw, const void* X, int64_t ldx
 int helix_trace_buffer(void* device_buf, size_t bytes);
 int helix_trace_words_per_cta(void);
 
-/* Calibration probe without a reference counterpart (the reference reports TFLOP/s only,
- * sgemm.cu:655-660): the FFMA rate, in TFLOP/s, that the current device sustains on the register
- * pattern of the fp32 GEMM's inner loop (8 x 8 outer-product block per thread, two 256-thread CTAs
- * per SM, no memory traffic), timed with events on `stream` over `rounds` x 1024 FFMA per thread.
- * Blocks until the probe has run.  The fp32 GEMM is rated against this figure as well as against
- * SMs x 128 lanes x 2 x clock. */
-int helix_probe_ffma_f32(int rounds, double* tflops, void* stream);
+/* Self-test of the bounded device-side wait (no reference counterpart: the reference's kernels have no
+ * waits that can fail).  One thread waits on a barrier that nothing arrives at; after `limit_ns`
+ * nanoseconds (at most one second) the wait gives up, HELIX_ERR_TIMEOUT appears in *status_dev and the
+ * kernel returns normally.  This is the path every kernel of the library takes when a pipeline stage
+ * never completes; the caller reads the status word after synchronising. */
+int helix_selftest_bounded_wait(uint64_t limit_ns, void* status_dev, void* stream);
 
 /* Number of kernel launches this process has queued through the library (all ops). */
 int64_t helix_launch_count(void);

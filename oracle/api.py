@@ -101,6 +101,18 @@ def sgemm_parallel(a, b, tiling=(8, 1, 32, 64, 1, 2, 6), threads=0, fma=False, o
     return c
 
 
+def gemv_f32_lane_tree(w, x):
+    """y[m,rows] = x[m,K] . w[rows,K]^T in fp32, summed as a 32-lane streaming GEMV sums it (lane chains of
+    fused multiply-adds over ascending k, then the xor tree); K a multiple of 4."""
+    w, x = _f32(w), _f32(x)
+    rows, K = w.shape
+    m = x.shape[0]
+    assert x.shape[1] == K
+    y = np.empty((m, rows), np.float32)
+    _chk(lib().oracle_gemv_f32_lane_tree(_p(w), _p(x), _p(y), rows, K, m), "gemv_f32_lane_tree")
+    return y
+
+
 def hgemm_naive(a, b, b_is_nk=True, fma=False):
     """fp16 x fp16 -> (fp16, fp32) as cpuF16F16Gemm (gemm.cu:26-37).
 

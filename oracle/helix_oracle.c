@@ -361,6 +361,36 @@ int oracle_sgemm_parallel(const float* a, const float* b, float* c, int M, int N
 }
 
 /* ------------------------------------------------------------------------- */
+/* FP32 GEMV in the summation order of a 32-lane streaming kernel (the scheme  */
+/* of the reference's mySGemvKernel_Stage4<float>, src_template/Ampere_FP32/    */
+/* gemv_template_fp32.cu:153-218, with fused multiply-adds): lane l owns the    */
+/* elements 4l..4l+3 of every 128-element stretch of K and keeps one fmaf chain */
+/* over them in ascending k; the 32 partial sums are combined by the xor tree   */
+/* 16, 8, 4, 2, 1.  y[i][r] = sum_k w[r][k] * x[i][k]; K a multiple of 4.       */
+/* ------------------------------------------------------------------------- */
+int oracle_gemv_f32_lane_tree(const float* w, const float* x, float* y, int rows, int K, int m) {
+  if (rows < 0 || K < 0 || m < 0 || (K & 3)) return ORACLE_EINVAL;
+#pragma omp parallel for schedule(static)
+  for (int r = 0; r < rows; ++r) {
+    for (int i = 0; i < m; ++i) {
+      float v[32], t[32];
+      for (int l = 0; l < 32; ++l) {
+        float acc = 0.0f;
+        for (int k0 = 4 * l; k0 < K; k0 += 128)
+          for (int j = 0; j < 4; ++j) acc = fmaf(w[(size_t)r * K + k0 + j], x[(size_t)i * K + k0 + j], acc);
+        v[l] = acc;
+      }
+      for (int off = 16; off > 0; off >>= 1) {
+        for (int l = 0; l < 32; ++l) t[l] = v[l] + v[l ^ off];
+        for (int l = 0; l < 32; ++l) v[l] = t[l];
+      }
+      y[(size_t)i * rows + r] = v[0];
+    }
+  }
+  return ORACLE_OK;
+}
+
+/* ------------------------------------------------------------------------- */
 /* FP16 storage, FP32 accumulate.  Follows cpuF16F16Gemm (gemm.cu:26-37):      */
 /* psum += (float)a * (float)b over ascending k, one rounding to half at the   */
 /* end.  b_is_nk=0: B is K x N row-major as in that loop; b_is_nk=1: B is      */

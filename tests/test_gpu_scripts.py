@@ -123,6 +123,12 @@ def test_op_level_list_sampled_parity_with_the_models_pick(workdir):
     d = costmodel.load(str(workdir / "build" / "prof_dict" / "Ampere_FP16_cost_model.dict"))
     shapes = get_gemm_op_MNKList()
     picked = shapes[::29] + [s for s in shapes if s[2] % 8][::7]
+    # the extremes of the DeepBench- and GNN-derived tables: K = 500 000 against one or four columns, 1.9 M rows
+    # against 16 columns with K = 66, K = 29, three to seven columns
+    extremes = [(512, 1, 500000), (1024, 4, 500000), (1889542, 16, 66), (43466, 16, 29), (2708, 16, 1433),
+                (7680, 2, 2560), (35, 700, 2048)] + [s for s in shapes if s[1] in (3, 6, 7)][:3]
+    assert all(e in shapes for e in extremes)
+    picked += extremes
     kinds = set()
     for idx, (M, N, K) in enumerate(picked):
         rng = np.random.default_rng(1000 + idx)
@@ -169,7 +175,11 @@ def test_conv_op_level_list_sampled_parity_with_the_models_pick(workdir):
     from utils.get_benchmark_shape_list import get_conv_op_shape_list
     oracle.build()
     d = costmodel.load(str(workdir / "build" / "prof_dict" / "Ampere_FP16_cost_model.dict"))
-    for idx, (B, IC, H, W, OC, kH, kW, stride, pad) in enumerate(get_conv_op_shape_list()[::53]):
+    layers = get_conv_op_shape_list()
+    # plus the DeepBench speech layers: one input channel, 5 x 20 and 5 x 10 filters, stride 2
+    speech = [(1, 1, 161, 700, 32, 5, 20, 2, 0), (4, 32, 79, 341, 32, 5, 10, 2, 0)]
+    assert all(l in layers for l in speech)
+    for idx, (B, IC, H, W, OC, kH, kW, stride, pad) in enumerate(layers[::53] + speech):
         rng = np.random.default_rng(2000 + idx)
         C = (IC + 7) // 8 * 8
         x = np.zeros((B, H, W, C), np.float16)

@@ -86,14 +86,3 @@ def test_sgemm_golden_vectors_from_reference_loop():
         util.assert_f32_close(got, g[n + "_c"], n)
     assert np.all(_run(g["s_one_a"], g["s_one_b"]) == 1000.0)
     assert np.array_equal(_run(g["s_id_a"], g["s_id_b"]), g["s_id_a"])
-
-
-def test_ffma_probe_reports_a_plausible_rate():
-    """The calibration probe: between a third of and a little above the nominal 128 lanes x 2 x clock x SMs."""
-    info = ops.device_info()
-    nominal = info.sm_count * 128 * 2 * info.clock_khz * 1e3 / 1e12
-    got = ops.probe_ffma_f32(500)
-    assert 0.33 * nominal < got < 1.05 * nominal, (got, nominal)
-    before = ops.launch_count()
-    ops.probe_ffma_f32(10)
-    assert ops.launch_count() == before + 2

@@ -93,19 +93,33 @@ def test_lpt_partition_balances_and_is_deterministic():
         assert p == workloads.lpt_partition(costs, parts)
 
 
-def test_shape_suites_have_the_reference_structure():
+def _digest(lists):
+    import hashlib
+    return hashlib.sha256(repr([[tuple(t) for t in lst] for lst in lists]).encode()).hexdigest()
+
+
+def test_shape_suites_equal_the_references():
+    """Counts and content hashes of the four shape-list functions, pinned from the reference's
+    scripts/utils/get_benchmark_shape_list.py (the hashes are printed by make_shape_tables.py)."""
     sys.path.insert(0, SCRIPTS)
     try:
         m = importlib.import_module("utils.get_benchmark_shape_list")
     finally:
         sys.path.remove(SCRIPTS)
     gemm = m.get_gemm_op_MNKList()
-    assert len(gemm) == 60 * 16 + 8 * 10 and all(len(s) == 3 for s in gemm)
-    bert, llama2, gpt2 = m.get_llm_opset_MNKList()
-    assert (len(bert), len(llama2), len(gpt2)) == (4380, 240, 5760)     # same counts as the reference's lists
-    alex, res, goog = m.get_cnn_opset_shape_List()
-    assert (len(alex), len(res), len(goog)) == (85, 340, 952)
-    assert all(len(s) == 9 for s in m.get_conv_op_shape_list())
+    assert len(gemm) == 1274 and all(len(s) == 3 for s in gemm)
+    assert _digest([gemm]) == "2f6ffeee2629219496dbe5448fd1e1cc2c29e8d6a541b58d9fa5d254c01dd6a6"
+    assert (512, 1, 500000) in gemm and (1889542, 16, 66) in gemm and (2708, 16, 1433) in gemm
+    llm = m.get_llm_opset_MNKList()
+    assert tuple(len(x) for x in llm) == (4380, 240, 5760)
+    assert _digest(llm) == "e37b93b87aac8b0f761df084fc4dcf4e742e3bded464fc27ebf1c1faba9c0d7a"
+    conv = m.get_conv_op_shape_list()
+    assert len(conv) == 1756 and all(len(s) == 9 for s in conv)
+    assert _digest([conv]) == "dd481163f4c5c2ba0c9bef19b3378683ad84af8ed7dc36d57003bb789266cf92"
+    assert (1, 1, 161, 700, 32, 5, 20, 2, 0) in conv
+    cnn = m.get_cnn_opset_shape_List()
+    assert tuple(len(x) for x in cnn) == (85, 340, 952)
+    assert _digest(cnn) == "d012f022a264451e930529cd8dd28deef1ad1c9edb5500b3a51c6f0a50cbe9f2"
 
 
 @pytest.mark.parametrize("script,args,expect", [

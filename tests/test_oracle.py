@@ -135,3 +135,18 @@ def test_half_conversion_matches_numpy(oracle):
     rng = np.random.default_rng(9)
     v = (rng.standard_normal(4096) * 10.0 ** rng.integers(-6, 5, 4096)).astype(np.float32)
     assert np.array_equal(oracle.f32_to_f16(v).view(np.uint16), v.astype(np.float16).view(np.uint16))
+
+
+def test_gemv_f32_lane_tree_is_a_reordering_of_the_plain_sum(oracle):
+    """The 32-lane summation order of the fp32 GEMV stays within fp32 reassociation noise of the plain fmaf chain
+    and of the fp64-accumulated product; with K <= 4 (one lane holds everything) it IS the plain chain."""
+    rng = np.random.default_rng(5)
+    w = rng.uniform(-1, 1, (37, 1000)).astype(np.float32)
+    x = rng.uniform(-1, 1, (3, 1000)).astype(np.float32)
+    y = oracle.gemv_f32_lane_tree(w, x)
+    ref64 = (x.astype(np.float64) @ w.astype(np.float64).T)
+    assert np.linalg.norm(y - ref64) / np.linalg.norm(ref64) <= 1e-6
+    chain = oracle.sgemm_naive(x, np.ascontiguousarray(w.T), fma=True)
+    assert np.linalg.norm(y - chain) / np.linalg.norm(chain) <= 1e-6
+    w4, x4 = w[:, :4].copy(), x[:, :4].copy()
+    assert np.array_equal(oracle.gemv_f32_lane_tree(w4, x4), oracle.sgemm_naive(x4, np.ascontiguousarray(w4.T), fma=True))
