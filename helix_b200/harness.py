@@ -385,10 +385,25 @@ def worker_conv_f32(device, unit, prof_dict):
 
 
 def run_shape_list(units, worker, prof_dict, gpus=1, predicted=None, journal=None):
-    """Rows (ordered like `units`) of a sweep over 1..N GPUs of this box."""
+    """Rows (ordered like `units`) of a sweep over 1..N GPUs of this box.  With `journal` (a JSONL path) every
+    finished shape is appended as one line and shapes already present there are not run again, so a sweep
+    that was interrupted resumes where it stopped."""
     from . import shard
     if gpus <= 1:
-        return [worker(torch.cuda.current_device() if torch.cuda.is_available() else 0, u, prof_dict) for u in units]
+        import json
+        done = shard.read_journal(journal)
+        rows = []
+        for i, u in enumerate(units):
+            if i in done and list(done[i].get("shape", [])) == list(u):
+                rows.append(done[i])
+                continue
+            row = dict(worker(torch.cuda.current_device() if torch.cuda.is_available() else 0, u, prof_dict))
+            row["index"] = i
+            if journal:
+                with open(journal, "a") as f:
+                    f.write(json.dumps(row) + "\n")
+            rows.append(row)
+        return rows
     rows, stats = shard.run_sharded(units, worker, list(range(gpus)), costs=predicted, journal=journal,
                                     fn_args=(prof_dict,))
     if stats["unfinished"]:

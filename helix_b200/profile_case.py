@@ -1,4 +1,5 @@
-"""Run one operator a few times on seeded data -- the target of `ncu` captures.
+"""Profiling tool, not part of the operator path: run one operator a few times on seeded data -- the target of
+the `ncu` captures whose summaries are kept under profiles/ (their command lines name this module).
 
   python -m helix_b200.profile_case gemm M N K [--batch B] [--bn 256] [--pair] [--stream-k] [--swap] [--reps 3]
   python -m helix_b200.profile_case conv B IC H W OC kH kW stride pad [--bn 128] [--reps 3]

@@ -8,22 +8,22 @@ from Ampere_FP16.Ampere_FP16_conv import get_Ampere_FP16_conv_cudnn_result
 root_path = os.getcwd()
 
 
-def Ampere_FP16_Helix_op_level_Conv_benchmark(backend="cuda", gpus=1, limit=0):
+def Ampere_FP16_Helix_op_level_Conv_benchmark(backend="cuda", gpus=1, limit=0, journal=None):
     from helix_b200 import costmodel, harness
     prof_dict = costmodel.load(f'{root_path}/build/prof_dict/Ampere_FP16_cost_model.dict')
 
     shape_list = get_conv_op_shape_list()
     if limit:
         shape_list = shape_list[:limit]
-    rows = harness.run_shape_list(shape_list, harness.worker_conv_f16, prof_dict, gpus)
+    rows = harness.run_shape_list(shape_list, harness.worker_conv_f16, prof_dict, gpus, None, journal=journal)
     for (batch, input_channel, H, W, output_channel, kH, kW, stride, pad), row in zip(shape_list, rows):
         helix_tflops = row["tflops"]
         print(f'{batch}x{input_channel}x{H}x{W}x{output_channel}x{kH}x{kW}x{stride}x{pad}: Helix: {helix_tflops:.2f} TFLOPS')
     return rows
 
 
-def Ampere_FP16_cudnn_op_level_Conv_benchmark():
-    shape_list = get_conv_op_shape_list()
+def Ampere_FP16_cudnn_op_level_Conv_benchmark(limit=0):
+    shape_list = get_conv_op_shape_list()[:limit or None]
     for batch, input_channel, H, W, output_channel, kH, kW, stride, pad in shape_list:
         _, cudnn_tflops = get_Ampere_FP16_conv_cudnn_result(batch, input_channel, H, W, output_channel, kH, kW, stride, pad)
         print(f'{batch}x{input_channel}x{H}x{W}x{output_channel}x{kH}x{kW}x{stride}x{pad}: cudnn: {cudnn_tflops:.2f} TFLOPS')

@@ -8,7 +8,7 @@ from Ampere_FP16.Ampere_FP16_gemm import get_Ampere_FP16_gemm_cublas_result
 root_path = os.getcwd()
 
 
-def Ampere_FP16_Helix_op_level_GEMM_benchmark(backend="cuda", gpus=1, limit=0):
+def Ampere_FP16_Helix_op_level_GEMM_benchmark(backend="cuda", gpus=1, limit=0, journal=None):
     from helix_b200 import costmodel, harness
     prof_dict = costmodel.load(f'{root_path}/build/prof_dict/Ampere_FP16_cost_model.dict')
 
@@ -16,15 +16,15 @@ def Ampere_FP16_Helix_op_level_GEMM_benchmark(backend="cuda", gpus=1, limit=0):
     if limit:
         MNKList = MNKList[:limit]
     predicted = [costmodel.predicted_time(prof_dict, costmodel.cost_model(prof_dict, M, N, K), M, N, K) for M, N, K in MNKList]
-    rows = harness.run_shape_list(MNKList, harness.worker_gemm_f16, prof_dict, gpus, predicted)
+    rows = harness.run_shape_list(MNKList, harness.worker_gemm_f16, prof_dict, gpus, predicted, journal=journal)
     for (M, N, K), row in zip(MNKList, rows):
         helix_tflops = row["tflops"]
         print(f'{M}x{N}x{K}: Helix: {helix_tflops:.2f} TFLOPS')
     return rows
 
 
-def Ampere_FP16_cublas_op_level_GEMM_benchmark():
-    MNKList = get_gemm_op_MNKList()
+def Ampere_FP16_cublas_op_level_GEMM_benchmark(limit=0):
+    MNKList = get_gemm_op_MNKList()[:limit or None]
     for M, N, K in MNKList:
         _, cublas_tflops = get_Ampere_FP16_gemm_cublas_result(M, N, K)
         print(f'{M}x{N}x{K}: cublas: {cublas_tflops:.2f} TFLOPS')

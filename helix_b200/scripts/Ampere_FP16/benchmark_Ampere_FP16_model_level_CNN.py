@@ -8,16 +8,16 @@ from Ampere_FP16.Ampere_FP16_conv import get_Ampere_FP16_conv_cudnn_result
 root_path = os.getcwd()
 
 
-def Ampere_FP16_Helix_model_level_CNN_benchmark(backend="cuda", gpus=1, limit=0):
+def Ampere_FP16_Helix_model_level_CNN_benchmark(backend="cuda", gpus=1, limit=0, journal=None):
     from helix_b200 import costmodel, harness
     prof_dict = costmodel.load(f'{root_path}/build/prof_dict/Ampere_FP16_cost_model.dict')
 
     costs = []
-    for shape_list in get_cnn_opset_shape_List():
+    for model_idx, shape_list in enumerate(get_cnn_opset_shape_List()):
         if limit:
             shape_list = shape_list[:limit]
         distinct = sorted(set(shape_list))
-        rows = harness.run_shape_list(distinct, harness.worker_conv_f16, prof_dict, gpus)
+        rows = harness.run_shape_list(distinct, harness.worker_conv_f16, prof_dict, gpus, None, journal=(f'{journal}.model{model_idx}' if journal else None))   # one journal per model: indices are per list
         ms = {u: r["ms"] for u, r in zip(distinct, rows)}
         costs.append(sum(ms[u] for u in shape_list))
     helix_AlexNet_cost, helix_ResNet_cost, helix_GoogleNet_cost = costs

@@ -8,18 +8,18 @@ from Ampere_FP16.Ampere_FP16_gemm import get_Ampere_FP16_gemm_cublas_result
 root_path = os.getcwd()
 
 
-def Ampere_FP16_Helix_model_level_LLM_benchmark(backend="cuda", gpus=1, limit=0):
+def Ampere_FP16_Helix_model_level_LLM_benchmark(backend="cuda", gpus=1, limit=0, journal=None):
     from helix_b200 import costmodel, harness
     prof_dict = costmodel.load(f'{root_path}/build/prof_dict/Ampere_FP16_cost_model.dict')
 
     lists = get_llm_opset_MNKList()
     costs = []
-    for MNKList in lists:
+    for model_idx, MNKList in enumerate(lists):
         if limit:
             MNKList = MNKList[:limit]
         # identical shapes repeat many times inside a model: measure each distinct shape once
         distinct = sorted(set(MNKList))
-        rows = harness.run_shape_list(distinct, harness.worker_gemm_f16, prof_dict, gpus)
+        rows = harness.run_shape_list(distinct, harness.worker_gemm_f16, prof_dict, gpus, None, journal=(f'{journal}.model{model_idx}' if journal else None))   # one journal per model: indices are per list
         ms = {u: r["ms"] for u, r in zip(distinct, rows)}
         costs.append(sum(ms[u] for u in MNKList))
     helix_Bert_cost, helix_LLAMA2_cost, helix_GPT2_cost = costs

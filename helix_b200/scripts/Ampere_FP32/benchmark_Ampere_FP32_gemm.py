@@ -8,22 +8,22 @@ from Ampere_FP32.Ampere_FP32_gemm import get_Ampere_FP32_gemm_cublas_result
 root_path = os.getcwd()
 
 
-def Ampere_FP32_Helix_op_level_GEMM_benchmark(backend="cuda", gpus=1, limit=0):
+def Ampere_FP32_Helix_op_level_GEMM_benchmark(backend="cuda", gpus=1, limit=0, journal=None):
     from helix_b200 import costmodel, harness
     prof_dict = costmodel.load(f'{root_path}/build/prof_dict/Ampere_FP32_cost_model.dict')
 
     MNKList = get_gemm_op_MNKList()
     if limit:
         MNKList = MNKList[:limit]
-    rows = harness.run_shape_list(MNKList, harness.worker_gemm_f32, prof_dict, gpus)
+    rows = harness.run_shape_list(MNKList, harness.worker_gemm_f32, prof_dict, gpus, None, journal=journal)
     for (M, N, K), row in zip(MNKList, rows):
         helix_tflops = row["tflops"]
         print(f'{M}x{N}x{K}: Helix: {helix_tflops:.2f} TFLOPS')
     return rows
 
 
-def Ampere_FP32_cublas_op_level_GEMM_benchmark():
-    for M, N, K in get_gemm_op_MNKList():
+def Ampere_FP32_cublas_op_level_GEMM_benchmark(limit=0):
+    for M, N, K in get_gemm_op_MNKList()[:limit or None]:
         _, cublas_tflops = get_Ampere_FP32_gemm_cublas_result(M, N, K)
         print(f'{M}x{N}x{K}: cublas: {cublas_tflops:.2f} TFLOPS')
 

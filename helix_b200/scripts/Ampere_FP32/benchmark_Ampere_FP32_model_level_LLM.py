@@ -8,15 +8,15 @@ from Ampere_FP32.Ampere_FP32_gemm import get_Ampere_FP32_gemm_cublas_result
 root_path = os.getcwd()
 
 
-def Ampere_FP32_Helix_model_level_LLM_benchmark(backend="cuda", gpus=1, limit=0):
+def Ampere_FP32_Helix_model_level_LLM_benchmark(backend="cuda", gpus=1, limit=0, journal=None):
     from helix_b200 import costmodel, harness
     prof_dict = costmodel.load(f'{root_path}/build/prof_dict/Ampere_FP32_cost_model.dict')
     costs = []
-    for MNKList in get_llm_opset_MNKList():
+    for model_idx, MNKList in enumerate(get_llm_opset_MNKList()):
         if limit:
             MNKList = MNKList[:limit]
         distinct = sorted(set(MNKList))
-        rows = harness.run_shape_list(distinct, harness.worker_gemm_f32, prof_dict, gpus)
+        rows = harness.run_shape_list(distinct, harness.worker_gemm_f32, prof_dict, gpus, None, journal=(f'{journal}.model{model_idx}' if journal else None))   # one journal per model: indices are per list
         ms = {u: r["ms"] for u, r in zip(distinct, rows)}
         costs.append(sum(ms[u] for u in MNKList))
     helix_Bert_cost, helix_LLAMA2_cost, helix_GPT2_cost = costs

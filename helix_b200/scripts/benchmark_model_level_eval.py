@@ -37,7 +37,7 @@ if __name__ == "__main__":
     if (args.model, args.backend, args.system) in func_dict.keys():
         fn = func_dict[(args.model, args.backend, args.system)]
         if args.system == 'Helix':
-            fn(gpus=args.gpus, limit=args.limit)
+            fn(gpus=args.gpus, limit=args.limit, journal=args.journal)
         else:
             fn()
     else:

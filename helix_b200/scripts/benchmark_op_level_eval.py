@@ -29,14 +29,16 @@ if __name__ == "__main__":
     parser.add_argument("-s", "--system", type=str, choices=['Helix', 'cublas', 'cudnn', 'cutlass', 'DietCode', 'onnxruntime', 'MKL', 'oneDNN', 'ACL'], default='Helix', help="system")
     parser.add_argument("--gpus", type=int, default=1, help="GPUs of this box to shard the shape list over")
     parser.add_argument("--limit", type=int, default=0, help="only the first N shapes (0 = all)")
+    parser.add_argument("--journal", type=str, default=None,
+                        help="JSONL file: one row per finished shape is appended; shapes found there are not run again")
     args = parser.parse_args()
 
     func_dict = _table() if args.backend in ('Ampere_FP16', 'Ampere_FP32') else {}
     if (args.op, args.backend, args.system) in func_dict.keys():
         fn = func_dict[(args.op, args.backend, args.system)]
         if args.system == 'Helix':
-            fn(gpus=args.gpus, limit=args.limit)
+            fn(gpus=args.gpus, limit=args.limit, journal=args.journal)
         else:
-            fn()
+            fn(limit=args.limit)
     else:
         print(f'{args.op} {args.backend} {args.system} is not supported')

@@ -16,14 +16,26 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _REF_DIR = os.path.join(_HERE, "_ref")
 _SGEMM_SO = os.path.join(_REF_DIR, "libref_sgemm.so")
 _HGEMM_SO = os.path.join(_REF_DIR, "libref_hgemm.so")
-REFERENCE_TREE = os.environ.get("HELIX_REFERENCE_TREE", "/root/reference")
+
+
+def _find_reference_tree():
+    """The reference checkout: HELIX_REFERENCE_TREE, else a directory named ``reference`` beside this
+    repository; an empty string when neither holds the reference's src_template/."""
+    repo = os.path.dirname(_HERE)
+    for cand in (os.environ.get("HELIX_REFERENCE_TREE", ""), os.path.join(os.path.dirname(repo), "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "src_template")):
+            return cand
+    return ""
+
+
+REFERENCE_TREE = _find_reference_tree()
 
 
 def build():
     """Build ``oracle/_ref`` if the reference tree is present; returns availability."""
     if available():
         return True
-    if not os.path.isdir(os.path.join(REFERENCE_TREE, "src_template")):
+    if not REFERENCE_TREE:
         return False
     subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REF={REFERENCE_TREE}"])
     return available()

@@ -43,6 +43,33 @@ def test_op_level_sweep_prints_the_reference_lines(workdir):
     assert sum("Helix:" in l for l in out.splitlines()) == 2
 
 
+def test_vendor_comparators_print_the_reference_lines(workdir):
+    """`-s cublas` / `-s cudnn` (context rows beside the B200-native numbers, never on the product path) run and
+    print the reference's lines (scripts/Ampere_FP16/benchmark_Ampere_FP16_gemm.py:19-23, ..._conv.py:19-23)."""
+    out = _run(workdir, "benchmark_op_level_eval.py", "-o", "GEMM", "-b", "Ampere_FP16", "-s", "cublas", "--limit", "3")
+    rows = [l for l in out.splitlines() if ": cublas: " in l]
+    assert len(rows) == 3 and all(l.endswith(" TFLOPS") and float(l.split()[-2]) > 0 for l in rows)
+    out = _run(workdir, "benchmark_op_level_eval.py", "-o", "Conv", "-b", "Ampere_FP16", "-s", "cudnn", "--limit", "3")
+    rows = [l for l in out.splitlines() if ": cudnn: " in l]
+    assert len(rows) == 3 and all(float(l.split()[-2]) > 0 for l in rows)
+    out = _run(workdir, "benchmark_op_level_eval.py", "-o", "GEMM", "-b", "Ampere_FP32", "-s", "cublas", "--limit", "2")
+    assert sum(": cublas: " in l for l in out.splitlines()) == 2
+
+
+def test_sweep_journal_resumes(workdir):
+    """--journal: rows are appended per shape and a second run takes them from the file instead of measuring."""
+    j = workdir / "sweep.jsonl"
+    out1 = _run(workdir, "benchmark_op_level_eval.py", "-o", "GEMM", "-b", "Ampere_FP16", "-s", "Helix", "--limit", "3",
+                "--journal", str(j))
+    assert len(j.read_text().splitlines()) == 3
+    out2 = _run(workdir, "benchmark_op_level_eval.py", "-o", "GEMM", "-b", "Ampere_FP16", "-s", "Helix", "--limit", "4",
+                "--journal", str(j))
+    assert len(j.read_text().splitlines()) == 4
+    first = [l for l in out1.splitlines() if "Helix:" in l]
+    again = [l for l in out2.splitlines() if "Helix:" in l]
+    assert again[:3] == first and len(again) == 4          # identical numbers: read back, not re-measured
+
+
 def test_runtime_cost_prints_the_reference_line(workdir):
     out = _run(workdir, "runtime_cost.py", "-b", "Ampere_FP16")
     lines = [l for l in out.splitlines() if l.startswith("The runtime cost of ")]

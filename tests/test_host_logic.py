@@ -355,3 +355,16 @@ def test_numa_binding_helpers_are_best_effort():
     before = os.sched_getaffinity(0)
     assert dist_util.bind_to_gpu_numa_node(0, sysfs="/nonexistent") is None     # unreadable topology: nothing changes
     assert os.sched_getaffinity(0) == before
+
+
+def test_kernel_exe_prints_the_reference_result_line():
+    """Token [-8] of the line is the average seconds, as the reference's parsers expect
+    (scripts/Ampere_FP16/Ampere_FP16_gemm.py:440; format of src_template/Ampere_FP16/gemm.cu:687-689)."""
+    from helix_b200 import kernel_exe
+    line = kernel_exe.result_line(4096, 11008, 4096, 1.0e-4, 1.25e-4, 2.0e-4)
+    assert line == ("M N K =   4096  11008   4096, Time =   0.00010000   0.00012500   0.00020000 s, "
+                    "AVG Performance =  2954.9375 Tflops")
+    assert float(line.split()[-8]) == 1.25e-4 and float(line.split()[-2]) == pytest.approx(2954.9375)
+    cb = kernel_exe.cublas_line(16, 32, 64, 0.5, 1.25)
+    assert float(cb.split()[-4]) == 0.5 and float(cb.split()[-2]) == 1.25      # cublas_f16.cu:101 token positions
+    assert kernel_exe.main(["gemm", "1", "2"]) == 2
