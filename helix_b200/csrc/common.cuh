@@ -82,16 +82,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false (after recording the failure) when the limit ran out
-// or another role of this CTA already gave up.
+// The same test, but the thread may be parked by the hardware for up to `hint_ns` while the phase is incomplete
+// (it issues nothing meanwhile, unlike a polling loop).
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (after recording the failure) when the limit ran out or another role of
+// this CTA already gave up.  While the phase is incomplete the thread is parked by the hardware (a
+// try_wait with a suspend-time hint) instead of polling: a polling warp competes with the MMA-issuing
+// warp for its scheduler and for the shared-memory pipe (measured 3-7 % on narrow-tile kernels).
 __device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                 int* status_dev, unsigned long long limit_ns) {
-  for (int i = 0; i < 2048; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
+  for (int i = 0; i < 16; ++i)
+    if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
   const unsigned long long t0 = global_timer_ns();
   while (true) {
-    for (int i = 0; i < 256; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
+    for (int i = 0; i < 8; ++i)
+      if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
     if (*abort_flag) return false;
     if (global_timer_ns() - t0 > limit_ns) {
       *abort_flag = 1;

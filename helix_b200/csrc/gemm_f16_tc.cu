@@ -19,7 +19,8 @@
 //     evenly to all CTAs, so that every SM stays busy whatever the tile count (one SM cannot
 //     pull more than about 1/148 of the HBM bandwidth, so memory-bound shapes need all of them);
 //   * epilogue warps read TMEM with tcgen05.ld, round once to fp16 and store to global memory;
-//     partial K ranges are stored as fp32 and summed in a fixed order by a second kernel;
+//     partial K ranges are stored as fp32 slots; split-K slices are summed in slice order by the CTA that
+//     completes a tile last, stream-K ranges by a small second kernel (both deterministic);
 //   * swap_ab puts the large N extent on the 128-row UMMA axis when M is skinny.
 // For convolution the A-side tile is gathered by 8 producer warps with 16-byte zero-filling
 // cp.async (8 lanes per output pixel, K axis ordered (r, s, c)), written in the same swizzled
@@ -30,6 +31,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -46,7 +48,7 @@ constexpr int kConvTableEntries = 4096;     // 8-channel chunks of the K axis (K
 constexpr int kConvProducerWarps = 8;       // gather warps: 16 tile rows each, 4 per thread
 constexpr int kConvRowsPerThread = 4;
 constexpr int kConvThreads = kConvProducerWarps * 32 + 32 + 128;  // + MMA warp + 4 epilogue warps
-constexpr int kGemmProducerWarps = 4;      // TMA-issuing warps: K slab n belongs to warp n % load_warps
+constexpr int kGemmProducerWarps = 4;      // warps ahead of the MMA warp: warp 0 idles, warps 1-3 issue TMA loads (slab n: issuer n % load_warps)
 constexpr int kGemmThreads = kGemmProducerWarps * 32 + 32 + 128;  // TMA warps + MMA warp + 4 epilogue warps
 constexpr int kStoreStagingBytes = 4 * 2 * 32 * 128;              // two 32-row x 128-byte boxes per epilogue warp
 constexpr int kEpiBarrier = 1;                                    // named barrier of the 128 epilogue threads
@@ -55,7 +57,9 @@ enum OutMode { kOutDirect = 0, kOutSplitSlice = 1, kOutStreamSlot = 2 };
 
 struct GemmParams {
   __half* C;
-  float* partial;
+  float* partial;   // fp32 slots of partial tiles, kBM x BN each, stored lane-major (see the epilogue)
+  unsigned long long* counters;   // split-K: one arrival counter per tile, {launch epoch : 32, arrivals : 32}
+  unsigned int epoch;             // tag of this launch in the counters (a counter with another tag is stale)
   int64_t ldc;
   int64_t stride_c;
   int PM, PN, K;  // extents on the 128-row axis, on the BN axis, and the reduction
@@ -64,7 +68,7 @@ struct GemmParams {
   int tiles_m, tiles_n, num_kb;
   int raster;
   int stages;
-  int load_warps;  // warps that issue TMA loads (1..kGemmProducerWarps); an issuing thread is held for
+  int load_warps;  // warps that issue TMA loads (1..kGemmProducerWarps - 1); an issuing thread is held for
                    // a few hundred cycles per tensor copy, so several issuers are needed to keep the
                    // ring full
   // tile-list schedule (stream_k == 0): items = tiles x split_k, item t of CTA c is c + i*grid
@@ -112,6 +116,7 @@ struct WorkItem {
   int kb0, kb1;
   int mode;  // OutMode
   int aux;   // split slice index or stream-K slot
+  int tile;  // linear tile index (split-K: names the tile's arrival counter and its slots)
 };
 
 __device__ __forceinline__ void decode_tile(const GemmParams& p, int t, WorkItem& w) {
@@ -138,6 +143,7 @@ __device__ __forceinline__ bool get_item(const GemmParams& p, int cta, int grid,
     int tile, ks;
     fast_divmod(t, p.fd_split, tile, ks);
     decode_tile(p, tile, w);
+    w.tile = tile;
     w.kb0 = ks * p.kb_per_split;
     w.kb1 = min(p.num_kb, w.kb0 + p.kb_per_split);
     w.mode = p.split_k > 1 ? kOutSplitSlice : kOutDirect;
@@ -211,6 +217,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   uint64_t* tmem_empty = bars + 18;
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+  volatile int* red_flag = reinterpret_cast<volatile int*>(bars + 21);   // split-K: the arrival count this CTA drew
   uint32_t* conv_tab = reinterpret_cast<uint32_t*>(bars + 22);
 
   const int warp = threadIdx.x >> 5;
@@ -271,11 +278,13 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       // tensor copy holds its issuing thread for a few hundred cycles whatever the box size, so
       // one thread alone cannot keep the ring full; consecutive slabs issued by different warps
       // also land in the same DRAM pages close in time.
-      if (lane == 0 && warp < p.load_warps) {
+      // warp 0 shares its scheduler with the MMA warp (warp 4) and stays idle: the issuing warps are 1, 2, 3
+      const int pwarp = warp - 1;
+      if (lane == 0 && pwarp >= 0 && pwarp < p.load_warps) {
         bool ok = true;
         int n_start = 0;      // number of the first slab of the current work item
-        int my_n = warp;      // next slab this warp requests; its ring stage and use parity follow it
-        int stage = warp;     // load_warps <= stages, so no wrap yet
+        int my_n = pwarp;     // next slab this warp requests; its ring stage and use parity follow it
+        int stage = pwarp;    // load_warps <= stages, so no wrap yet
         uint32_t phase = 0;
         WorkItem w;
         for (int idx = 0; ok && get_item(p, cta, grid, idx, w); ++idx) {
@@ -290,7 +299,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             pix_w = wo * p.g.stride - p.g.pad;
           }
           const int nkb = w.kb1 - w.kb0;
-          if (warp == 0) trace_mark(p, idx, 0);
+          if (pwarp == 0) trace_mark(p, idx, 0);
           for (; my_n < n_start + nkb; my_n += p.load_warps) {
             const int kb = w.kb0 + (my_n - n_start);
             ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status);
@@ -347,7 +356,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             if (stage >= stages) { stage -= stages; phase ^= 1; }
           }
           n_start += nkb;
-          if (warp == 0) trace_mark(p, idx, 1);
+          if (pwarp == 0) trace_mark(p, idx, 1);
         }
         // The last group of the CTA's slab sequence may be short: its missing slabs are made up by plain
         // arrivals, each ordered after the release of its ring stage like a real slab.
@@ -505,44 +514,46 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       const int trow = quarter * 32 + lane;      // row inside the tile
       const int row = w.m_blk * kBM + trow;      // index on the 128-row (A side) axis
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      // 64 columns of this warp's 32 rows, rounded once to fp16, through the warp's swizzled 32 x 128-byte
+      // staging box and one TMA store (full 128-byte lines, edges clipped by the tensor map); two boxes per
+      // warp alternate, so one is filled while the store of the other drains.  Only used when tma_store is set.
+      uint8_t* const stage_boxes = sC + (size_t)quarter * (2 * 32 * 128);
+      auto emit = [&](const uint32_t (&lo)[32], const uint32_t (&hi)[32], int c0) {
+        const int col0 = w.n_blk * BN + c0;
+        if (col0 >= p.PN) return;   // warp-uniform: padding columns only
+        uint8_t* stage_box = stage_boxes + box * (32 * 128);
+        const uint32_t row_base = smem_u32(stage_box) + lane * 128;
+        box ^= 1;
+        if (lane == 0) tma_store_wait_read_1();   // the store issued two boxes ago has left this buffer
+        __syncwarp();
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          const uint32_t* src = ch < 4 ? &lo[ch * 8] : &hi[(ch - 4) * 8];
+          __half2 h0 = __floats2half2_rn(__uint_as_float(src[0]), __uint_as_float(src[1]));
+          __half2 h1 = __floats2half2_rn(__uint_as_float(src[2]), __uint_as_float(src[3]));
+          __half2 h2 = __floats2half2_rn(__uint_as_float(src[4]), __uint_as_float(src[5]));
+          __half2 h3 = __floats2half2_rn(__uint_as_float(src[6]), __uint_as_float(src[7]));
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + ((ch ^ (lane & 7)) << 4)),
+                       "r"(*reinterpret_cast<uint32_t*>(&h0)), "r"(*reinterpret_cast<uint32_t*>(&h1)),
+                       "r"(*reinterpret_cast<uint32_t*>(&h2)), "r"(*reinterpret_cast<uint32_t*>(&h3))
+                       : "memory");
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_3d(&tmap_c, stage_box, col0, w.m_blk * kBM + quarter * 32, w.b);
+          tma_store_commit();
+        }
+      };
       if constexpr (BN >= 64) {
         if (p.tma_store && w.mode == kOutDirect) {
           // Fast path: 64 columns at a time go TMEM -> registers -> fp16 -> this warp's swizzled
           // 32 x 128-byte staging box -> one TMA store (full 128-byte lines, edges clipped by the
           // tensor map).  The TMEM load of the next 64 columns is in flight while the current ones
           // are converted and stored.
-          // two staging boxes per warp: one is filled while the TMA store of the other drains
-          uint8_t* const stage_boxes = sC + (size_t)quarter * (2 * 32 * 128);
           uint32_t ra[32], rb[32], na[32], nb[32];
           // registers of a TMEM load are valid only after tcgen05.wait::ld, so the two register sets
           // alternate by name instead of being copied
-          auto emit = [&](const uint32_t (&lo)[32], const uint32_t (&hi)[32], int c0) {
-            const int col0 = w.n_blk * BN + c0;
-            if (col0 >= p.PN) return;   // warp-uniform: padding columns only
-            uint8_t* stage_box = stage_boxes + box * (32 * 128);
-            const uint32_t row_base = smem_u32(stage_box) + lane * 128;
-            box ^= 1;
-            if (lane == 0) tma_store_wait_read_1();   // the store issued two boxes ago has left this buffer
-            __syncwarp();
-#pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
-              const uint32_t* src = ch < 4 ? &lo[ch * 8] : &hi[(ch - 4) * 8];
-              __half2 h0 = __floats2half2_rn(__uint_as_float(src[0]), __uint_as_float(src[1]));
-              __half2 h1 = __floats2half2_rn(__uint_as_float(src[2]), __uint_as_float(src[3]));
-              __half2 h2 = __floats2half2_rn(__uint_as_float(src[4]), __uint_as_float(src[5]));
-              __half2 h3 = __floats2half2_rn(__uint_as_float(src[6]), __uint_as_float(src[7]));
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + ((ch ^ (lane & 7)) << 4)),
-                           "r"(*reinterpret_cast<uint32_t*>(&h0)), "r"(*reinterpret_cast<uint32_t*>(&h1)),
-                           "r"(*reinterpret_cast<uint32_t*>(&h2)), "r"(*reinterpret_cast<uint32_t*>(&h3))
-                           : "memory");
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_3d(&tmap_c, stage_box, col0, w.m_blk * kBM + quarter * 32, w.b);
-              tma_store_commit();
-            }
-          };
           tmem_ld_32x32b_x32(taddr, ra);
           tmem_ld_32x32b_x32(taddr + 32, rb);
 #pragma unroll
@@ -616,68 +627,147 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         }
       }
       constexpr int kChunk = BN >= 32 ? 32 : 16;
+      // kChunk columns of this thread's row, rounded once to fp16, straight to global memory (any alignment,
+      // ragged edges, swapped operands)
+      auto store_direct = [&](const uint32_t (&r)[kChunk], int c0) {
+        const int col0 = w.n_blk * BN + c0;  // index on the BN (B side) axis
+        if (col0 >= p.PN || row >= p.PM) return;
+        if (p.swap) {
+          // rows index N of C, columns index M: C[m, n] with m = col, n = row
+          __half* dst = p.C + (int64_t)w.b * p.stride_c + row;
+#pragma unroll
+          for (int jj = 0; jj < kChunk; ++jj)
+            if (col0 + jj < p.PN) dst[(int64_t)(col0 + jj) * p.ldc] = __float2half_rn(__uint_as_float(r[jj]));
+          return;
+        }
+        __half* dst = p.C + (int64_t)w.b * p.stride_c + (int64_t)row * p.ldc + col0;
+        if (vec_ok && col0 + kChunk <= p.PN) {
+#pragma unroll
+          for (int jj = 0; jj < kChunk; jj += 8) {
+            uint4 v;
+            __half2 h0 = __floats2half2_rn(__uint_as_float(r[jj + 0]), __uint_as_float(r[jj + 1]));
+            __half2 h1 = __floats2half2_rn(__uint_as_float(r[jj + 2]), __uint_as_float(r[jj + 3]));
+            __half2 h2 = __floats2half2_rn(__uint_as_float(r[jj + 4]), __uint_as_float(r[jj + 5]));
+            __half2 h3 = __floats2half2_rn(__uint_as_float(r[jj + 6]), __uint_as_float(r[jj + 7]));
+            v.x = *reinterpret_cast<uint32_t*>(&h0);
+            v.y = *reinterpret_cast<uint32_t*>(&h1);
+            v.z = *reinterpret_cast<uint32_t*>(&h2);
+            v.w = *reinterpret_cast<uint32_t*>(&h3);
+            *reinterpret_cast<uint4*>(dst + jj) = v;
+          }
+        } else {
+#pragma unroll
+          for (int jj = 0; jj < kChunk; ++jj)
+            if (col0 + jj < p.PN) dst[jj] = __float2half_rn(__uint_as_float(r[jj]));
+        }
+      };
+      if (w.mode != kOutDirect) {
+        // Part of a tile's K range: the fp32 accumulator (padding included) goes to a slot of kBM x BN
+        // floats.  A slot is lane-major -- the four floats (row, 4j..4j+3) of the 32 rows of a warp lie side
+        // by side -- so every store and every load of a warp covers 512 contiguous bytes.
+        const int64_t slot_idx = w.mode == kOutStreamSlot ? (int64_t)w.aux : (int64_t)w.tile * p.split_k + w.aux;
+        float* slot = p.partial + slot_idx * (kBM * BN) + ((size_t)quarter * (BN / 4) * 32 + lane) * 4;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += kChunk) {
+          uint32_t r[kChunk];
+          if constexpr (kChunk == 32) tmem_ld_32x32b_x32(taddr + c0, r);
+          else tmem_ld_32x32b_x16(taddr + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int jj = 0; jj < kChunk; jj += 4)
+            *reinterpret_cast<float4*>(slot + (size_t)((c0 + jj) / 4) * 128) =
+                make_float4(__uint_as_float(r[jj]), __uint_as_float(r[jj + 1]), __uint_as_float(r[jj + 2]),
+                            __uint_as_float(r[jj + 3]));
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        if (w.mode == kOutSplitSlice) {
+          // The CTA that completes a tile's last K slice adds the slices' slots in slice order (a fixed
+          // order whoever comes last, so the result is deterministic), rounds once and writes C.
+          // The counter needs no clearing: its upper half names the launch that last used it, a stale one
+          // restarts at one arrival, and the CTA that completes a tile leaves the count at zero so that a
+          // replay of the same launch (a CUDA graph) starts afresh.
+          __threadfence();
+          named_bar_sync(kEpiBarrier, 128);
+          if (quarter == 0 && lane == 0) {
+            unsigned long long* ctr = p.counters + w.tile;
+            unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(ctr), want;
+            while (true) {
+              const unsigned int arrivals = (unsigned int)(seen >> 32) == p.epoch ? (unsigned int)seen + 1u : 1u;
+              want = ((unsigned long long)p.epoch << 32) | (arrivals == (unsigned int)p.split_k ? 0u : arrivals);
+              const unsigned long long old = atomicCAS(ctr, seen, want);
+              if (old == seen) { *red_flag = (int)arrivals; break; }
+              seen = old;
+            }
+          }
+          named_bar_sync(kEpiBarrier, 128);
+          if (*red_flag == p.split_k) {
+            __threadfence();
+            const float* slot0 = p.partial + (int64_t)w.tile * p.split_k * (kBM * BN) +
+                                 ((size_t)quarter * (BN / 4) * 32 + lane) * 4;
+            auto sum_chunk = [&](uint32_t (&r)[kChunk], int c0) {
+              float a[kChunk];
+#pragma unroll
+              for (int jj = 0; jj < kChunk; ++jj) a[jj] = 0.0f;
+              // two slices per step, their loads in flight together (the slots sit in L2: latency, not
+              // bandwidth, is what the sum waits for); the adds stay in slice order
+              for (int ks = 0; ks < p.split_k; ks += 2) {
+                const float* s0 = slot0 + (size_t)ks * (kBM * BN);
+                const bool two = ks + 1 < p.split_k;
+                const float* s1 = two ? s0 + kBM * BN : s0;
+                float4 v0[kChunk / 4], v1[kChunk / 4];
+#pragma unroll
+                for (int jj = 0; jj < kChunk; jj += 4) {
+                  v0[jj / 4] = __ldcg(reinterpret_cast<const float4*>(s0 + (size_t)((c0 + jj) / 4) * 128));
+                  v1[jj / 4] = __ldcg(reinterpret_cast<const float4*>(s1 + (size_t)((c0 + jj) / 4) * 128));
+                }
+#pragma unroll
+                for (int jj = 0; jj < kChunk; jj += 4) {
+                  a[jj] += v0[jj / 4].x; a[jj + 1] += v0[jj / 4].y; a[jj + 2] += v0[jj / 4].z; a[jj + 3] += v0[jj / 4].w;
+                  if (two) {
+                    a[jj] += v1[jj / 4].x; a[jj + 1] += v1[jj / 4].y; a[jj + 2] += v1[jj / 4].z; a[jj + 3] += v1[jj / 4].w;
+                  }
+                }
+              }
+#pragma unroll
+              for (int jj = 0; jj < kChunk; ++jj) r[jj] = __float_as_uint(a[jj]);
+            };
+            bool done = false;
+            if constexpr (BN >= 64) {
+              if (p.tma_store) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 64) {
+                  uint32_t lo[32], hi[32];
+                  sum_chunk(lo, c0);
+                  sum_chunk(hi, c0 + 32);
+                  emit(lo, hi, c0);
+                }
+                done = true;
+              }
+            }
+            if (!done) {
+#pragma unroll 1
+              for (int c0 = 0; c0 < BN; c0 += kChunk) {
+                uint32_t r[kChunk];
+                sum_chunk(r, c0);
+                store_direct(r, c0);
+              }
+            }
+          }
+          // the flag is rewritten for the next item only after every thread has read it
+          named_bar_sync(kEpiBarrier, 128);
+        }
+        if (quarter == 0 && lane == 0) trace_mark(p, idx, 5);
+        continue;
+      }
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += kChunk) {
         uint32_t r[kChunk];
         if constexpr (kChunk == 32) tmem_ld_32x32b_x32(taddr + c0, r);
         else tmem_ld_32x32b_x16(taddr + c0, r);
         tmem_ld_wait();
-        const int col0 = w.n_blk * BN + c0;  // index on the BN (B side) axis
-        if (w.mode == kOutStreamSlot) {
-          // whole tile, padding included: the fix-up kernel knows the valid extent
-          float* dst = p.partial + ((int64_t)w.aux * kBM + trow) * BN + c0;
-#pragma unroll
-          for (int jj = 0; jj < kChunk; jj += 4)
-            *reinterpret_cast<float4*>(dst + jj) = make_float4(__uint_as_float(r[jj]), __uint_as_float(r[jj + 1]),
-                                                               __uint_as_float(r[jj + 2]), __uint_as_float(r[jj + 3]));
-        } else if (col0 >= p.PN) {
-          // nothing but padding from here on (warp-uniform)
-        } else if (w.mode == kOutSplitSlice) {
-          if (row < p.PM) {
-            float* dst = p.partial + (((int64_t)w.aux * p.batch + w.b) * p.PM + row) * p.PN + col0;
-            if (col0 + kChunk <= p.PN && (p.PN & 3) == 0) {
-#pragma unroll
-              for (int jj = 0; jj < kChunk; jj += 4)
-                *reinterpret_cast<float4*>(dst + jj) = make_float4(__uint_as_float(r[jj]), __uint_as_float(r[jj + 1]),
-                                                                   __uint_as_float(r[jj + 2]), __uint_as_float(r[jj + 3]));
-            } else {
-#pragma unroll
-              for (int jj = 0; jj < kChunk; ++jj)
-                if (col0 + jj < p.PN) dst[jj] = __uint_as_float(r[jj]);
-            }
-          }
-        } else if (p.swap) {
-          // rows index N of C, columns index M: C[m, n] with m = col, n = row
-          if (row < p.PM) {
-            __half* dst = p.C + (int64_t)w.b * p.stride_c + row;
-#pragma unroll
-            for (int jj = 0; jj < kChunk; ++jj)
-              if (col0 + jj < p.PN) dst[(int64_t)(col0 + jj) * p.ldc] = __float2half_rn(__uint_as_float(r[jj]));
-          }
-        } else {
-          if (row < p.PM) {
-            __half* dst = p.C + (int64_t)w.b * p.stride_c + (int64_t)row * p.ldc + col0;
-            if (vec_ok && col0 + kChunk <= p.PN) {
-#pragma unroll
-              for (int jj = 0; jj < kChunk; jj += 8) {
-                uint4 v;
-                __half2 h0 = __floats2half2_rn(__uint_as_float(r[jj + 0]), __uint_as_float(r[jj + 1]));
-                __half2 h1 = __floats2half2_rn(__uint_as_float(r[jj + 2]), __uint_as_float(r[jj + 3]));
-                __half2 h2 = __floats2half2_rn(__uint_as_float(r[jj + 4]), __uint_as_float(r[jj + 5]));
-                __half2 h3 = __floats2half2_rn(__uint_as_float(r[jj + 6]), __uint_as_float(r[jj + 7]));
-                v.x = *reinterpret_cast<uint32_t*>(&h0);
-                v.y = *reinterpret_cast<uint32_t*>(&h1);
-                v.z = *reinterpret_cast<uint32_t*>(&h2);
-                v.w = *reinterpret_cast<uint32_t*>(&h3);
-                *reinterpret_cast<uint4*>(dst + jj) = v;
-              }
-            } else {
-#pragma unroll
-              for (int jj = 0; jj < kChunk; ++jj)
-                if (col0 + jj < p.PN) dst[jj] = __float2half_rn(__uint_as_float(r[jj]));
-            }
-          }
-        }
+        store_direct(r, c0);
         __syncwarp();
       }
       tc_fence_before_sync();
@@ -708,22 +798,6 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   }
 }
 
-// Sums split-K partials in slice order (deterministic), rounds once, applies swap_ab.
-__global__ void gemm_splitk_reduce_kernel(const float* __restrict__ partial, __half* __restrict__ C, int64_t ldc,
-                                          int64_t stride_c, int PM, int PN, int batch, int split_k, int swap) {
-  const int64_t per = (int64_t)PM * PN;
-  const int64_t total = per * batch;
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    float s = 0.0f;
-    for (int ks = 0; ks < split_k; ++ks) s += partial[(int64_t)ks * total + i];
-    const int b = (int)(i / per);
-    const int64_t rem = i - (int64_t)b * per;
-    const int row = (int)(rem / PN), col = (int)(rem - (int64_t)row * PN);
-    const int64_t o = swap ? (int64_t)col * ldc + row : (int64_t)row * ldc + col;
-    C[(int64_t)b * stride_c + o] = __float2half_rn(s);
-  }
-}
-
 // Stream-K fix-up: one block per dealt-out tile.  A tile whose K slabs were shared by several
 // CTAs is the sum of their fp32 slots, added in CTA order (deterministic) and rounded once.
 // Grid: (blocks per tile, dealt-out tiles); one thread per 4 consecutive columns of a tile row, so
@@ -745,7 +819,9 @@ __global__ void gemm_streamk_fixup_kernel(const GemmParams p, int bn, int grid) 
   for (int c = c_lo; c <= c_hi; ++c) {
     const int first_tile = (c * p.sk_upc) / p.num_kb;
     const int slot = 2 * c + (j == first_tile ? 0 : 1);
-    const float4 v = *reinterpret_cast<const float4*>(p.partial + ((int64_t)slot * kBM + trow) * bn + tcol);
+    // slots are lane-major: the float4 (row, 4j..4j+3) sits at ((row / 32 * (bn / 4) + j) * 32 + row % 32) * 4
+    const float4 v = *reinterpret_cast<const float4*>(
+        p.partial + (int64_t)slot * kBM * bn + ((size_t)((trow >> 5) * (bn >> 2) + (tcol >> 2)) * 32 + (trow & 31)) * 4);
     s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
   }
   const float vals[4] = {s.x, s.y, s.z, s.w};
@@ -1021,6 +1097,26 @@ static void default_config_impl(int M, int N, int K, int batch, int sm_count, bo
       best = dp;
       out->tile_n = bn;
       out->stream_k = 0;
+      out->split_k = 1;
+    }
+    if (tiles < sm_count && num_kb >= 16) {
+      // K cut into S slices, one work item each, summed by the CTA that completes a tile last: pays when a
+      // few tiles leave most SMs idle over a long K.  Overhead measured on 3 x 3 convolutions with 49..98
+      // tiles and on 128 x 4096 x 11008: about 2 us plus (4 + 1.5 S) us per 256 columns of tile width.
+      const int cand[5] = {2, 3, 4, 6, 8};
+      for (int c = 0; c < 5; ++c) {
+        const int S = cand[c];
+        if (num_kb / S < 4) break;
+        const int64_t items = tiles * S;
+        const double t = (double)((items + sm_count - 1) / sm_count) * ((num_kb + S - 1) / S) * slab_us(bn) + 4.0 + 2.0 +
+                         (4.0 + 1.5 * S) * bn / 256.0;
+        if (t < best * 0.93) {   // a workspace and ordered launches only for a clear gain
+          best = t;
+          out->tile_n = bn;
+          out->stream_k = 0;
+          out->split_k = S;
+        }
+      }
     }
     if (tail != 0 && num_kb >= 8) {
       // dealt-out slabs, the fp32 slots' round trip through HBM, and the fix-up launch
@@ -1032,6 +1128,7 @@ static void default_config_impl(int M, int N, int K, int batch, int sm_count, bo
         best = sk;
         out->tile_n = bn;
         out->stream_k = 1;
+        out->split_k = 1;
       }
     }
   }
@@ -1052,6 +1149,7 @@ static void default_config_impl(int M, int N, int K, int batch, int sm_count, bo
         out->cta_group = 2;
         out->tile_n = bn;
         out->stream_k = 0;
+        out->split_k = 1;
         out->stages = gemm_f16_pair_max_stages(bn);
       }
     }
@@ -1098,6 +1196,8 @@ static void streamk_plan(int64_t tiles, int num_kb, int grid, int* dp_rounds, in
   *sk_upc = std::max(1, upc);
 }
 
+static size_t splitk_counter_bytes(int64_t tiles) { return ((size_t)tiles * sizeof(unsigned long long) + 1023) / 1024 * 1024; }
+
 size_t gemm_f16_workspace_bytes(const helix_cfg_t* cfg, int M, int N, int K, int batch, int sm_count) {
   if (!cfg) return 0;
   if (cfg->cta_group == 2) return gemm_f16_pair_workspace_bytes(*cfg, M, N, K, batch, sm_count);
@@ -1110,7 +1210,14 @@ size_t gemm_f16_workspace_bytes(const helix_cfg_t* cfg, int M, int N, int K, int
     return (size_t)2 * grid * kBM * bn * sizeof(float);
   }
   if (cfg->split_k <= 1) return 0;
-  return (size_t)cfg->split_k * std::max(batch, 1) * (size_t)M * N * sizeof(float);
+  // split-K: arrival counters (one per tile, rounded up to 1 KiB), then one kBM x BN fp32 slot per tile and slice
+  const int bn = cfg->tile_n;
+  const int pm = cfg->swap_ab ? N : M, pn = cfg->swap_ab ? M : N;
+  const int64_t tiles = (int64_t)((pm + kBM - 1) / kBM) * ((pn + bn - 1) / bn) * std::max(batch, 1);
+  const int num_kb = std::max(1, (K + kBK - 1) / kBK);
+  const int split = std::min(cfg->split_k, num_kb);
+  if (split <= 1) return 0;
+  return splitk_counter_bytes(tiles) + (size_t)tiles * split * kBM * bn * sizeof(float);
 }
 
 // Timeline capture: while a buffer is set, every one-CTA GEMM / convolution launch whose grid fits
@@ -1195,7 +1302,7 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
   // Never more issuing warps than ring stages: a warp waits on a stage's "empty" barrier by
   // parity, which is only meaningful while it is at most one use of that stage ahead of the
   // consumer; with load_warps <= stages its previous slab guarantees that.
-  p.load_warps = std::max(1, std::min({cfg.load_group > 0 ? cfg.load_group : 2, kGemmProducerWarps,
+  p.load_warps = std::max(1, std::min({cfg.load_group > 0 ? cfg.load_group : 2, kGemmProducerWarps - 1,
                                        p.stages}));
   p.swap = cfg.swap_ab ? 1 : 0;
   p.C = static_cast<__half*>(C);
@@ -1226,9 +1333,15 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
     p.total_items = (int)total;
     grid = (int)std::min<int64_t>(total, sm_count);
     if (p.split_k > 1) {
-      const size_t need = (size_t)p.split_k * p.batch * (size_t)p.PM * p.PN * sizeof(float);
-      if (!ws || ws_bytes < need) return HELIX_ERR_WORKSPACE;
-      p.partial = static_cast<float*>(ws);
+      const size_t cbytes = splitk_counter_bytes(tiles);
+      const size_t need = cbytes + (size_t)tiles * p.split_k * kBM * bn * sizeof(float);
+      if (!ws || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 15)) return HELIX_ERR_WORKSPACE;
+      p.counters = static_cast<unsigned long long*>(ws);
+      p.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + cbytes);
+      // a fresh tag per launch: whatever the counter words hold from other launches (or from no launch at
+      // all) reads as stale, so the workspace needs no clearing
+      static std::atomic<unsigned int> next_epoch{0x5eed0001u};
+      p.epoch = next_epoch.fetch_add(1u);
       reduce = true;
     }
   }
@@ -1273,14 +1386,6 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
 #undef HELIX_BN_CASE
   if (e != cudaSuccess) return HELIX_ERR_CUDA;
   ++*launches;
-  if (reduce) {
-    const int64_t n = (int64_t)p.PM * p.PN * p.batch;
-    const int blocks = (int)std::min<int64_t>((n + 255) / 256, (int64_t)sm_count * 8);
-    gemm_splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p.partial, p.C, ldc, sc, p.PM, p.PN, p.batch, p.split_k,
-                                                         p.swap);
-    if (cudaGetLastError() != cudaSuccess) return HELIX_ERR_CUDA;
-    ++*launches;
-  }
   if (fixup) {
     const dim3 fgrid((kBM * (bn >> 2) + 255) / 256, p.sk_tiles);
     gemm_streamk_fixup_kernel<<<fgrid, 256, 0, stream>>>(p, bn, grid);
@@ -1308,7 +1413,10 @@ int gemm_f16_launch(const helix_cfg_t* cfg_in, const void* A, int64_t lda, const
   } else {
     gemm_f16_default_config(M, N, K, batch, sm_count, false, &cfg);
     // the automatic choice degrades to the workspace-free schedule when no scratch was passed
-    if (!ws || ws_bytes < gemm_f16_workspace_bytes(&cfg, M, N, K, batch, sm_count)) cfg.stream_k = 0;
+    if (!ws || ws_bytes < gemm_f16_workspace_bytes(&cfg, M, N, K, batch, sm_count)) {
+      cfg.stream_k = 0;
+      cfg.split_k = 1;
+    }
   }
   if (cfg.cta_group == 2)   // CTA pairs sharing a 256 x BN tile: its own kernel
     return gemm_f16_pair_launch(cfg, A, lda, B, ldb, C, ldc, M, N, K, batch, sa, sb, sc, ws, ws_bytes, status_dev,
@@ -1366,7 +1474,10 @@ int conv_f16_launch(const helix_cfg_t* cfg_in, const void* x, const void* w, voi
     cfg = *cfg_in;
   } else {
     conv_f16_default_config(g, sm_count, &cfg);
-    if (!ws || ws_bytes < gemm_f16_workspace_bytes(&cfg, M, N, K, 1, sm_count)) cfg.stream_k = 0;
+    if (!ws || ws_bytes < gemm_f16_workspace_bytes(&cfg, M, N, K, 1, sm_count)) {
+      cfg.stream_k = 0;
+      cfg.split_k = 1;
+    }
   }
   if (cfg.tile_m != kBM || cfg.cta_group > 1) return HELIX_ERR_UNSUPPORTED;
   if (cfg.swap_ab) {

@@ -360,8 +360,11 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int row = row0 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
       if (it.slot >= 0) {
-        // part of a tile's K range: the fp32 accumulator (padding included) goes to this pair's slot
-        float* dst = p.partial + ((size_t)it.slot * (2 * kBM) + rank * kBM + quarter * 32 + lane) * BN;
+        // part of a tile's K range: the fp32 accumulator (padding included) goes to this pair's slot of
+        // 256 x BN floats, stored lane-major (the four floats (row, 4j..4j+3) of a warp's 32 rows side by side),
+        // so that every store of a warp covers 512 contiguous bytes
+        float* dst = p.partial + (size_t)it.slot * (2 * kBM) * BN +
+                     ((size_t)(rank * 4 + quarter) * (BN / 4) * 32 + lane) * 4;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
           uint32_t r[32];
@@ -369,8 +372,9 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           tmem_ld_wait();
 #pragma unroll
           for (int jj = 0; jj < 32; jj += 4)
-            *reinterpret_cast<float4*>(dst + c0 + jj) = make_float4(__uint_as_float(r[jj]), __uint_as_float(r[jj + 1]),
-                                                                    __uint_as_float(r[jj + 2]), __uint_as_float(r[jj + 3]));
+            *reinterpret_cast<float4*>(dst + (size_t)((c0 + jj) / 4) * 128) =
+                make_float4(__uint_as_float(r[jj]), __uint_as_float(r[jj + 1]), __uint_as_float(r[jj + 2]),
+                            __uint_as_float(r[jj + 3]));
         }
         tc_fence_before_sync();
         __syncwarp();
@@ -501,7 +505,8 @@ __global__ void gemm2_streamk_fixup_kernel(const Gemm2Params p, int bn, int num_
   for (int c = c_lo; c <= c_hi; ++c) {
     const int first_tile = (c * p.sk_upc) / p.num_kb;
     const int slot = 2 * c + (j == first_tile ? 0 : 1);
-    const float4 v = *reinterpret_cast<const float4*>(p.partial + ((size_t)slot * (2 * kBM) + trow) * bn + tcol);
+    const float4 v = *reinterpret_cast<const float4*>(
+        p.partial + (size_t)slot * (2 * kBM) * bn + ((size_t)((trow >> 5) * (bn >> 2) + (tcol >> 2)) * 32 + (trow & 31)) * 4);
     s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
   }
   const float vals[4] = {s.x, s.y, s.z, s.w};

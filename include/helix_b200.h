@@ -77,13 +77,15 @@ typedef struct helix_cfg {
   int tile_k;    /* K slab per stage (GEMM_F16/CONV: 64; GEMM_F32: 8 or 16)          */
   int stages;    /* shared-memory ring depth (0 = as many as fit)                    */
   int cta_group; /* 1 = one CTA per tile, 2 = CTA pair sharing one 256-row tile      */
-  int split_k;   /* >= 1; > 1 needs a workspace                                      */
+  int split_k;   /* >= 1; > 1 needs a workspace (it needs no clearing: the arrival counters in it are
+                    tagged per launch); the K slices of a tile are summed in slice order by the CTA
+                    that completes the tile last                                        */
   int swap_ab;   /* 1 = put N on the 128-row UMMA axis (skinny M)                    */
   int raster;    /* M-blocks per rasterisation group (L2 reuse), 0 = default         */
   int thread_m;  /* GEMM_F32: per-thread register block rows                         */
   int thread_n;  /* GEMM_F32: per-thread register block cols                         */
   int load_group;/* GEMM_F16/CONV: warps per CTA that issue TMA loads, consecutive K slabs going to
-                    different warps (0 = 2; at most 4, 3 for CTA pairs, never more than stages);
+                    different warps (0 = 2; at most 3, never more than stages);
                     GEMV_F16: 16-byte loads in flight per thread and row (0 = default)  */
   int stream_k;  /* GEMM_F16/CONV: 1 = whole waves of tiles round-robin, the K slabs of the
                     remaining tiles dealt evenly to all CTAs or CTA pairs (needs a workspace);

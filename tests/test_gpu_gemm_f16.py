@@ -82,6 +82,51 @@ def test_gemm_split_k(oracle, split, swap):
     util.assert_f16_close(got, ref32, f"split_k={split} swap={swap}")
 
 
+def test_gemm_split_k_needs_no_clean_workspace_and_replays_from_a_graph(oracle):
+    """The split-K arrival counters are tagged per launch and left at zero by the CTA that completes a tile:
+    a workspace full of garbage works, several tiles per CTA and ragged edges work, the slices are summed in
+    slice order whoever arrives last (same bits every time), and a captured launch can be replayed."""
+    M, N, K = 1000, 520, 4096          # 8 x 3 tiles of 128 x 256 (ragged), 64 K slabs cut in 5
+    a, b = datagen.c3_gemm(M, N, K, seed=14)
+    ad, bd = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    cfg = _cfg(256, split_k=5)
+    out = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    l = ops.launch_gemm_f16(ad, bd, out, cfg)
+    ws = torch.randint(0, 255, (l.ws_bytes,), dtype=torch.uint8, device="cuda")     # garbage, counters included
+    ws[:4096] = 0xFF
+    l = ops.launch_gemm_f16(ad, bd, out, cfg, ws=ws)
+    ops.run(l)
+    torch.cuda.synchronize()
+    ops.check_status()
+    first = out.clone()
+    _, ref32 = oracle.hgemm_fast(a, b)
+    util.assert_f16_close(first.cpu().numpy(), ref32, "split-K on a dirty workspace")
+    for _ in range(3):
+        out.zero_()
+        ops.run(l)
+        torch.cuda.synchronize()
+        assert torch.equal(out, first)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        ops.run(l)
+        ops.run(l)
+    for _ in range(3):
+        out.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, first)
+    ops.check_status()
+    # a narrow tile without the TMA store path (N not a multiple of 8) and a batch
+    a2, b2 = datagen.c3_gemm(300, 100, 1024, seed=15, batch=3)
+    got = _run(a2, b2, _cfg(64, split_k=4))
+    for i in range(3):
+        _, r = oracle.hgemm_naive(a2[i], b2[i])
+        util.assert_f16_close(got[i], r, f"batched split-K entry {i}")
+    a3, b3 = datagen.c3_gemm(200, 97, 1024 + 8, seed=16)
+    _, r3 = oracle.hgemm_naive(a3, b3)
+    util.assert_f16_close(_run(a3, b3, _cfg(32, split_k=3)), r3, "split-K, N = 97")
+
+
 def test_gemm_many_tiles_persistent_and_stage_wrap(oracle):
     """More tiles than SMs and more K slabs than stages: several accumulator and ring phases."""
     M, N, K = 2048, 2304, 1024
