@@ -80,7 +80,6 @@ struct GemmParams {
   int sk_tiles;    // tiles whose K slabs are dealt out
   int sk_upc;      // K slabs per CTA in the dealt part (<= num_kb, so a range touches <= 2 tiles)
   int tma_store;   // whole tiles leave through shared memory and a TMA store (tmap_c is valid)
-  int swap_fast;   // swap: tiles are transposed through shared memory and leave as 16-byte stores
   int independent; // nothing read or written here is written by the kernel queued just before
   int probe;       // tuning instrument (helix_cfg_t.probe): 1 = issue no MMA, 2 = no A loads, 4 = no B loads
   int group;       // ring stages that share one "full" barrier (see the MMA issuer); stages is a multiple of it
@@ -581,42 +580,38 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         }
       }
       if constexpr (BN >= 32) {
-        if (p.swap && p.swap_fast && w.mode == kOutDirect) {
-          // Swapped operands: TMEM lanes index columns of C's memory rows (C[col][row]).  32 tile
-          // columns at a time are converted and transposed through shared memory ([32 cols][128
-          // rows] fp16, two buffers alternating), then leave as 16-byte stores along the
-          // contiguous axis of C: each thread writes whole 8-element segments.
-          const int m0 = w.m_blk * kBM;
-          __half* cbase = p.C + (int64_t)w.b * p.stride_c;
-          const int t = quarter * 32 + lane;
-#pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (p.swap && w.mode == kOutDirect) {
+          // Swapped operands: TMEM lanes index the contiguous axis of C (C[col][row]: for a convolution the
+          // output channels of one pixel).  A warp holds 32 consecutive rows of every tile column, so one
+          // 2-byte store per lane writes 64 contiguous bytes of one C row: no transposition through shared
+          // memory, 32 store instructions per 32 columns, the TMEM load of the next 32 columns in flight
+          // meanwhile.  (A staged transposition with 16-byte stores took 3.7-4.6 us per 128 x 256 tile.)
+          __half* const cb = p.C + (int64_t)w.b * p.stride_c + row;
+          const bool row_ok = row < p.PM;
+          uint32_t r0[32], r1[32];
+          auto put = [&](const uint32_t (&r)[32], int c0) {
             const int col0 = w.n_blk * BN + c0;
-            if (col0 >= p.PN) break;   // uniform over the four warps: padding columns only
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(taddr + c0, r);
+            if (!row_ok || col0 >= p.PN) return;
+            __half* dst = cb + (int64_t)col0 * p.ldc;
+            if (col0 + 32 <= p.PN) {
+#pragma unroll
+              for (int jj = 0; jj < 32; ++jj) dst[(int64_t)jj * p.ldc] = __float2half_rn(__uint_as_float(r[jj]));
+            } else {
+#pragma unroll
+              for (int jj = 0; jj < 32; ++jj)
+                if (col0 + jj < p.PN) dst[(int64_t)jj * p.ldc] = __float2half_rn(__uint_as_float(r[jj]));
+            }
+          };
+          tmem_ld_32x32b_x32(taddr, r0);
+#pragma unroll
+          for (int c0 = 0; c0 < BN; c0 += 64) {
             tmem_ld_wait();
-            __half* stg = reinterpret_cast<__half*>(sC + box * 8192);
-            box ^= 1;
-#pragma unroll
-            for (int jj = 0; jj < 32; ++jj) stg[jj * kBM + trow] = __float2half_rn(__uint_as_float(r[jj]));
-            named_bar_sync(kEpiBarrier, 128);
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              const int q = v * 128 + t;
-              const int cj = q >> 4, seg = q & 15;
-              const int col = col0 + cj, rw = m0 + seg * 8;
-              if (col < p.PN && rw < p.PM) {
-                const uint4 val = *reinterpret_cast<const uint4*>(stg + cj * kBM + seg * 8);
-                __half* dst = cbase + (int64_t)col * p.ldc + rw;
-                if (rw + 8 <= p.PM) {
-                  *reinterpret_cast<uint4*>(dst) = val;
-                } else {
-                  const __half* hv = reinterpret_cast<const __half*>(&val);
-                  for (int e = 0; e < 8; ++e)
-                    if (rw + e < p.PM) dst[e] = hv[e];
-                }
-              }
+            if (c0 + 32 < BN) tmem_ld_32x32b_x32(taddr + c0 + 32, r1);
+            put(r0, c0);
+            if (c0 + 32 < BN) {
+              tmem_ld_wait();
+              if (c0 + 64 < BN) tmem_ld_32x32b_x32(taddr + c0 + 64, r0);
+              put(r1, c0 + 32);
             }
           }
           tc_fence_before_sync();
@@ -1353,8 +1348,6 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
   if (!p.swap && bn >= 64 && (ldc & 7) == 0 && (sc & 7) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
       make_tmap(&tc, C, p.PN, p.PM, p.batch, ldc, sc, 32) == HELIX_OK)
     p.tma_store = 1;
-  // swapped output: 16-byte stores along C's contiguous axis need aligned rows
-  p.swap_fast = (p.swap && bn >= 32 && (ldc & 7) == 0 && (sc & 7) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
   // a launch that shares its workspace with its neighbours on the stream is never independent of them
   p.independent = (independent && !fixup && !reduce) ? 1 : 0;
   p.fd_per_batch = make_fastdiv(p.tiles_m * p.tiles_n);

@@ -329,3 +329,48 @@ def test_gemm_independent_launch_chain_matches_ordered(oracle):
     for o in outs:
         util.assert_f16_close(o.cpu().numpy(), ref32, "independent chain")
     assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[3])
+
+
+def test_an_independent_launch_does_not_break_the_order_of_its_neighbours(oracle):
+    """A (long) -> B (short, flagged HELIX_LAUNCH_INDEPENDENT, unrelated buffers) -> C (ordered, reads A's
+    output).  B does not wait for A before it works, but it waits before it exits, so C -- which waits for B --
+    never starts reading A's output while A still writes it."""
+    from helix_b200._lib import LAUNCH_INDEPENDENT
+    a1, b1 = datagen.c3_gemm(256, 512, 8192, seed=31)          # A: 2 x 2 tiles, 128 K slabs each
+    _, b2 = datagen.c3_gemm(8, 384, 512, seed=32)
+    a3, b3 = datagen.c3_gemm(128, 128, 64, seed=33)            # B: one tile, one slab
+    d = [torch.from_numpy(x).cuda() for x in (a1, b1, b2, a3, b3)]
+    c1 = torch.zeros((256, 512), dtype=torch.float16, device="cuda")
+    c2 = torch.zeros((256, 384), dtype=torch.float16, device="cuda")
+    c3 = torch.zeros((128, 128), dtype=torch.float16, device="cuda")
+    la = ops.launch_gemm_f16(d[0], d[1], c1, _cfg(256))
+    lc = ops.launch_gemm_f16(c1, d[2], c2, _cfg(128))
+    lb = ops.launch_gemm_f16(d[3], d[4], c3, _cfg(128))
+    lb.flags = LAUNCH_INDEPENDENT
+    ops.run(la)
+    torch.cuda.synchronize()
+    ops.run(lc)
+    torch.cuda.synchronize()
+    want = c2.clone()                                          # the chain with a host synchronisation in between
+    _, ref1 = oracle.hgemm_naive(a1, b1)
+    util.assert_f16_close(c1.cpu().numpy(), ref1, "first product")
+    _, ref2 = oracle.hgemm_naive(c1.cpu().numpy(), b2)
+    util.assert_f16_close(want.cpu().numpy(), ref2, "second product")
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        ops.run(la)
+        ops.run(lb)
+        ops.run(lc)
+    for trial in range(20):
+        c1.zero_()
+        c2.zero_()
+        torch.cuda.synchronize()
+        if trial % 2:
+            g.replay()
+        else:
+            ops.run(la)
+            ops.run(lb)
+            ops.run(lc)
+        torch.cuda.synchronize()
+        assert torch.equal(c2, want), trial
+    ops.check_status()
