@@ -70,6 +70,7 @@ int gemm_f16_pair_launch(const helix_cfg_t& cfg, const void* A, int64_t lda, con
                          int64_t* launches);
 // ---- conv_f16_halo.cu (stride-1 convolution with the input window resident in shared memory)
 bool conv_f16_halo_eligible(const ConvGeom& g, const helix_cfg_t* cfg);
+double conv_f16_halo_estimate_us(const ConvGeom& g, int sm_count);   // < 0: geometry not covered
 int conv_f16_halo_launch(const helix_cfg_t* cfg, const void* x, const void* w, void* y, const ConvGeom& g,
                          int* status_dev, int sm_count, bool independent, cudaStream_t stream, int64_t* launches);
 int conv_f16_launch(const helix_cfg_t* cfg, const void* x, const void* w, void* y, const ConvGeom& g, void* ws,

@@ -160,7 +160,7 @@ def test_conv_window_resident_kernel(oracle, geom):
 ])
 def test_conv_pixels_on_wide_axis(oracle, geom, bn):
     """swap_ab for convolutions: output channels on the 128-row axis of the tile, bn pixels per im2col box
-    on the other; the tile leaves transposed through shared memory."""
+    on the other; each warp store writes 32 consecutive channels of one pixel."""
     B, C, H, W, OC, kh, kw, stride, pad = geom
     x, w = datagen.c4_conv(*geom, seed=29)
     got = _run(x, w, stride, pad, ops.make_cfg(OP_CONV_F16, tile_m=128, tile_n=bn, tile_k=64, swap_ab=1))
