@@ -662,8 +662,11 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         // by side -- so every store and every load of a warp covers 512 contiguous bytes.
         const int64_t slot_idx = w.mode == kOutStreamSlot ? (int64_t)w.aux : (int64_t)w.tile * p.split_k + w.aux;
         float* slot = p.partial + slot_idx * (kBM * BN) + ((size_t)quarter * (BN / 4) * 32 + lane) * 4;
+        // A warp whose 32 rows all lie beyond the matrix (M = 16: three of the four) has nothing to add to a
+        // split-K sum: it neither stores nor sums its part of the slots.
+        const bool live = w.mode != kOutSplitSlice || w.m_blk * kBM + quarter * 32 < p.PM;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += kChunk) {
+        for (int c0 = 0; live && c0 < BN; c0 += kChunk) {
           uint32_t r[kChunk];
           if constexpr (kChunk == 32) tmem_ld_32x32b_x32(taddr + c0, r);
           else tmem_ld_32x32b_x16(taddr + c0, r);
@@ -697,7 +700,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             }
           }
           named_bar_sync(kEpiBarrier, 128);
-          if (*red_flag == p.split_k) {
+          if (*red_flag == p.split_k && live) {
             __threadfence();
             const float* slot0 = p.partial + (int64_t)w.tile * p.split_k * (kBM * BN) +
                                  ((size_t)quarter * (BN / 4) * 32 + lane) * 4;
