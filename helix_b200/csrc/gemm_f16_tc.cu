@@ -1052,26 +1052,39 @@ static void default_config_impl(int M, int N, int K, int batch, int sm_count, bo
   out->split_k = 1;
   out->load_group = 2;   // measured: two issuing warps keep the ring full, more add nothing
   const int num_kb = (K + kBK - 1) / kBK;
-  // One row block of A (M <= 128) against a long weight matrix streams B from HBM once and is
-  // memory bound: the 16 KiB A box only carries M rows (rows beyond M are never fetched), so the
-  // widest tile moves the most bytes per tensor copy.  Measured on 8..128 x 4096..11008 x
-  // 4096..11008: about 5.3 TB/s once enough CTAs stream, 0.4 TB/s per CTA below that, and
-  // neither swap_ab, split-K nor stream-K does better.
+  // One row block of A (M <= 128) against a long weight matrix streams B from HBM once and is memory bound.
+  // What a lone launch achieves is set by the bytes it keeps in flight: a CTA holds `stages` slabs in its ring and
+  // HBM answers a slab about 1.8 us after the request under load (measured: 128 x 4096 x 11008 on 16 CTAs of
+  // 128 x 256 tiles streams at 1.3 TB/s, 73 us), so the choice spreads the stream over as many CTAs as pay for the
+  // split-K sum (2 us plus (4 + 1.5 S) us per 256 columns, for the row quarters that hold rows of C).  Measured
+  // lone launches: 16 x 11008 x 4096 31 -> 24 us, 128 x 4096 x 11008 73 -> 29 us, 64 x 4096 x 4096 25 -> 16 us.
+  // (Launches on distinct buffers that overlap on idle SMs do best with the widest tile and no split: 16-18 us.)
   if (!conv && M <= kBM && N >= 1024 && num_kb >= 8) {
-    const double bytes = 2.0 * batch * ((double)M * K + (double)N * K + (double)M * N);
+    const double b_bytes = 2.0 * batch * (double)N * K, a_bytes = 2.0 * batch * (double)M * K;
+    const double live = std::min(4, (std::min(M, kBM) + 31) / 32) / 4.0;
     double best_t = 1e30;
-    const int widths[2] = {256, 128};
-    for (int i = 0; i < 2; ++i) {
+    const int widths[3] = {256, 128, 64};
+    const int splits[5] = {1, 2, 3, 4, 6};
+    for (int i = 0; i < 3; ++i) {
       const int bn = widths[i];
       const int64_t tiles = (int64_t)((N + bn - 1) / bn) * batch;
-      const int64_t rounds = (tiles + sm_count - 1) / sm_count;
-      // HBM time of the whole problem against the time one CTA needs for its own slabs at the
-      // rate a single SM takes boxes in (about 0.4 TB/s with two issuing warps)
+      const int stages = max_stages(bn, false);
       const double slab_bytes = (double)(std::min(M, kBM) + bn) * kBK * 2;
-      const double t = std::max(bytes / 5.3e6, (double)rounds * num_kb * slab_bytes / 0.4e6) + 2.5;
-      if (t < best_t * 0.97) {   // ties go to the wider tile
-        best_t = t;
-        out->tile_n = bn;
+      const double cta_rate = std::min(180e3, stages * slab_bytes / 1.8);   // bytes per us
+      for (int c = 0; c < 5; ++c) {
+        const int S = splits[c];
+        if (S > 1 && (tiles * S > sm_count || num_kb / S < 8)) break;
+        const int64_t ctas = std::min<int64_t>(tiles * S, sm_count);
+        const int64_t rounds = (tiles * S + sm_count - 1) / sm_count;
+        // every CTA re-reads its K range of A (from L2); B comes from HBM once
+        const double in_flight_bound = (b_bytes + a_bytes * (double)((N + bn - 1) / bn)) / (ctas * cta_rate) * rounds;
+        const double t = std::max(in_flight_bound, (a_bytes + b_bytes) / 5.5e6) + 6.0 +
+                         (S > 1 ? 2.0 + (4.0 + 1.5 * S) * bn / 256.0 * live : 0.0);
+        if (t < best_t * (S > 1 ? 0.95 : 0.999)) {   // ties go to the wider tile and the smaller split
+          best_t = t;
+          out->tile_n = bn;
+          out->split_k = S;
+        }
       }
     }
     out->swap_ab = 0;

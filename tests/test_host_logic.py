@@ -368,3 +368,25 @@ def test_kernel_exe_prints_the_reference_result_line():
     cb = kernel_exe.cublas_line(16, 32, 64, 0.5, 1.25)
     assert float(cb.split()[-4]) == 0.5 and float(cb.split()[-2]) == 1.25      # cublas_f16.cu:101 token positions
     assert kernel_exe.main(["gemm", "1", "2"]) == 2
+
+
+def test_legacy_port_restates_the_references_pick():
+    """oracle/legacy_port.py: executable names <-> dictionary keys, and the reference's cost model
+    (scripts/Ampere_FP16/Ampere_FP16_gemm.py:420-430): waves of 108 blocks x probe time, K ignored."""
+    from oracle import legacy_port as lp
+    assert lp.exe_key("gemm_4_128_256_64_64") == (4, 128, 256, 64, 64, 0)
+    assert lp.exe_key("gemm_splitK_3_64_64_32_32") == (3, 64, 64, 32, 32, 1)
+    assert lp.exe_key("gemv") == (0, 1, 128, 0, 0, 0) and lp.exe_key("gemv_splitK") == (0, 1, 128, 0, 0, 1)
+    assert lp.exe_key("sgemm_128_128_8_8_8_4_4_4") is None and lp.exe_key("im2col") is None
+    for name in ("gemm_4_128_256_64_64", "gemm_splitK_3_64_64_32_32", "gemv", "gemv_splitK"):
+        assert lp.exe_name(lp.exe_key(name)) == name
+    prof = {(3, 128, 128, 64, 64, 0): 1.0e-4, (3, 256, 128, 64, 64, 0): 1.7e-4, (3, 128, 128, 64, 64, 1): 0.6e-4,
+            (0, 1, 128, 0, 0, 0): 2.0e-6}
+    # 4096^2 outputs: 1024 tiles of 128x128 = 10 waves x 1.0e-4; 512 tiles of 256x128 = 5 waves x 1.7e-4 (the pick);
+    # split-K doubles the blocks: 19 waves x 0.6e-4; the GEMV key: 4096 * 32 blocks
+    assert lp.reference_cost_model(prof, 4096, 4096, 4096) == (3, 256, 128, 64, 64, 0)
+    assert lp.reference_cost_model(prof, 4096, 4096, 64) == (3, 256, 128, 64, 64, 0)      # K plays no part
+    assert lp.reference_cost_model(prof, 1, 4096, 4096) == (0, 1, 128, 0, 0, 0)           # one row: 32 blocks, 1 wave
+    assert lp.reference_cost_model(prof, 128, 128, 4096) == (0, 1, 128, 0, 0, 0)           # 128 GEMV blocks: 2 waves x 2 us
+    del prof[(0, 1, 128, 0, 0, 0)]
+    assert lp.reference_cost_model(prof, 128, 128, 4096) == (3, 128, 128, 64, 64, 1)      # one wave each: cheapest probe
