@@ -142,11 +142,16 @@ size_t gemv_f16_workspace_bytes(int rows, int m, int split_k) {
 }
 
 int gemv_f16_default_split(int rows, int K, int sm_count) {
-  // Cut K only when there are too few rows to give every SM a few warps: the partials cost a
-  // second launch and forbid overlapping with the neighbouring launches.
+  // Cut K only when there are too few rows to keep enough bytes in flight: a warp holds 4 KiB of loads, and
+  // the stream needs some 24 warps per SM before HBM saturates (512 rows x 500 000: split 4 reads at 2.9 TB/s,
+  // split 16 at 6.5).  The partials cost a second launch and forbid overlapping with the neighbouring
+  // launches, so beyond four warps per SM only very long rows are cut.
   const int groups = (rows + 1) / 2;
   int split = 1;
-  while (split < 16 && (int64_t)groups * split < (int64_t)sm_count * 4 && K / (split * 2) >= 2048) split *= 2;
+  while (split < 16 && K / (split * 2) >= 2048 &&
+         ((int64_t)groups * split < (int64_t)sm_count * 4 ||
+          ((int64_t)groups * split < (int64_t)sm_count * 24 && K / (split * 2) >= 16384)))
+    split *= 2;
   return split;
 }
 

@@ -114,7 +114,11 @@ size_t gemv_f32_workspace_bytes(int rows, int m, int split_k) {
 int gemv_f32_default_split(int rows, int K, int sm_count) {
   const int groups = (rows + 1) / 2;
   int split = 1;
-  while (split < 16 && (int64_t)groups * split < (int64_t)sm_count * 4 && K / (split * 2) >= 1024) split *= 2;
+  // as the fp16 kernel: beyond four warps per SM only very long rows are cut
+  while (split < 16 && K / (split * 2) >= 1024 &&
+         ((int64_t)groups * split < (int64_t)sm_count * 4 ||
+          ((int64_t)groups * split < (int64_t)sm_count * 24 && K / (split * 2) >= 8192)))
+    split *= 2;
   return split;
 }
 

@@ -31,25 +31,48 @@ def require_gpu():
         raise RuntimeError("the Helix B200 backends need a CUDA device; there is no CPU fallback")
 
 
-def key_to_cfg(key, conv=False):
-    """Dictionary key -> library configuration."""
+def key_to_cfg(key, conv=False, prof_dict=None):
+    """Dictionary key -> library configuration.  With the profiled dictionary at hand, the number of
+    TMA-issuing warps is the one the profile found fastest for the tile width (("load_group", bn))."""
     if key[0] == 0:
         return ops.make_cfg(OP_GEMV_F16, tile_m=1, tile_n=key[2], tile_k=256, split_k=key[5], load_group=key[3])
     stages, tm, bn, group, swap, mode = key
+    split = mode if mode in costmodel.SPLIT_MODES else 1
+    lg = int((prof_dict or {}).get(("load_group", bn), 0)) if group == 1 else 0
     return ops.make_cfg(OP_CONV_F16 if conv else OP_GEMM_F16, tile_m=tm, tile_n=bn, tile_k=costmodel.TILE_K,
-                        stages=0, cta_group=group, swap_ab=swap, stream_k=mode, load_group=0)
+                        stages=0, cta_group=group, swap_ab=swap, stream_k=(1 if mode == 1 else 0), split_k=split,
+                        load_group=lg)
+
+
+def overlaps(M, N, K, batch=None):
+    """True where time_gemm_f16 rotates operand sets and flags its launches independent, i.e. measures the
+    throughput of overlapping launches rather than one launch's latency: the protocol flag the cost model
+    takes from its caller."""
+    b = batch or 1
+    return 2.0 * b * M * N * K / (2.0 * b * (M * K + N * K + M * N)) <= costmodel.ROTATE_INTENSITY
+
+
+def cost_model(prof_dict, M, N, K, batch=None, conv=False):
+    """costmodel.cost_model for a shape that this harness is going to time (its protocol passed along)."""
+    return costmodel.cost_model(prof_dict, M, N, K, batch or 1, conv, overlapped=overlaps(M, N, K, batch))
+
+
+def predicted_time(prof_dict, key, M, N, K, batch=None, conv=False):
+    return costmodel.predicted_time(prof_dict, key, M, N, K, batch or 1, conv, overlapped=overlaps(M, N, K, batch))
 
 
 def _randn(shape, scale):
     return torch.randn(shape, device="cuda", dtype=torch.float16) * scale
 
 
-def time_gemm_f16(M, N, K, cfg=None, batch=None, iters=20):
-    """Seconds per launch of the fp16 GEMM; operands rotate through > 2x L2 when the shape is memory-bound."""
+def time_gemm_f16(M, N, K, cfg=None, batch=None, iters=20, lone=False):
+    """Seconds per launch of the fp16 GEMM; operands rotate through > 2x L2 when the shape is memory-bound
+    (launches on distinct buffer sets, flagged independent, overlap).  lone=True: one buffer set, every launch
+    waiting for its predecessor -- what a caller's single call sees."""
     b = batch or 1
     bytes_ = 2.0 * b * (M * K + N * K + M * N)
     flops = 2.0 * b * M * N * K
-    nbuf = 1 if flops / bytes_ > costmodel.ROTATE_INTENSITY else int(ROTATE_BYTES // bytes_) + 1
+    nbuf = 1 if (lone or flops / bytes_ > costmodel.ROTATE_INTENSITY) else int(ROTATE_BYTES // bytes_) + 1
     sa, sb, sc = ((M, K), (N, K), (M, N)) if batch is None else ((b, M, K), (b, N, K), (b, M, N))
     s = 1.0 / math.sqrt(K)
     bufs = [(_randn(sa, s), _randn(sb, s), torch.empty(sc, device="cuda", dtype=torch.float16)) for _ in range(nbuf)]
@@ -180,6 +203,9 @@ def profile_fp16(fast=False, progress=None):
         for swap in (0, 1):
             for mode in (0, 1):
                 d[(costmodel.max_stages(bn), 128, bn, 1, swap, mode)] = tuple(float(v) for v in val)
+        if bn >= 64:
+            for split in costmodel.SPLIT_MODES:      # same slab figures; the sum's cost is ("splitk_overhead", bn)
+                d[(costmodel.max_stages(bn), 128, bn, 1, 0, split)] = tuple(float(v) for v in val)
     # stream-K: measured excess over the slab model on a half-wave problem
     for bn in wide:
         M, N, K = 128 * (sms // 2), bn, 4096
@@ -197,6 +223,43 @@ def profile_fp16(fast=False, progress=None):
         d[("conv_slab", bn)] = _two_point(t1, waves * 9, t2, waves * 36)[1]
     if fast:
         d[("conv_slab", 128)] = 0.5 * (d[("conv_slab", 64)] + d[("conv_slab", 256)])
+    # swapped convolution tiles (output channels on the 128 rows, bn pixels per im2col box): slope per slab on
+    # 128 output channels, 28 x 28, batch 32 (25088 pixels)
+    for bn in ((256,) if fast else (256, 128)):
+        ccfg = ops.make_cfg(OP_CONV_F16, 128, bn, 64, swap_ab=1)
+        waves = -(-(-(-25088 // bn)) // sms)
+        t1 = time_conv_f16(32, 64, 28, 28, 128, 3, 3, 1, 1, ccfg); tick()
+        t2 = time_conv_f16(32, 256, 28, 28, 128, 3, 3, 1, 1, ccfg); tick()
+        d[("conv_slab_swap", bn)] = _two_point(t1, waves * 9, t2, waves * 36)[1]
+    # split-K: what the slot round trip and the last arriver's sum add, from two slice counts on a quarter-wave
+    # problem: t - (fixed + slabs * slab) = a + b * S
+    for bn in wide:
+        M, N, K = 128 * (sms // 4), bn, 4096
+        tf, ts = measured[bn]
+        over = {}
+        for S in (2, 4):
+            c = ops.make_cfg(OP_GEMM_F16, 128, bn, 64, split_k=S)
+            over[S] = time_gemm_f16(M, N, K, c) - (tf + (64 // S) * ts); tick()
+        b = max((over[4] - over[2]) / 2.0, 0.0)
+        d[("splitk_overhead", bn)] = (float(max(over[2] - 2.0 * b, 1e-6)), float(b))
+    if fast:
+        d[("splitk_overhead", 128)] = tuple(0.5 * (x + y) for x, y in zip(d[("splitk_overhead", 64)], d[("splitk_overhead", 256)]))
+    # search over the fields the key does not carry: TMA-issuing warps per CTA (load_group 1..3) on a tensor-bound
+    # probe, kept per tile width and applied by key_to_cfg; ring depth on the same probe (recorded: the deepest ring
+    # that fits is never slower, which is why the key space holds one depth per width)
+    if not fast:
+        for bn in wide:
+            best = None
+            for lg in (1, 2, 3):
+                t = time_gemm_f16(4096, 4096, 1024, ops.make_cfg(OP_GEMM_F16, 128, bn, 64, load_group=lg)); tick()
+                d[("load_group_probe", bn, lg)] = float(t)
+                if best is None or t < best[1] * 0.99:
+                    best = (lg, t)
+            d[("load_group", bn)] = best[0]
+            smax = costmodel.max_stages(bn)
+            for st in sorted({2, max(2, smax // 2), smax}):
+                t = time_gemm_f16(4096, 4096, 1024, ops.make_cfg(OP_GEMM_F16, 128, bn, 64, stages=st)); tick()
+                d[("stages_probe", bn, st)] = float(t)
     # GEMV: fixed cost and seconds per streamed byte for each variant
     variants = costmodel.GEMV_VARIANTS[:1] if fast else costmodel.GEMV_VARIANTS
     best_rate = 0.0
@@ -245,7 +308,7 @@ def gemm_f16_result(prof_dict, M, N, K, batch=None):
     """(cost_ms, tflops) of the predicted-best configuration, the contract of
     get_Ampere_FP16_gemm_Helix_result (Ampere_FP16_gemm.py:432-441, cuda branch: milliseconds)."""
     require_gpu()
-    key = costmodel.cost_model(prof_dict, M, N, K, batch or 1)
+    key = cost_model(prof_dict, M, N, K, batch)
     if key is None:
         raise RuntimeError("empty cost-model dictionary: run profile_template.py first")
     if key[0] == 0:
@@ -254,7 +317,7 @@ def gemm_f16_result(prof_dict, M, N, K, batch=None):
         t = time_gemv_f16(rows, Kp, m, key_to_cfg(key), transposed)
     else:
         Kp = (K + 7) // 8 * 8      # leading dimensions follow the 16-byte rule; the padding columns are zero work
-        t = time_gemm_f16(M, N, Kp, key_to_cfg(key), batch)
+        t = time_gemm_f16(M, N, Kp, key_to_cfg(key, prof_dict=prof_dict), batch)
     cost_ms = t * 1e3
     return cost_ms, 2.0 * M * N * K * (batch or 1) / 1e9 / cost_ms
 
@@ -302,10 +365,14 @@ def conv_f16_result(prof_dict, batch, IC, H, W, OC, kH, kW, stride, pad):
     Ho, Wo = ops.conv_out_hw(H, W, kH, kW, stride, pad)
     M, N, K = batch * Ho * Wo, OC, IC * kH * kW
     as_gemm = kH == 1 and kW == 1 and stride == 1 and pad == 0
-    key = costmodel.cost_model(prof_dict, M, N, (K + 7) // 8 * 8, 1, conv=not as_gemm)
+    C = (IC + 7) // 8 * 8
+    im2col = C % 64 == 0 and batch * H * W * C * 2 >= 131072 and stride <= 8      # the library's tensor-map rule
+    # the convolution harness times one buffer set with ordered launches: a lone launch
+    key = costmodel.cost_model(prof_dict, M, N, (K + 7) // 8 * 8, 1,
+                               conv=False if as_gemm else ("im2col" if im2col else True))
     if key is None or key[0] == 0:
         key = (costmodel.max_stages(128), 128, 128, 1, 0, 0)
-    t = time_conv_f16(batch, IC, H, W, OC, kH, kW, stride, pad, key_to_cfg(key, conv=True))
+    t = time_conv_f16(batch, IC, H, W, OC, kH, kW, stride, pad, key_to_cfg(key, conv=True, prof_dict=prof_dict))
     cost_ms = t * 1e3
     return cost_ms, 2.0 * M * N * K / 1e9 / cost_ms
 

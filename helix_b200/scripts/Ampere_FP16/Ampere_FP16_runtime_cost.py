@@ -8,8 +8,8 @@ root_path = os.getcwd()
 
 
 def cost_model(prof_dict, M, N, K):
-    from helix_b200 import costmodel
-    return costmodel.cost_model(prof_dict, M, N, K)
+    from helix_b200 import harness
+    return harness.cost_model(prof_dict, M, N, K)
 
 
 def get_Helix_runtime_cost(prof_dict, M, N, K):

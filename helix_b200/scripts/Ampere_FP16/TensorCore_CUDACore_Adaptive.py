@@ -13,20 +13,20 @@ root_path = os.getcwd()
 
 
 def cost_model(prof_dict, M, N, K):
-    from helix_b200 import costmodel
-    return costmodel.cost_model(prof_dict, M, N, K)
+    from helix_b200 import harness
+    return harness.cost_model(prof_dict, M, N, K)
 
 
 def cost_model_without_gemv(prof_dict, M, N, K):
     """The reference's variant that skips the GEMV keys (TensorCore_CUDACore_Adaptive.py:21-34)."""
-    from helix_b200 import costmodel
-    return costmodel.cost_model({k: v for k, v in prof_dict.items() if not (len(k) == 6 and k[0] == 0)}, M, N, K)
+    from helix_b200 import harness
+    return harness.cost_model({k: v for k, v in prof_dict.items() if not (len(k) == 6 and k[0] == 0)}, M, N, K)
 
 
 def cost_model_gemv_only(prof_dict, M, N, K):
-    from helix_b200 import costmodel
+    from helix_b200 import harness
     gemv = {k: v for k, v in prof_dict.items() if len(k) != 6 or k[0] == 0}
-    return costmodel.cost_model(gemv, min(M, 8), N, K)
+    return harness.cost_model(gemv, min(M, 8), N, K)
 
 
 def get_Helix_result(prof_dict, M, N, K):

@@ -15,7 +15,7 @@ def Ampere_FP16_Helix_op_level_GEMM_benchmark(backend="cuda", gpus=1, limit=0, j
     MNKList = get_gemm_op_MNKList()
     if limit:
         MNKList = MNKList[:limit]
-    predicted = [costmodel.predicted_time(prof_dict, costmodel.cost_model(prof_dict, M, N, K), M, N, K) for M, N, K in MNKList]
+    predicted = [harness.predicted_time(prof_dict, harness.cost_model(prof_dict, M, N, K), M, N, K) for M, N, K in MNKList]
     rows = harness.run_shape_list(MNKList, harness.worker_gemm_f16, prof_dict, gpus, predicted, journal=journal)
     for (M, N, K), row in zip(MNKList, rows):
         helix_tflops = row["tflops"]

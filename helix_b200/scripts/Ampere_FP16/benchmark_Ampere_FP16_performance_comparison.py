@@ -20,23 +20,23 @@ def _kernel_keys(prof_dict):
 
 
 def cost_model(prof_dict, M, N, K):
-    from helix_b200 import costmodel
-    return costmodel.cost_model(prof_dict, M, N, K)
+    from helix_b200 import harness
+    return harness.cost_model(prof_dict, M, N, K)
 
 
 def cost_model_static1(prof_dict, M, N, K):
-    from helix_b200 import costmodel
+    from helix_b200 import harness
     plain = {k: v for k, v in prof_dict.items()
              if len(k) != 6 or (k[0] != 0 and k[3] == 1 and k[4] == 0 and k[5] == 0)}
-    return costmodel.cost_model(plain, M, N, K)
+    return harness.cost_model(plain, M, N, K)
 
 
 def cost_model_static2(prof_dict, M, N, K):
     """Shape-blind: the tensor-core key with the smallest profiled seconds per K slab that can run at all."""
-    from helix_b200 import costmodel
+    from helix_b200 import harness
     best, best_key = float("inf"), None
     for k in _kernel_keys(prof_dict):
-        if k[0] == 0 or costmodel.predicted_time(prof_dict, k, M, N, K) == float("inf"):
+        if k[0] == 0 or harness.predicted_time(prof_dict, k, M, N, K) == float("inf"):
             continue
         per_slab = prof_dict[k][1] / (k[1] * k[2] * k[3])       # seconds per slab per output element
         if per_slab < best:
@@ -54,12 +54,12 @@ def get_Helix_Default_result(prof_dict, M, N, K):
 
 
 def get_Helix_Oracle_result(prof_dict, M, N, K):
-    from helix_b200 import costmodel
+    from helix_b200 import harness
     best = 0.0
     for k in _kernel_keys(prof_dict):
         if k[0] == 0 and min(M, N) > 8:
             continue
-        if costmodel.predicted_time(prof_dict, k, M, N, K) == float("inf"):
+        if harness.predicted_time(prof_dict, k, M, N, K) == float("inf"):
             continue
         best = max(best, _tflops(k, M, N, K))
     return best

@@ -18,7 +18,7 @@ DEFAULT_SHAPES = [(500, 1024, 1024), (128, 512, 1000), (5000, 712, 2048), (32, 5
 
 def candidates(prof_dict, M, N, K):
     """[(id, key, predicted seconds)] in dictionary order, ids counted over kernel keys from 1."""
-    from helix_b200 import costmodel
+    from helix_b200 import harness
     out, idx = [], 0
     for k in prof_dict:
         if len(k) != 6:
@@ -26,7 +26,7 @@ def candidates(prof_dict, M, N, K):
         idx += 1
         if k[0] == 0 and min(M, N) > 8:
             continue
-        t = costmodel.predicted_time(prof_dict, k, M, N, K)
+        t = harness.predicted_time(prof_dict, k, M, N, K)
         if t < float("inf"):
             out.append((idx, k, t))
     return out

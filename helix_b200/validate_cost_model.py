@@ -37,8 +37,8 @@ def main(argv=None):
     print("%-28s %-28s %10s %10s %6s %10s" % ("shape (M,N,K,batch)", "model's pick", "pred us", "meas us", "ratio", "best us"))
     worst = 0.0
     for (M, N, K, b) in shapes():
-        key = costmodel.cost_model(d, M, N, K, b or 1)
-        pred = costmodel.predicted_time(d, key, M, N, K, b or 1)
+        key = harness.cost_model(d, M, N, K, b)
+        pred = harness.predicted_time(d, key, M, N, K, b)
         meas = harness.time_gemm_f16(M, N, K, harness.key_to_cfg(key), b)
         best = float("nan")
         if args.exhaustive:
@@ -49,6 +49,24 @@ def main(argv=None):
                                                           best * 1e6), flush=True)
     if args.exhaustive:
         print("worst pick / exhaustive best: %.2f" % worst)
+    # the same model asked about ONE launch (no overlap with neighbours), for the memory-bound shapes
+    print("lone launches:")
+    for (M, N, K, b) in [s for s in shapes() if harness.overlaps(*s)]:
+        key = costmodel.cost_model(d, M, N, K, b or 1)
+        pred = costmodel.predicted_time(d, key, M, N, K, b or 1)
+        meas = harness.time_gemm_f16(M, N, K, harness.key_to_cfg(key, prof_dict=d), b, lone=True)
+        lib = harness.time_gemm_f16(M, N, K, None, b, lone=True)
+        print("%-28s %-28s %10.1f %10.1f %6.2f   library default %.1f" % ((M, N, K, b), key, pred * 1e6, meas * 1e6,
+                                                                         pred / meas, lib * 1e6), flush=True)
+    # convolutions (the five ResNet-style layers): the model's pick against the library's default
+    print("convolutions:")
+    for layer in datagen.C4_LAYERS:
+        B, C, H, W, OC, kh, kw, stride, pad = layer
+        cost_ms, _ = harness.conv_f16_result(d, *layer)
+        lib = harness.time_conv_f16(*layer)
+        print("%-40s model's pick %8.1f us   library default %8.1f us" % (layer, cost_ms * 1e3, lib * 1e6), flush=True)
+    print("searched fields:", {k: v for k, v in d.items() if k[0] in ("load_group", "load_group_probe", "stages_probe",
+                                                                     "splitk_overhead", "conv_slab", "conv_slab_swap")})
     return 0
 
 

@@ -17,11 +17,13 @@ the way the reference drives them.
 
 Each executable allocates uninitialised buffers, runs 10 warm-up and 10 timed launches and prints one line whose
 whitespace token [-8] is the average time in seconds (src_template/Ampere_FP16/gemm.cu:687-689; the gemv line
-labels it "ms" but divides its millisecond figure by 1e3 first, gemv.cu:394-399); ``im2col`` prints its average
-microseconds divided by 1e9 (im2col.cu:120-128,191).  Measurement context only: nothing in the library, the tests
+labels it "ms" but divides its millisecond figure by 1e3 first, gemv.cu:394-399).  The reference's ``im2col``
+executable prints its average microseconds divided by 1e9 with "%f" (im2col.cu:191), i.e. 0.000000, so its time
+comes from ``im2col_us``: the same unmodified source and timing routine behind an entry point that prints the
+microseconds (oracle/legacy_im2col_main.cu).  Measurement context only: nothing in the library, the tests
 or bench.py uses it.
 
-  python oracle/legacy_port.py [--json out.json]
+  python oracle/legacy_port.py [--json out.json] [--only gemm|conv|other]
 """
 import argparse
 import json
@@ -59,10 +61,10 @@ def run_exe(path, *ints, timeout=300):
 
 
 def run_im2col(path, layer, timeout=300):
-    """Microseconds of the reference's im2col executable for one layer, or None."""
+    """Microseconds per launch of the reference's im2col kernel for one layer (im2col_us), or None."""
     try:
         out = subprocess.run([path] + [str(v) for v in layer], capture_output=True, text=True, timeout=timeout)
-        return float(out.stdout.split()[0]) * 1e9
+        return float(out.stdout.split()[0])
     except (subprocess.TimeoutExpired, ValueError, IndexError):
         return None
 
@@ -126,6 +128,8 @@ def run_config(key, M, N, K):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
+    ap.add_argument("--only", choices=["all", "gemm", "conv", "other"], default="all",
+                    help="run one group of rows (the profile always runs: the pick needs it)")
     args = ap.parse_args(argv)
     if not os.path.isdir(LEGACY):
         print("oracle/_ref/legacy is missing: run `make -C oracle legacy REF=<reference checkout>`")
@@ -142,7 +146,7 @@ def main(argv=None):
 
     # fp16 GEMMs: the reference's pick, and the best of the subset
     gemm_keys = [k for k in prof if k[0] != 0]
-    for (M, N, K) in HGEMM_SHAPES:
+    for (M, N, K) in (HGEMM_SHAPES if args.only in ("all", "gemm") else []):
         pick = reference_cost_model(prof, M, N, K)
         t_pick = run_config(pick, M, N, K) if pick else None
         best = None
@@ -161,8 +165,8 @@ def main(argv=None):
         rows.append(row)
 
     # convolutions: im2col executable + the picked GEMM, the reference's two-process path
-    im2col = os.path.join(LEGACY, "im2col")
-    if os.path.exists(im2col):
+    im2col = os.path.join(LEGACY, "im2col_us")
+    if os.path.exists(im2col) and args.only in ("all", "conv"):
         for layer in CONV_LAYERS:
             B, IC, H, W, OC, kH, kW, stride, pad = layer
             M = B * ((H + 2 * pad - kH) // stride + 1) * ((W + 2 * pad - kW) // stride + 1)
@@ -188,7 +192,7 @@ def main(argv=None):
             rows.append(row)
 
     # fp32 GEMM and GEMV executables: best of the built ones
-    for prefix, shapes in (("sgemm_", SGEMM_SHAPES), ("gemv", GEMV_SHAPES)):
+    for prefix, shapes in ((("sgemm_", SGEMM_SHAPES), ("gemv", GEMV_SHAPES)) if args.only in ("all", "other") else ()):
         for (M, N, K) in shapes:
             best = None
             for e in exes:

@@ -67,8 +67,14 @@ def test_default_config_and_workspace_are_consistent(lib):
             tiles = -(-pm // 128) * -(-pn // c.tile_n) * b
             grid = min(tiles * -(-K // 64), 148)   # no device here: the library assumes 148 SMs
             assert ws == (0 if tiles % grid == 0 else 2 * grid * 128 * c.tile_n * 4)
+        elif c.split_k == 1:
+            assert ws == 0
         else:
-            assert ws == (0 if c.split_k == 1 else c.split_k * b * M * N * 4)
+            # split-K: one 8-byte arrival counter per tile (rounded up to 1 KiB), then one 128 x tile_n fp32 slot
+            # per tile and slice
+            pm, pn = (N, M) if c.swap_ab else (M, N)
+            tiles = -(-pm // 128) * -(-pn // c.tile_n) * b
+            assert ws == -(-tiles * 8 // 1024) * 1024 + tiles * c.split_k * 128 * c.tile_n * 4
 
 
 def test_launch_without_device_reports_nodevice_or_runs(lib):

@@ -344,7 +344,9 @@ def test_ablation_selection_policies_on_a_synthetic_dictionary():
     cand = curve.candidates(d, 476, 1024, 1024)
     ids = [c[0] for c in cand]
     assert ids == sorted(ids) and all(c[1][0] != 0 for c in cand)
-    assert min(cand, key=lambda c: c[2])[1] == costmodel.cost_model(d, 476, 1024, 1024)
+    # (a shape the timing harness overlaps: the scripts' prediction carries that protocol flag)
+    assert min(cand, key=lambda c: c[2])[1] == costmodel.cost_model(d, 476, 1024, 1024, overlapped=True)
+    assert comp.cost_model(d, 476, 1024, 1024) == costmodel.cost_model(d, 476, 1024, 1024, overlapped=True)
     assert any(c[1][0] == 0 for c in curve.candidates(d, 4, 1024, 1024))
 
 
@@ -390,3 +392,40 @@ def test_legacy_port_restates_the_references_pick():
     assert lp.reference_cost_model(prof, 128, 128, 4096) == (0, 1, 128, 0, 0, 0)           # 128 GEMV blocks: 2 waves x 2 us
     del prof[(0, 1, 128, 0, 0, 0)]
     assert lp.reference_cost_model(prof, 128, 128, 4096) == (3, 128, 128, 64, 64, 1)      # one wave each: cheapest probe
+
+
+def test_cost_model_split_k_modes_and_launch_protocol():
+    """Modes 2..4 of a key mean split-K over that many slices (one work item each, all resident at once);
+    the prediction describes a lone launch unless the caller says its launches overlap."""
+    from helix_b200 import harness
+    d = synthetic_dict()
+    d[("splitk_overhead", 128)] = (5e-6, 1.2e-6)
+    d[("conv_slab_swap", 256)] = 0.5e-6
+    d.update({("skinny_fixed",): 2.5e-6, ("wide_gbs_per_sm",): 400.0, ("hbm_wide_gbs",): 5300.0, ("skinny_l2_gbs",): 9300.0})
+    k128 = (costmodel.max_stages(128), 128, 128, 1, 0, 0)
+    split4 = k128[:5] + (4,)
+    assert split4 in costmodel.gemm_keys() and costmodel.is_valid_config(128, 0, 4, 6)
+    # 98 tiles x 4 slices do not fit 148 SMs at once: not applicable; 32 tiles x 4 do
+    assert costmodel.gemm_time(d, split4, 6272, 256, 2304) == float("inf")
+    t1 = costmodel.gemm_time(d, k128, 4096, 128, 8192)
+    t4 = costmodel.gemm_time(d, split4, 4096, 128, 8192)
+    assert t4 < t1                                    # 32 tiles, 128 slabs each: a quarter of the slabs plus the sum
+    assert abs(t4 - (4e-6 + 32 * 0.31e-6 + 5e-6 + 4 * 1.2e-6)) < 1e-9
+    # one row block of A: alone, the widest tile on 16 CTAs is bound by its bytes in flight and a split wins;
+    # overlapped launches do best unsplit on the widest tile
+    lone = costmodel.cost_model(d, 128, 4096, 11008)
+    over = costmodel.cost_model(d, 128, 4096, 11008, overlapped=True)
+    assert lone[5] != 0 and over[5] == 0                # alone: K is spread over more CTAs (split-K or stream-K)
+    wide = (costmodel.max_stages(256), 128, 256, 1, 0, 0)
+    assert costmodel.gemm_time(d, wide[:5] + (3,), 128, 4096, 11008) < costmodel.gemm_time(d, wide, 128, 4096, 11008)
+    assert costmodel.predicted_time(d, lone, 128, 4096, 11008) < costmodel.predicted_time(d, over, 128, 4096, 11008)
+    # swapped convolution tiles only where the caller says the geometry goes through the im2col tensor map
+    sw = (costmodel.max_stages(256), 128, 256, 1, 1, 0)
+    assert costmodel.gemm_time(d, sw, 25088, 128, 1152, conv=True) == float("inf")
+    assert costmodel.gemm_time(d, sw, 25088, 128, 1152, conv="im2col") < float("inf")
+    # keys -> configurations
+    c = harness.key_to_cfg(split4, prof_dict={("load_group", 128): 3})
+    assert (c.split_k, c.stream_k, c.load_group, c.tile_n) == (4, 0, 3, 128)
+    c = harness.key_to_cfg(k128[:5] + (1,))
+    assert (c.split_k, c.stream_k) == (1, 1)
+    assert harness.overlaps(16, 11008, 4096) and not harness.overlaps(4096, 4096, 4096)
