@@ -455,6 +455,11 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       bool ok = true;
       int nslab = 0;
       int gpos = 0, gidx = 0;   // position of the next slab inside its group of stages, and the group
+      // with timeline capture on: where this thread's cycles go, summed over its slabs (barrier wait, fence +
+      // descriptors, the four MMAs, commit, everything between one slab's commit and the next slab's wait)
+      const bool tr = p.trace != nullptr;
+      unsigned int c_wait = 0, c_desc = 0, c_mma = 0, c_commit = 0, c_rest = 0, c_slabs = 0;
+      long long t_prev = 0;
       WorkItem w;
       for (int idx = 0; ok && get_item(p, cta, grid, idx, w); ++idx) {
         const int acc = idx & 1;
@@ -468,11 +473,14 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           // One wait per group of stages: reading shared memory (the barrier) costs this thread some 200
           // cycles on top of the 45 it needs to hand one MMA to the tensor core, more than a 64-deep slab
           // of a narrow tile keeps the tensor core busy.  The stages are still released one by one.
+          const long long t0 = tr ? clock64() : 0;
+          if (tr && kb > w.kb0) c_rest += (unsigned int)(t0 - t_prev);
           if (gpos == 0) {
             ok = mbar_wait(&full_bar[gidx], phase, abort_flag, p.status);
             if (!ok) break;
           }
           if (++gpos == p.group) { gpos = 0; ++gidx; }
+          const long long t1 = tr ? clock64() : 0;
           trace_slab(p, 1, nslab++);
           // The gathered A tile was written through the generic proxy (cp.async); order those
           // writes, now visible through the barrier, before the tensor core's async-proxy reads.
@@ -480,6 +488,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           tc_fence_after_sync();
           const uint64_t da = umma_desc_sw128(smem_u32(sA + (size_t)stage * kATileBytes));
           const uint64_t db = umma_desc_sw128(smem_u32(sB + (size_t)stage * L::kBTileBytes));
+          const long long t2 = tr ? clock64() : 0;
           if (!(p.probe & 1)) {
 #pragma unroll
             for (int k = 0; k < kBK / 16; ++k) {
@@ -487,11 +496,26 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
               umma_f16_ss(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kb > w.kb0) || (k > 0));
             }
           }
+          const long long t3 = tr ? clock64() : 0;
           umma_commit(&empty_bar[stage]);
           if (++stage == stages) { stage = 0; phase ^= 1; gidx = 0; }
+          if (tr) {
+            t_prev = clock64();
+            c_wait += (unsigned int)(t1 - t0);
+            c_desc += (unsigned int)(t2 - t1);
+            c_mma += (unsigned int)(t3 - t2);
+            c_commit += (unsigned int)(t_prev - t3);
+            ++c_slabs;
+          }
         }
         if (ok) umma_commit(&tmem_full[acc]);
         trace_mark(p, idx, 3);
+      }
+      if (tr) {
+        unsigned long long* h = p.trace + (size_t)cta * kTraceWords;
+        h[5] = (unsigned long long)c_wait | ((unsigned long long)c_desc << 32);
+        h[6] = (unsigned long long)c_mma | ((unsigned long long)c_commit << 32);
+        h[7] = (unsigned long long)c_slabs | ((unsigned long long)c_rest << 32);
       }
     }
   } else {

@@ -254,7 +254,9 @@ int helix_gemv_f16_static(const void* W, int64_t ldw, const void* X, int64_t ldx
  * reference has only whole-kernel cudaEvent times, gemm.cu:622-660).  While a device buffer is
  * set, each such launch whose grid fits writes helix_trace_words_per_cta() 64-bit words per CTA
  * into it: [0] globaltimer and [1] clock64 at CTA start, [2] clock64 when global memory may first
- * be touched, [3] clock64 and [4] globaltimer at teardown; from word 8 on, for each of the first
+ * be touched, [3] clock64 and [4] globaltimer at teardown; (one-CTA kernel) [5]..[7] the MMA-issuing thread's
+ * cycles summed over its K slabs, two 32-bit sums per word: barrier waits | fence and descriptors, the four MMAs |
+ * the commit, slab count | everything between a commit and the next wait; from word 8 on, for each of the first
  * 20 work items of the CTA, six clock64 stamps: first / last load request, MMA issue start / end,
  * epilogue start / end; then, for the CTA's first 32 K slabs, the clock64 at which each was
  * requested (32 words) and at which the MMA issuer found it loaded (32 words).  Later launches
