@@ -240,7 +240,8 @@ conv_f16_win_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     }
   } else if (warp == 3) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // the whole warp walks the loop convergently (warp-uniform state, waits end in a vote); one elected lane issues
+    {
       const uint32_t idesc = umma_idesc_f16(kBM, p.npos);
       bool ok = true;
       int idx = 0, nslab = 0;
@@ -250,13 +251,13 @@ conv_f16_win_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       for (int t = cta; ok && win_item(p, t, it); t += grid, ++idx) {
         const int acc = idx & 1;
         const uint32_t acc_phase = (idx >> 1) & 1;
-        ok = mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag, p.status);
+        ok = __all_sync(0xffffffffu, mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag, p.status));
         if (!ok) break;
         tc_fence_after_sync();
-        wtrace_item(p, idx, 2);
+        if (lane == 0) wtrace_item(p, idx, 2);
         const uint32_t d_tmem = tmem_base + acc * kMaxPos;
         for (int cb = 0; cb < p.cblocks && ok; ++cb) {
-          ok = mbar_wait(&hfull[hs], hph, abort_flag, p.status);
+          ok = __all_sync(0xffffffffu, mbar_wait(&hfull[hs], hph, abort_flag, p.status));
           if (!ok) break;
           const uint32_t win0 = smem_u32(sWin + (size_t)hs * p.buf_bytes);
           uint32_t tap_row = 0;      // first window row of the tap, in bytes: (fr * Wp + fs) * 128
@@ -265,11 +266,12 @@ conv_f16_win_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             // one wait per group of weight slabs: reading the barrier costs this thread some 200 cycles on
             // top of the 45 it needs to hand an MMA to the tensor core; the stages are released one by one
             if (gpos == 0) {
-              ok = mbar_wait(&wfull[gidx], wph, abort_flag, p.status);
+              ok = __all_sync(0xffffffffu, mbar_wait(&wfull[gidx], wph, abort_flag, p.status));
               if (!ok) break;
             }
             if (++gpos == p.w_group) { gpos = 0; ++gidx; }
-            wtrace_slab(p, 1, nslab++);
+            if (lane == 0) wtrace_slab(p, 1, nslab);
+            ++nslab;
             tc_fence_after_sync();
             const uint64_t da = umma_desc_sw128(smem_u32(sW + (size_t)ws * kWBytes));
             // The tensor core derives the swizzle phase of a row from the row's absolute shared-memory
@@ -279,18 +281,18 @@ conv_f16_win_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             if (!(p.probe & 1)) {
 #pragma unroll
               for (int k = 0; k < kBK / 16; ++k)
-                umma_f16_ss(d_tmem, da + 2 * k, db + 2 * k, idesc, (cb > 0) || (tap > 0) || (k > 0));
+                umma_f16_ss_elect(d_tmem, da + 2 * k, db + 2 * k, idesc, (cb > 0) || (tap > 0) || (k > 0));
             }
-            umma_commit(&wempty[ws]);
+            umma_commit_elect(&wempty[ws]);
             if (++ws == p.w_stages) { ws = 0; wph ^= 1; gidx = 0; }
             tap_row += 128u;
             if (++fs == p.S) { fs = 0; tap_row += (uint32_t)(p.Wp - p.S) * 128u; }
           }
-          if (ok) umma_commit(&hempty[hs]);
+          if (ok) umma_commit_elect(&hempty[hs]);
           if (++hs == kWinStages) { hs = 0; hph ^= 1; }
         }
-        if (ok) umma_commit(&tfull[acc]);
-        wtrace_item(p, idx, 3);
+        if (ok) umma_commit_elect(&tfull[acc]);
+        if (lane == 0) wtrace_item(p, idx, 3);
       }
     }
   } else {

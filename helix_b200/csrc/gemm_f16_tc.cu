@@ -52,6 +52,7 @@ constexpr int kGemmProducerWarps = 4;      // warps ahead of the MMA warp: warp 
 constexpr int kGemmThreads = kGemmProducerWarps * 32 + 32 + 128;  // TMA warps + MMA warp + 4 epilogue warps
 constexpr int kStoreStagingBytes = 4 * 2 * 32 * 128;              // two 32-row x 128-byte boxes per epilogue warp
 constexpr int kEpiBarrier = 1;                                    // named barrier of the 128 epilogue threads
+constexpr int kFwdBarrier = 2;   // named barriers 2..9: arrival of one group of ring stages, forwarded to the MMA warp
 
 enum OutMode { kOutDirect = 0, kOutSplitSlice = 1, kOutStreamSlot = 2 };
 
@@ -277,7 +278,30 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       // tensor copy holds its issuing thread for a few hundred cycles whatever the box size, so
       // one thread alone cannot keep the ring full; consecutive slabs issued by different warps
       // also land in the same DRAM pages close in time.
-      // warp 0 shares its scheduler with the MMA warp (warp 4) and stays idle: the issuing warps are 1, 2, 3
+      // Warp 0 shares its scheduler with the MMA warp (warp 4) and issues no loads: the issuing warps are 1, 2, 3.
+      // Warp 0 watches the ring's arrival barriers for the MMA warp.  A shared-memory read by the MMA warp itself
+      // queues behind the tcgen05.mma instructions it has just issued (in-order memory pipe: some 200 cycles
+      // during which it can hand over nothing new); a hardware named barrier does not.  So warp 0 waits on
+      // full_bar[g] and then meets the MMA warp at named barrier kFwdBarrier + g.  Both warps walk the same
+      // sequence of groups to its end whatever happens (after a failed wait they skip everything but the
+      // rendezvous), so neither can be left waiting at a named barrier; the two are in lockstep per group, so
+      // arrivals cannot run ahead either.
+      if (warp == 0) {
+        bool ok = true;
+        int stage = 0, gpos = 0, gidx = 0;
+        uint32_t phase = 0;
+        WorkItem w;
+        for (int idx = 0; get_item(p, cta, grid, idx, w); ++idx) {
+          for (int kb = w.kb0; kb < w.kb1; ++kb) {
+            if (gpos == 0) {
+              if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[gidx], phase, abort_flag, p.status));
+              named_bar_sync(kFwdBarrier + gidx, 64);
+            }
+            if (++gpos == p.group) { gpos = 0; ++gidx; }
+            if (++stage == stages) { stage = 0; phase ^= 1; gidx = 0; }
+          }
+        }
+      }
       const int pwarp = warp - 1;
       if (lane == 0 && pwarp >= 0 && pwarp < p.load_warps) {
         bool ok = true;
@@ -449,39 +473,51 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the loop convergently (all loop state is warp-uniform, waits end in a vote) and one
+    // elected lane issues the tcgen05 instructions: descriptors and barrier addresses then live in uniform
+    // registers instead of being moved there per operand from one lane's registers.
+    {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int nslab = 0;
       int gpos = 0, gidx = 0;   // position of the next slab inside its group of stages, and the group
-      // with timeline capture on: where this thread's cycles go, summed over its slabs (barrier wait, fence +
+      // with timeline capture on: where the issuing warp's cycles go, summed over its slabs (barrier wait, fence +
       // descriptors, the four MMAs, commit, everything between one slab's commit and the next slab's wait)
       const bool tr = p.trace != nullptr;
       unsigned int c_wait = 0, c_desc = 0, c_mma = 0, c_commit = 0, c_rest = 0, c_slabs = 0;
       long long t_prev = 0;
       WorkItem w;
-      for (int idx = 0; ok && get_item(p, cta, grid, idx, w); ++idx) {
+      // Without the gathering producer (CONV = 0) the arrival of a group of stages reaches this warp through a
+      // named barrier shared with warp 0; the sequence is then walked to its end even after a failed wait
+      // (ok = false: nothing is issued any more, only the rendezvous are kept).
+      constexpr bool kForward = !CONV;
+      for (int idx = 0; (kForward || ok) && get_item(p, cta, grid, idx, w); ++idx) {
         const int acc = idx & 1;
         const uint32_t acc_phase = (idx >> 1) & 1;
-        ok = mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status);
-        if (!ok) break;
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status));
+        if (!ok && !kForward) break;
         tc_fence_after_sync();
-        trace_mark(p, idx, 2);
+        if (lane == 0) trace_mark(p, idx, 2);
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
-          // One wait per group of stages: reading shared memory (the barrier) costs this thread some 200
+          // One wait per group of stages: reading shared memory (the barrier) costs the issuing warp some 200
           // cycles on top of the 45 it needs to hand one MMA to the tensor core, more than a 64-deep slab
           // of a narrow tile keeps the tensor core busy.  The stages are still released one by one.
           const long long t0 = tr ? clock64() : 0;
           if (tr && kb > w.kb0) c_rest += (unsigned int)(t0 - t_prev);
           if (gpos == 0) {
-            ok = mbar_wait(&full_bar[gidx], phase, abort_flag, p.status);
-            if (!ok) break;
+            if (kForward) {
+              named_bar_sync(kFwdBarrier + gidx, 64);
+            } else {
+              ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[gidx], phase, abort_flag, p.status));
+              if (!ok) break;
+            }
           }
           if (++gpos == p.group) { gpos = 0; ++gidx; }
           const long long t1 = tr ? clock64() : 0;
-          trace_slab(p, 1, nslab++);
+          if (lane == 0) trace_slab(p, 1, nslab);
+          ++nslab;
           // The gathered A tile was written through the generic proxy (cp.async); order those
           // writes, now visible through the barrier, before the tensor core's async-proxy reads.
           if (CONV) fence_proxy_async_smem();
@@ -489,15 +525,15 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           const uint64_t da = umma_desc_sw128(smem_u32(sA + (size_t)stage * kATileBytes));
           const uint64_t db = umma_desc_sw128(smem_u32(sB + (size_t)stage * L::kBTileBytes));
           const long long t2 = tr ? clock64() : 0;
-          if (!(p.probe & 1)) {
+          if (ok && !(p.probe & 1)) {
 #pragma unroll
             for (int k = 0; k < kBK / 16; ++k) {
               // advancing 16 halves = 32 bytes along K inside the swizzle atom: +2 in the address field
-              umma_f16_ss(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kb > w.kb0) || (k > 0));
+              umma_f16_ss_elect(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kb > w.kb0) || (k > 0));
             }
           }
           const long long t3 = tr ? clock64() : 0;
-          umma_commit(&empty_bar[stage]);
+          if (ok) umma_commit_elect(&empty_bar[stage]);
           if (++stage == stages) { stage = 0; phase ^= 1; gidx = 0; }
           if (tr) {
             t_prev = clock64();
@@ -508,10 +544,10 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             ++c_slabs;
           }
         }
-        if (ok) umma_commit(&tmem_full[acc]);
-        trace_mark(p, idx, 3);
+        if (ok) umma_commit_elect(&tmem_full[acc]);
+        if (lane == 0) trace_mark(p, idx, 3);
       }
-      if (tr) {
+      if (tr && lane == 0) {
         unsigned long long* h = p.trace + (size_t)cta * kTraceWords;
         h[5] = (unsigned long long)c_wait | ((unsigned long long)c_desc << 32);
         h[6] = (unsigned long long)c_mma | ((unsigned long long)c_commit << 32);
