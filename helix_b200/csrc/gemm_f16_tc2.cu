@@ -36,6 +36,7 @@ constexpr int kPairProducerWarps = 3;   // warp 0 and warps 6, 7 issue TMA loads
 constexpr int kThreads = 32 + 32 + 128 + 64;
 constexpr int kStagingBytes = 2 * 128 * 128;     // two 128-row x 128-byte boxes shared by the four epilogue warps
 constexpr int kEpiBarrier = 1;                   // named barrier of the 128 epilogue threads
+constexpr int kFwdBarrier2 = 2;                  // named barriers 2..9: arrival of a group of ring stages, forwarded to the MMA warp
 
 struct Gemm2Params {
   __half* C;
@@ -184,6 +185,31 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
       : "memory");
 }
 
+// The same two instructions for a warp that walks its issue loop convergently: every lane executes the statement,
+// one elected lane issues (see umma_f16_ss_elect in common.cuh).
+__device__ __forceinline__ void umma_f16_ss_pair_elect(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                       bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair_elect(uint64_t* bar) {
+  const uint32_t mask = 3;
+  asm volatile(
+      "{\n\t.reg .b16 lo, hi;\n\t.reg .pred q;\n\t"
+      "mov.b32 {lo, hi}, %1;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], lo;\n\t}" ::"r"(
+          smem_u32(bar)),
+      "r"(mask)
+      : "memory");
+}
+
 template <int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -250,6 +276,26 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // lives in ring stage n % stages.  One thread cannot keep the ring full: a tensor copy holds
     // its issuing thread for a few hundred cycles.
     const int issuer = warp == 0 ? 0 : warp - 5;
+    // With at most two issuing warps, warp 7 of the even CTA watches the ring's arrival barriers for the MMA warp
+    // and meets it at a named barrier per group of stages: a shared-memory read by the MMA warp itself would queue
+    // behind the MMAs it has just issued.  Both warps walk the same sequence of groups to its end whatever
+    // happens (after a failed wait only the rendezvous are kept), in lockstep per group.
+    if (warp == 7 && rank == 0 && p.load_warps < kPairProducerWarps) {
+      bool ok = true;
+      int stage = 0, gpos = 0, gidx = 0;
+      uint32_t phase = 0;
+      Item2 it;
+      for (int idx = 0; get_item2(p, pair, num_pairs, idx, it); ++idx) {
+        for (int kb = it.kb0; kb < it.kb1; ++kb) {
+          if (gpos == 0) {
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[gidx], phase, abort_flag, p.status));
+            named_bar_sync(kFwdBarrier2 + gidx, 64);
+          }
+          if (++gpos == p.group) { gpos = 0; ++gidx; }
+          if (++stage == stages) { stage = 0; phase ^= 1; gidx = 0; }
+        }
+      }
+    }
     if (lane == 0 && issuer < p.load_warps) {
       bool ok = true;
       int n_start = 0;
@@ -300,43 +346,51 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (even CTA only)
-    if (lane == 0 && rank == 0) {
+    // The whole warp walks the loop convergently (warp-uniform state, waits end in a vote) and one elected lane
+    // issues.  With a watcher warp (forward) the arrival of a group of stages comes through a named barrier and the
+    // sequence is walked to its end even after a failed wait (ok = false: only the rendezvous are kept).
+    if (rank == 0) {
+      const bool forward = p.load_warps < kPairProducerWarps;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int nslab = 0;
       int gpos = 0, gidx = 0;   // position of the next slab inside its group of stages, and the group
       Item2 it;
-      for (int idx = 0; ok && get_item2(p, pair, num_pairs, idx, it); ++idx) {
+      for (int idx = 0; (forward || ok) && get_item2(p, pair, num_pairs, idx, it); ++idx) {
         const int acc = idx & 1;
         const uint32_t acc_phase = (idx >> 1) & 1;
-        ok = mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status);
-        if (!ok) break;
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status));
+        if (!ok && !forward) break;
         tc_fence_after_sync();
-        trace2_tile(p, idx, 2);
+        if (lane == 0) trace2_tile(p, idx, 2);
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
-          // one wait per group of stages (a shared-memory read costs the issuing thread some 200 cycles);
-          // the stages are still released one by one
+          // one rendezvous (or wait) per group of stages; the stages are still released one by one
           if (gpos == 0) {
-            ok = mbar_wait(&full_bar[gidx], phase, abort_flag, p.status);
-            if (!ok) break;
+            if (forward) {
+              named_bar_sync(kFwdBarrier2 + gidx, 64);
+            } else {
+              ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[gidx], phase, abort_flag, p.status));
+              if (!ok) break;
+            }
           }
           if (++gpos == p.group) { gpos = 0; ++gidx; }
-          trace2_slab(p, 1, nslab++);
+          if (lane == 0) trace2_slab(p, 1, nslab);
+          ++nslab;
           tc_fence_after_sync();
           const uint64_t da = umma_desc_sw128(smem_u32(sA + (size_t)stage * kATileBytes));
           const uint64_t db = umma_desc_sw128(smem_u32(sB + (size_t)stage * kBHalfBytes));
-          if (!(p.probe & 1)) {
+          if (ok && !(p.probe & 1)) {
 #pragma unroll
             for (int k = 0; k < kBK / 16; ++k)
-              umma_f16_ss_pair(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kb > it.kb0) || (k > 0));
+              umma_f16_ss_pair_elect(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kb > it.kb0) || (k > 0));
           }
-          umma_commit_pair(&empty_bar[stage]);
+          if (ok) umma_commit_pair_elect(&empty_bar[stage]);
           if (++stage == stages) { stage = 0; phase ^= 1; gidx = 0; }
         }
-        if (ok) umma_commit_pair(&tmem_full[acc]);
-        trace2_tile(p, idx, 3);
+        if (ok) umma_commit_pair_elect(&tmem_full[acc]);
+        if (lane == 0) trace2_tile(p, idx, 3);
       }
     }
   } else {
