@@ -228,11 +228,13 @@ def per_config_table(peaks):
     dev = "cuda"
     out = {}
     r3 = lambda us, rate, frac: [round(us, 2), round(rate, 1), round(frac, 3)]
-    # bring the clocks up before the short measurements (the GPU has idled during the CPU legs)
-    a = torch.randn(4096, 4096, device=dev, dtype=torch.float16) / 64
-    c = torch.empty(4096, 4096, device=dev, dtype=torch.float16)
-    ops.time_launches([ops.launch_gemm_f16(a, a, c)] * 4, warmup=3, iters=1500, use_graph=True)    # ~0.6 s
-    del a, c
+    # Every row is a kernel timed alone against a burst peak, so every row starts from a rested GPU: after a
+    # stretch at the power cap the clocks stay low for a while (a table measured back to back showed 1100 MHz
+    # samples and rows 20-50 % slower than the same kernels measured one at a time).
+    def timed(ls, warmup=3, iters=20):
+        torch.cuda.synchronize()
+        time.sleep(0.5)
+        return ops.time_launches(ls, warmup=warmup, iters=iters, use_graph=True)
     # C2: fp16 GEMV 4096 x 4096, m = 1: twelve rotating W buffers (12 x 32 MiB > 2 x L2) in three
     # launch-ordering modes, plus one 268 MB matrix (16384 x 8192) streamed by chains of ordered launches
     rows = K = 4096
@@ -245,7 +247,7 @@ def per_config_table(peaks):
     for name, flag in (("independent", LAUNCH_INDEPENDENT), ("static_weights", LAUNCH_STATIC_A), ("ordered", 0)):
         for l in ls:
             l.flags = flag
-        avg, _, _ = ops.time_launches(ls, warmup=5, iters=50, use_graph=True)
+        avg, _, _ = timed(ls, warmup=5, iters=50)
         gb = gemv_bytes / avg / 1e9
         g[name] = r3(avg * 1e6, gb, gb / peaks["hbm_gbs"])
     del ws, ys, ls
@@ -253,7 +255,7 @@ def per_config_table(peaks):
     xb = torch.randn(1, 8192, device=dev, dtype=torch.float16)
     yb = [torch.empty(1, 16384, device=dev, dtype=torch.float16) for _ in big]
     ls = [ops.launch_gemv_f16(w, xb, y) for w, y in zip(big, yb)]
-    avg, _, _ = ops.time_launches(ls, warmup=3, iters=20, use_graph=True)
+    avg, _, _ = timed(ls, warmup=3, iters=20)
     gb = (16384 * 8192 * 2 + 8192 * 2 + 16384 * 2) / avg / 1e9
     g["16384x8192_ordered"] = r3(avg * 1e6, gb, gb / peaks["hbm_gbs"])
     del big, yb, ls
@@ -270,7 +272,7 @@ def per_config_table(peaks):
                  torch.randn(N, K, device=dev, dtype=torch.float16) / K ** 0.5,
                  torch.empty(M, N, device=dev, dtype=torch.float16)) for _ in range(nbuf)]
         a, b, c = bufs[0]
-        avg, _, _ = ops.time_launches([ops.launch_gemm_f16(a, b, c)] * 4, warmup=3, iters=20, use_graph=True)
+        avg, _, _ = timed([ops.launch_gemm_f16(a, b, c)] * 4, warmup=3, iters=20)
         if membound:
             gbs = by / avg / 1e9
             row = {"alone": r3(avg * 1e6, gbs, gbs / peaks["hbm_gbs"])}
@@ -278,7 +280,7 @@ def per_config_table(peaks):
             ls = [ops.launch_gemm_f16(a, b, c, wide) for a, b, c in bufs]
             for l in ls:
                 l.flags = LAUNCH_INDEPENDENT
-            avg, _, _ = ops.time_launches(ls, warmup=3, iters=20, use_graph=True)
+            avg, _, _ = timed(ls, warmup=3, iters=20)
             gbs = by / avg / 1e9
             row["overlapped"] = r3(avg * 1e6, gbs, gbs / peaks["hbm_gbs"])
             row["unit"] = "GB/s"
@@ -300,10 +302,10 @@ def per_config_table(peaks):
             ww = torch.randn(OC, kh, kw, C, device=dev, dtype=torch.float16) * (2.0 / (C * kh * kw)) ** 0.5
             yy = torch.empty(B, Ho, Wo, OC, device=dev, dtype=torch.float16)
             ls.append(ops.launch_conv2d_f16(xx, ww, yy, s, p))
-        avg, _, _ = ops.time_launches([ls[0]] * 4, warmup=3, iters=20, use_graph=True)
+        avg, _, _ = timed([ls[0]] * 4, warmup=3, iters=20)
         for l in ls:
             l.flags = LAUNCH_INDEPENDENT
-        over, _, _ = ops.time_launches(ls, warmup=3, iters=20, use_graph=True)
+        over, _, _ = timed(ls, warmup=3, iters=20)
         fl = 2.0 * B * Ho * Wo * OC * C * kh * kw
         by = 2.0 * (xx.numel() + ww.numel() + yy.numel())
         floor = max(fl / (peaks["tflops"] * 1e12), by / (peaks["hbm_gbs"] * 1e9))
@@ -316,7 +318,7 @@ def per_config_table(peaks):
         a = torch.rand(n, n, device=dev) * 2 - 1
         b = torch.rand(n, n, device=dev) * 2 - 1
         c = torch.empty(n, n, device=dev)
-        avg, _, _ = ops.time_launches([ops.launch_gemm_f32(a, b, c)] * 4, warmup=3, iters=10, use_graph=True)
+        avg, _, _ = timed([ops.launch_gemm_f32(a, b, c)] * 4, warmup=3, iters=10)
         tf = 2.0 * n ** 3 / avg / 1e12
         c1[str(n)] = r3(avg * 1e6, tf, tf / 74.4)
         del a, b, c
@@ -325,7 +327,7 @@ def per_config_table(peaks):
     wf = [torch.rand(8192, 8192, device=dev) * 2 - 1 for _ in range(2)]
     xf = torch.rand(1, 8192, device=dev) * 2 - 1
     yf = [torch.empty(1, 8192, device=dev) for _ in wf]
-    avg, _, _ = ops.time_launches([ops.launch_gemv_f32(w, xf, y) for w, y in zip(wf, yf)], warmup=3, iters=20, use_graph=True)
+    avg, _, _ = timed([ops.launch_gemv_f32(w, xf, y) for w, y in zip(wf, yf)], warmup=3, iters=20)
     gb = (8192 * 8192 * 4 + 2 * 8192 * 4) / avg / 1e9
     out["gemv_f32_8192x8192_m1 [us, GB/s, of_hbm]"] = r3(avg * 1e6, gb, gb / peaks["hbm_gbs"])
     del wf, yf
@@ -340,6 +342,8 @@ def extras(peaks):
     c32 = {}
     for layer in datagen.C4_LAYERS[:2] + datagen.C4_LAYERS[3:4]:
         B, C, H, W, OC, kh, kw, s, p = layer
+        torch.cuda.synchronize()
+        time.sleep(0.5)           # every row starts from a rested GPU (see per_config_table)
         t = harness.time_conv_f32(*layer)
         Ho, Wo = ops.conv_out_hw(H, W, kh, kw, s, p)
         tf = 2.0 * B * Ho * Wo * OC * C * kh * kw / t / 1e12
@@ -349,9 +353,13 @@ def extras(peaks):
     comp = {}
     try:
         for (M, N, K) in datagen.C3_SHAPES:
+            torch.cuda.synchronize()
+            time.sleep(0.5)
             ms, tf = harness.cublas_gemm_result(M, N, K)
             comp["cublas %dx%dx%d" % (M, N, K)] = {"us": round(ms * 1e3, 1), "TFLOP/s": round(tf, 1)}
         for layer in datagen.C4_LAYERS:
+            torch.cuda.synchronize()
+            time.sleep(0.5)
             ms, tf = harness.cudnn_conv_result(*layer)
             comp["cudnn " + "x".join(map(str, layer))] = {"us": round(ms * 1e3, 1), "TFLOP/s": round(tf, 1)}
     except Exception as exc:     # a comparator that fails does not fail the benchmark
@@ -376,6 +384,7 @@ def kernel_breakdown(sw, ops, limit_units=125):
     flop / bytes per group."""
     from helix_b200 import workloads
     import ctypes
+    import torch
     from helix_b200._lib import Launch
     groups = {}
     for u, l0 in list(zip(sw.units, sw.launches))[:limit_units]:
@@ -388,6 +397,8 @@ def kernel_breakdown(sw, ops, limit_units=125):
         g["bytes"] += workloads.unit_bytes(u)
     out = {}
     for name, g in groups.items():
+        torch.cuda.synchronize()
+        time.sleep(0.5)           # each group starts from a rested GPU: it is rated against the burst peak
         avg, _, _ = ops.time_launches(g["launches"], warmup=3, iters=10, use_graph=True)
         n = len(g["launches"])
         out[name] = {"launches": n, "us": avg * n * 1e6, "flop": g["flop"], "bytes": g["bytes"]}
