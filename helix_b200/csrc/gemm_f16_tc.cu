@@ -83,6 +83,7 @@ struct GemmParams {
   int tma_store;   // whole tiles leave through shared memory and a TMA store (tmap_c is valid)
   int independent; // nothing read or written here is written by the kernel queued just before
   int probe;       // tuning instrument (helix_cfg_t.probe): 1 = issue no MMA, 2 = no A loads, 4 = no B loads
+  int eshift;      // 1: two consecutive ring stages share one "empty" barrier and one commit of the MMA issuer (0: one each)
   int group;       // ring stages that share one "full" barrier (see the MMA issuer); stages is a multiple of it
   FastDiv fd_grp;
   int* status;
@@ -231,7 +232,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       p.trace[(size_t)cta * kTraceWords + 1] = (unsigned long long)clock64();
     }
     // "full" barriers are shared by groups of `group` consecutive stages (one arrival per slab),
-    // "empty" barriers are per stage
+    // "empty" barriers are per stage, or per pair of stages (eshift)
     for (int s = 0; s < stages; ++s) {
       if (s * p.group < stages) mbar_init(&full_bar[s], CONV ? kConvProducerWarps * 32 + 1 : p.group);
       mbar_init(&empty_bar[s], 1);
@@ -325,7 +326,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           if (pwarp == 0) trace_mark(p, idx, 0);
           for (; my_n < n_start + nkb; my_n += p.load_warps) {
             const int kb = w.kb0 + (my_n - n_start);
-            ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status);
+            ok = mbar_wait(&empty_bar[stage >> p.eshift], phase ^ 1, abort_flag, p.status);
             if (!ok) break;
             trace_slab(p, 0, my_n);
             uint64_t* const fb = &full_bar[fast_div(stage, p.fd_grp)];
@@ -385,7 +386,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         // arrivals, each ordered after the release of its ring stage like a real slab.
         const int n_pad = (n_start + p.group - 1) / p.group * p.group;
         for (; ok && my_n < n_pad; my_n += p.load_warps) {
-          ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status);
+          ok = mbar_wait(&empty_bar[stage >> p.eshift], phase ^ 1, abort_flag, p.status);
           if (!ok) break;
           mbar_arrive(&full_bar[fast_div(stage, p.fd_grp)]);
           stage += p.load_warps;
@@ -439,7 +440,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           }
         }
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
-          if (lane == 0) ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status);
+          if (lane == 0) ok = mbar_wait(&empty_bar[stage >> p.eshift], phase ^ 1, abort_flag, p.status);
           ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
           if (!ok) break;
           if (threadIdx.x == 0) {
@@ -513,15 +514,16 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
               ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[gidx], phase, abort_flag, p.status));
               if (!ok) break;
             }
+            // The whole group is in shared memory now: one ordering point serves all its slabs.  The gathered A
+            // tiles were written through the generic proxy (cp.async); those writes, visible through the
+            // barrier, are ordered before the tensor core's async-proxy reads.
+            if (CONV) fence_proxy_async_smem();
+            tc_fence_after_sync();
           }
           if (++gpos == p.group) { gpos = 0; ++gidx; }
           const long long t1 = tr ? clock64() : 0;
           if (lane == 0) trace_slab(p, 1, nslab);
           ++nslab;
-          // The gathered A tile was written through the generic proxy (cp.async); order those
-          // writes, now visible through the barrier, before the tensor core's async-proxy reads.
-          if (CONV) fence_proxy_async_smem();
-          tc_fence_after_sync();
           const uint64_t da = umma_desc_sw128(smem_u32(sA + (size_t)stage * kATileBytes));
           const uint64_t db = umma_desc_sw128(smem_u32(sB + (size_t)stage * L::kBTileBytes));
           const long long t2 = tr ? clock64() : 0;
@@ -533,7 +535,8 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             }
           }
           const long long t3 = tr ? clock64() : 0;
-          if (ok) umma_commit_elect(&empty_bar[stage]);
+          // release the stage -- or, with paired stages, both stages of the pair after its second slab
+          if (ok && ((stage & p.eshift) == p.eshift)) umma_commit_elect(&empty_bar[stage >> p.eshift]);
           if (++stage == stages) { stage = 0; phase ^= 1; gidx = 0; }
           if (tr) {
             t_prev = clock64();
@@ -547,6 +550,8 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         if (ok) umma_commit_elect(&tmem_full[acc]);
         if (lane == 0) trace_mark(p, idx, 3);
       }
+      // the sequence ended on the first stage of a pair: release the pair for the producers' padding arrivals
+      if (ok && p.eshift && (stage & 1)) umma_commit_elect(&empty_bar[stage >> 1]);
       if (tr && lane == 0) {
         unsigned long long* h = p.trace + (size_t)cta * kTraceWords;
         h[5] = (unsigned long long)c_wait | ((unsigned long long)c_desc << 32);
@@ -1370,6 +1375,10 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
     p.stages = p.stages / p.group * p.group;
   }
   p.fd_grp = make_fastdiv(p.group);
+  // Rings of eight stages (tiles up to 64 wide) release their stages in pairs: one commit of the MMA issuer per two
+  // slabs (396 against 421 cycles per slab).  Six-stage rings lose by it (the coarser release starves the ring:
+  // 496 against 440 cycles per slab at 128 wide) and keep one barrier per stage.  Probe bit 3 switches the pairing off.
+  p.eshift = (!conv && p.stages >= 8 && p.stages % 2 == 0 && !(cfg.probe & 8)) ? 1 : 0;
   // Never more issuing warps than ring stages: a warp waits on a stage's "empty" barrier by
   // parity, which is only meaningful while it is at most one use of that stage ahead of the
   // consumer; with load_warps <= stages its previous slab guarantees that.

@@ -102,9 +102,9 @@ typedef struct helix_cfg {
   int probe;     /* tuning instrument, 0 in normal use.  GEMM_F16 / CONV_F16 through a tensor map: bit 0 = the
                     issuing thread skips its tcgen05.mma instructions, bit 1 = the A-side operand is not
                     loaded, bit 2 = the B-side operand is not loaded.  Timing such a launch separates
-                    operand delivery from tensor-core time; its output is meaningless.  Bits 4-5, when not
-                    zero, fix how many ring stages share one arrival barrier (1 -> 1, 2 -> 2, 3 -> 4 stages);
-                    results are not affected                                                        */
+                    operand delivery from tensor-core time; its output is meaningless.  Bit 3 = every ring
+                    stage is released on its own (no pairing of stages per commit); bits 4-6, when not zero,
+                    fix how many ring stages share one arrival barrier; results are not affected by either */
 } helix_cfg_t;
 
 /* A fully described launch; the tagged union the timing entry point iterates. */
