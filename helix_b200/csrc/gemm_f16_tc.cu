@@ -30,6 +30,8 @@
 // Every mbarrier wait is bounded (see mbar_wait); there is no cluster launch and no multicast.
 #include <cuda.h>
 
+#include <type_traits>
+
 #include <algorithm>
 #include <atomic>
 #include <cstring>
@@ -53,6 +55,7 @@ constexpr int kGemmThreads = kGemmProducerWarps * 32 + 32 + 128;  // TMA warps +
 constexpr int kStoreStagingBytes = 4 * 2 * 32 * 128;              // two 32-row x 128-byte boxes per epilogue warp
 constexpr int kEpiBarrier = 1;                                    // named barrier of the 128 epilogue threads
 constexpr int kFwdBarrier = 2;   // named barriers 2..9: arrival of one group of ring stages, forwarded to the MMA warp
+constexpr int kTokBarrier = 10;  // named barriers 10, 11: issue order of two MMA warps that alternate K slabs
 
 enum OutMode { kOutDirect = 0, kOutSplitSlice = 1, kOutStreamSlot = 2 };
 
@@ -83,6 +86,7 @@ struct GemmParams {
   int tma_store;   // whole tiles leave through shared memory and a TMA store (tmap_c is valid)
   int independent; // nothing read or written here is written by the kernel queued just before
   int probe;       // tuning instrument (helix_cfg_t.probe): 1 = issue no MMA, 2 = no A loads, 4 = no B loads
+  int dual;        // 1: two warps issue the MMAs of alternate K slabs (warp 3 joins the MMA warp; needs load_warps <= 2)
   int eshift;      // 1: two consecutive ring stages share one "empty" barrier and one commit of the MMA issuer (0: one each)
   int group;       // ring stages that share one "full" barrier (see the MMA issuer); stages is a multiple of it
   FastDiv fd_grp;
@@ -189,6 +193,117 @@ struct SmemLayout {
   }
 };
 
+// The MMA-issuing role of the one-CTA kernel, walked convergently by a whole warp (all loop state is warp-uniform, waits
+// end in a vote) with one elected lane issuing the tcgen05 instructions: descriptors and barrier addresses then live in
+// uniform registers instead of being moved there per operand from one lane's registers.  DUAL: two warps run this loop
+// and issue alternate slabs (ME = 0 / 1).  Both are compile-time constants of each copy of the loop so that
+// everything it computes stays warp-uniform for the compiler.
+template <int BN, bool CONV, bool DUAL, int ME>
+__device__ __forceinline__ void mma_issue_loop(const GemmParams& p, const int cta, const int grid, const int lane,
+                                               const int stages, uint8_t* sA, uint8_t* sB, uint64_t* full_bar,
+                                               uint64_t* empty_bar, uint64_t* tmem_full, uint64_t* tmem_empty,
+                                               volatile int* abort_flag, const uint32_t tmem_base) {
+  constexpr uint32_t kIdesc = umma_idesc_f16(kBM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int nslab = 0;
+      int gpos = 0, gidx = 0;   // position of the next slab inside its group of stages, and the group
+      // with timeline capture on: where the issuing warp's cycles go, summed over its slabs (barrier wait, fence +
+      // descriptors, the four MMAs, commit, everything between one slab's commit and the next slab's wait)
+      const bool tr = p.trace != nullptr && ME == 0;
+      unsigned int c_wait = 0, c_desc = 0, c_mma = 0, c_commit = 0, c_rest = 0, c_slabs = 0;
+      long long t_prev = 0;
+      WorkItem w;
+      // Without the gathering producer (CONV = 0) the arrival of a group of stages reaches this warp through a
+      // named barrier shared with warp 0; the sequence is then walked to its end even after a failed wait
+      // (ok = false: nothing is issued any more, only the rendezvous are kept).
+      constexpr bool kForward = !CONV;
+      for (int idx = 0; (kForward || ok) && get_item(p, cta, grid, idx, w); ++idx) {
+        const int acc = idx & 1;
+        const uint32_t acc_phase = (idx >> 1) & 1;
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status));
+        if (!ok && !kForward) break;
+        tc_fence_after_sync();
+        if (lane == 0 && ME == 0) trace_mark(p, idx, 2);
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          // One wait per group of stages: reading shared memory (the barrier) costs the issuing warp some 200
+          // cycles on top of the 45 it needs to hand one MMA to the tensor core, more than a 64-deep slab
+          // of a narrow tile keeps the tensor core busy.  The stages are still released one by one.
+          const long long t0 = tr ? clock64() : 0;
+          if (tr && kb > w.kb0) c_rest += (unsigned int)(t0 - t_prev);
+          if (gpos == 0) {
+            if (kForward) {
+              named_bar_sync(kFwdBarrier + gidx, DUAL ? 96 : 64);
+            } else {
+              ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[gidx], phase, abort_flag, p.status));
+              if (!ok) break;
+            }
+            // The whole group is in shared memory now: one ordering point serves all its slabs.  The gathered A
+            // tiles were written through the generic proxy (cp.async); those writes, visible through the
+            // barrier, are ordered before the tensor core's async-proxy reads.
+            if (CONV) fence_proxy_async_smem();
+            tc_fence_after_sync();
+          }
+          if (++gpos == p.group) { gpos = 0; ++gidx; }
+          const long long t1 = tr ? clock64() : 0;
+          // Two issuing warps alternate slabs (slab n belongs to warp n & 1); the order of their MMAs is fixed by a
+          // token: the owner of slab n - 1 arrives at a named barrier after issuing, fenced, and the owner of slab n
+          // meets it there before issuing.  While one warp's MMAs queue for the tensor pipe, the other does its
+          // descriptors, commit and rendezvous.
+          const int n = nslab++;
+          const bool mine = !DUAL || (n & 1) == ME;
+          long long t2 = 0, t3 = 0;
+          if (mine) {
+          if (lane == 0) trace_slab(p, 1, n);
+          const uint64_t da = umma_desc_sw128(smem_u32(sA + (size_t)stage * kATileBytes));
+          const uint64_t db = umma_desc_sw128(smem_u32(sB + (size_t)stage * SmemLayout<BN>::kBTileBytes));
+          if (DUAL && n > 0) {   // everything but the MMAs themselves is done before the token is awaited
+            named_bar_sync(kTokBarrier + ((n - 1) & 1), 64);
+            tc_fence_after_sync();
+          }
+          t2 = tr ? clock64() : 0;
+          if (ok && !(p.probe & 1)) {
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k) {
+              // advancing 16 halves = 32 bytes along K inside the swizzle atom: +2 in the address field
+              umma_f16_ss_elect(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kb > w.kb0) || (k > 0));
+            }
+          }
+          t3 = tr ? clock64() : 0;
+          if (DUAL) {   // hand the token on (the other warp meets it before its next slab, or after its loop)
+            tc_fence_before_sync();
+            asm volatile("bar.arrive %0, 64;" ::"r"(kTokBarrier + (n & 1)) : "memory");
+          }
+          // release the stage -- or, with paired stages, both stages of the pair after its second slab
+          if (ok && ((stage & p.eshift) == p.eshift)) umma_commit_elect(&empty_bar[stage >> p.eshift]);
+          }   // mine
+          if (++stage == stages) { stage = 0; phase ^= 1; gidx = 0; }
+          if (tr && mine) {
+            t_prev = clock64();
+            c_wait += (unsigned int)(t1 - t0);
+            c_desc += (unsigned int)(t2 - t1);
+            c_mma += (unsigned int)(t3 - t2);
+            c_commit += (unsigned int)(t_prev - t3);
+            ++c_slabs;
+          }
+        }
+        if (ok) umma_commit_elect(&tmem_full[acc]);      // dual: both warps, each for its own MMAs (count 2)
+        if (lane == 0 && ME == 0) trace_mark(p, idx, 3);
+      }
+      // the token of the last slab is met by the warp that did not issue it, so that no arrival is left over
+      if (DUAL && nslab > 0 && ((nslab - 1) & 1) != ME) named_bar_sync(kTokBarrier + ((nslab - 1) & 1), 64);
+      // the sequence ended on the first stage of a pair: release the pair for the producers' padding arrivals
+      if (ok && p.eshift && (stage & 1)) umma_commit_elect(&empty_bar[stage >> 1]);
+      if (tr && lane == 0) {
+        unsigned long long* h = p.trace + (size_t)cta * kTraceWords;
+        h[5] = (unsigned long long)c_wait | ((unsigned long long)c_desc << 32);
+        h[6] = (unsigned long long)c_mma | ((unsigned long long)c_commit << 32);
+        h[7] = (unsigned long long)c_slabs | ((unsigned long long)c_rest << 32);
+      }
+}
+
 template <int BN, bool CONV>
 __global__ void __launch_bounds__(CONV ? kConvThreads : kGemmThreads, 1)
 gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -238,7 +353,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_full[a], p.dual ? 2 : 1);
       mbar_init(&tmem_empty[a], 4);
     }
     *abort_flag = 0;
@@ -271,7 +386,19 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   if (!p.independent) griddep_wait();
   if (threadIdx.x == 0 && p.trace != nullptr) p.trace[(size_t)cta * kTraceWords + 2] = (unsigned long long)clock64();
 
-  if (warp < kProducerWarps) {
+  // the MMA-issuing role: warp kMmaWarp, and with dual issue also warp 3, which then issues no loads
+  const bool second_issuer = !CONV && p.dual && warp == 3;
+  if (warp == kMmaWarp) {
+    if (!CONV && p.dual)
+      mma_issue_loop<BN, CONV, true, 0>(p, cta, grid, lane, stages, sA, sB, full_bar, empty_bar, tmem_full, tmem_empty,
+                                        abort_flag, tmem_base);
+    else
+      mma_issue_loop<BN, CONV, false, 0>(p, cta, grid, lane, stages, sA, sB, full_bar, empty_bar, tmem_full, tmem_empty,
+                                         abort_flag, tmem_base);
+  } else if (second_issuer) {
+    mma_issue_loop<BN, CONV, !CONV, 1>(p, cta, grid, lane, stages, sA, sB, full_bar, empty_bar, tmem_full, tmem_empty,
+                                       abort_flag, tmem_base);
+  } else if (warp < kProducerWarps) {
     // ------------------------------------------------------------------ producers
     if (!CONV) {
       // Producer warp j requests the K slabs n = j, j + load_warps, ... of the CTA's slab sequence
@@ -296,7 +423,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           for (int kb = w.kb0; kb < w.kb1; ++kb) {
             if (gpos == 0) {
               if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[gidx], phase, abort_flag, p.status));
-              named_bar_sync(kFwdBarrier + gidx, 64);
+              named_bar_sync(kFwdBarrier + gidx, p.dual ? 96 : 64);
             }
             if (++gpos == p.group) { gpos = 0; ++gidx; }
             if (++stage == stages) { stage = 0; phase ^= 1; gidx = 0; }
@@ -471,93 +598,6 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         if (threadIdx.x == 0) trace_mark(p, idx, 1);
       }
       cp_async_wait<0>();  // nothing of this thread's is in flight when the CTA tears down
-    }
-  } else if (warp == kMmaWarp) {
-    // ------------------------------------------------------------------ MMA issuer
-    // The whole warp walks the loop convergently (all loop state is warp-uniform, waits end in a vote) and one
-    // elected lane issues the tcgen05 instructions: descriptors and barrier addresses then live in uniform
-    // registers instead of being moved there per operand from one lane's registers.
-    {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      int nslab = 0;
-      int gpos = 0, gidx = 0;   // position of the next slab inside its group of stages, and the group
-      // with timeline capture on: where the issuing warp's cycles go, summed over its slabs (barrier wait, fence +
-      // descriptors, the four MMAs, commit, everything between one slab's commit and the next slab's wait)
-      const bool tr = p.trace != nullptr;
-      unsigned int c_wait = 0, c_desc = 0, c_mma = 0, c_commit = 0, c_rest = 0, c_slabs = 0;
-      long long t_prev = 0;
-      WorkItem w;
-      // Without the gathering producer (CONV = 0) the arrival of a group of stages reaches this warp through a
-      // named barrier shared with warp 0; the sequence is then walked to its end even after a failed wait
-      // (ok = false: nothing is issued any more, only the rendezvous are kept).
-      constexpr bool kForward = !CONV;
-      for (int idx = 0; (kForward || ok) && get_item(p, cta, grid, idx, w); ++idx) {
-        const int acc = idx & 1;
-        const uint32_t acc_phase = (idx >> 1) & 1;
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status));
-        if (!ok && !kForward) break;
-        tc_fence_after_sync();
-        if (lane == 0) trace_mark(p, idx, 2);
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = w.kb0; kb < w.kb1; ++kb) {
-          // One wait per group of stages: reading shared memory (the barrier) costs the issuing warp some 200
-          // cycles on top of the 45 it needs to hand one MMA to the tensor core, more than a 64-deep slab
-          // of a narrow tile keeps the tensor core busy.  The stages are still released one by one.
-          const long long t0 = tr ? clock64() : 0;
-          if (tr && kb > w.kb0) c_rest += (unsigned int)(t0 - t_prev);
-          if (gpos == 0) {
-            if (kForward) {
-              named_bar_sync(kFwdBarrier + gidx, 64);
-            } else {
-              ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[gidx], phase, abort_flag, p.status));
-              if (!ok) break;
-            }
-            // The whole group is in shared memory now: one ordering point serves all its slabs.  The gathered A
-            // tiles were written through the generic proxy (cp.async); those writes, visible through the
-            // barrier, are ordered before the tensor core's async-proxy reads.
-            if (CONV) fence_proxy_async_smem();
-            tc_fence_after_sync();
-          }
-          if (++gpos == p.group) { gpos = 0; ++gidx; }
-          const long long t1 = tr ? clock64() : 0;
-          if (lane == 0) trace_slab(p, 1, nslab);
-          ++nslab;
-          const uint64_t da = umma_desc_sw128(smem_u32(sA + (size_t)stage * kATileBytes));
-          const uint64_t db = umma_desc_sw128(smem_u32(sB + (size_t)stage * L::kBTileBytes));
-          const long long t2 = tr ? clock64() : 0;
-          if (ok && !(p.probe & 1)) {
-#pragma unroll
-            for (int k = 0; k < kBK / 16; ++k) {
-              // advancing 16 halves = 32 bytes along K inside the swizzle atom: +2 in the address field
-              umma_f16_ss_elect(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kb > w.kb0) || (k > 0));
-            }
-          }
-          const long long t3 = tr ? clock64() : 0;
-          // release the stage -- or, with paired stages, both stages of the pair after its second slab
-          if (ok && ((stage & p.eshift) == p.eshift)) umma_commit_elect(&empty_bar[stage >> p.eshift]);
-          if (++stage == stages) { stage = 0; phase ^= 1; gidx = 0; }
-          if (tr) {
-            t_prev = clock64();
-            c_wait += (unsigned int)(t1 - t0);
-            c_desc += (unsigned int)(t2 - t1);
-            c_mma += (unsigned int)(t3 - t2);
-            c_commit += (unsigned int)(t_prev - t3);
-            ++c_slabs;
-          }
-        }
-        if (ok) umma_commit_elect(&tmem_full[acc]);
-        if (lane == 0) trace_mark(p, idx, 3);
-      }
-      // the sequence ended on the first stage of a pair: release the pair for the producers' padding arrivals
-      if (ok && p.eshift && (stage & 1)) umma_commit_elect(&empty_bar[stage >> 1]);
-      if (tr && lane == 0) {
-        unsigned long long* h = p.trace + (size_t)cta * kTraceWords;
-        h[5] = (unsigned long long)c_wait | ((unsigned long long)c_desc << 32);
-        h[6] = (unsigned long long)c_mma | ((unsigned long long)c_commit << 32);
-        h[7] = (unsigned long long)c_slabs | ((unsigned long long)c_rest << 32);
-      }
     }
   } else {
     // ------------------------------------------------------------------ epilogue
@@ -1384,6 +1424,10 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
   // consumer; with load_warps <= stages its previous slab guarantees that.
   p.load_warps = std::max(1, std::min({cfg.load_group > 0 ? cfg.load_group : 2, kGemmProducerWarps - 1,
                                        p.stages}));
+  // Two MMA-issuing warps (warp 3 joins warp 4) where warp 3 issues no loads; stages are then released one by one,
+  // each by the warp that read it.  Probe bit 7 asks for it.
+  p.dual = (!conv && (cfg.probe & 0x80) && p.load_warps <= 2) ? 1 : 0;
+  if (p.dual) p.eshift = 0;
   p.swap = cfg.swap_ab ? 1 : 0;
   p.C = static_cast<__half*>(C);
   p.ldc = ldc;

@@ -104,7 +104,9 @@ typedef struct helix_cfg {
                     loaded, bit 2 = the B-side operand is not loaded.  Timing such a launch separates
                     operand delivery from tensor-core time; its output is meaningless.  Bit 3 = every ring
                     stage is released on its own (no pairing of stages per commit); bits 4-6, when not zero,
-                    fix how many ring stages share one arrival barrier; results are not affected by either */
+                    fix how many ring stages share one arrival barrier; bit 7 = two warps issue the MMAs
+                    of alternate K slabs (one-CTA kernel with at most two loading warps; measured 4-8 %
+                    faster on tiles up to 128 wide, not a default); results are not affected by these   */
 } helix_cfg_t;
 
 /* A fully described launch; the tagged union the timing entry point iterates. */

@@ -374,3 +374,19 @@ def test_an_independent_launch_does_not_break_the_order_of_its_neighbours(oracle
         torch.cuda.synchronize()
         assert torch.equal(c2, want), trial
     ops.check_status()
+
+
+@pytest.mark.parametrize("shape,bn", [((300, 200, 520), 64), ((1024, 768, 2048), 128), ((512, 1024, 4096), 256)])
+def test_two_issuing_warps_give_the_same_bits(shape, bn):
+    """probe bit 7: two warps issue the MMAs of alternate K slabs, their order fixed by a token that travels through
+    two named barriers; the accumulation order, hence every bit of the result, is that of the single issuer."""
+    M, N, K = shape
+    a = torch.randn((M, K), device="cuda", dtype=torch.float16) / K ** 0.5
+    b = torch.randn((N, K), device="cuda", dtype=torch.float16) / K ** 0.5
+    one = ops.gemm_f16(a, b, cfg=ops.make_cfg(OP_GEMM_F16, 128, bn, 64))
+    two = ops.gemm_f16(a, b, cfg=ops.make_cfg(OP_GEMM_F16, 128, bn, 64, probe=0x80))
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(one, two)
+    ref = a.float() @ b.float().T
+    assert float((two.float() - ref).norm() / ref.norm()) < 2e-3
