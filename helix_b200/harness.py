@@ -480,10 +480,37 @@ def run_shape_list(units, worker, prof_dict, gpus=1, predicted=None, journal=Non
 
 # ----------------------------------------------------------------------------- vendor comparators (context only)
 def time_torch(fn, iters=20):
+    """Seconds per call of a torch operation: `iters` calls captured in a CUDA graph and replayed (so that a
+    vendor kernel of a few microseconds is not rated by the host's launch rate); eager calls if capture fails."""
     for _ in range(3):
         fn()
     torch.cuda.synchronize()
+    graph = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(iters):
+                fn()
+        graph = g
+    except Exception:
+        graph = None
+        torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if graph is not None:
+        graph.replay()
+        torch.cuda.synchronize()
+        reps = 3
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / (iters * reps)
     e0.record()
     for _ in range(iters):
         fn()
