@@ -334,11 +334,6 @@ __device__ __forceinline__ void griddep_launch_dependents() { asm volatile("grid
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ---------------------------------------------------------------- misc loads
-// Ask the L2 to fetch `bytes` from global memory (16-byte aligned address, a multiple of 16 bytes); no register or
-// shared memory receives anything, the thread does not wait.
-__device__ __forceinline__ void prefetch_l2_bulk(const void* p, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ uint4 ldg_stream_16(const void* p) {
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"

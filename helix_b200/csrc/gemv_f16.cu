@@ -43,18 +43,6 @@ gemv_f16_kernel(const __half* __restrict__ W, int64_t ldw, const __half* __restr
   const int k_begin = ks * k_per_split;
   const int k_end = min(K, k_begin + k_per_split);
 
-  // Mode 1 with a weight matrix that fits the L2 (order_mode 3 = mode 1 plus this): before the kernel waits for
-  // its predecessor, every warp asks the L2 for all the rows it is going to read, so that the HBM transfer of the
-  // weights overlaps the predecessor's tail and this launch's own ramp; after the wait the loads hit the L2.
-  const bool prefetch = order_mode == 3;
-  if (prefetch) order_mode = 1;
-  if (prefetch && lane < RPW && k_end > k_begin) {
-    for (int g = blockIdx.x * warps_per_block + warp; g < row_groups; g += gridDim.x * warps_per_block) {
-      const int row = g * RPW + lane;
-      if (row < rows) prefetch_l2_bulk(W + (int64_t)row * ldw + k_begin, (uint32_t)(k_end - k_begin) * 2u);
-    }
-  }
-
   for (int g = blockIdx.x * warps_per_block + warp; g < row_groups; g += gridDim.x * warps_per_block) {
     const int r0 = g * RPW;
     float acc[RPW][MRHS];
@@ -184,9 +172,7 @@ static int launch_gemv(const __half* W, int64_t ldw, const __half* X, int64_t ld
   k_per_split = (k_per_split + 255) / 256 * 256;
   dim3 grid(blocks, split_k);
   // split-K shares its scratch with neighbouring launches, so it always orders itself after them
-  int indep = split_k == 1 ? independent : 0;
-  // static weights that fit the L2 with room to spare: fetch them into the L2 before waiting for the predecessor
-  if (indep == 1 && (double)rows * K * 2.0 <= 48e6) indep = 3;
+  const int indep = split_k == 1 ? independent : 0;
   cudaLaunchConfig_t lc = {};
   lc.gridDim = grid;
   lc.blockDim = dim3(warps * 32);
