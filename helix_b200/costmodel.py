@@ -116,8 +116,10 @@ def _lone_skinny_time(prof_dict, bn, stages, split, M, N, K, batch, sms):
     return t
 
 
-def gemm_time(prof_dict, key, M, N, K, batch=1, conv=False, overlapped=False):
-    """Predicted seconds of one GEMM launch with configuration `key` (inf if inapplicable)."""
+def gemm_time(prof_dict, key, M, N, K, batch=1, conv=False, overlapped=False, operand_bytes=None):
+    """Predicted seconds of one GEMM launch with configuration `key` (inf if inapplicable).  `operand_bytes`: what the
+    launch really moves when that is not 2 (MK + NK + MN) -- an implicit-GEMM convolution reads every input pixel once,
+    not once per filter tap."""
     stages, tm, bn, group, swap, mode = key
     split = mode if mode in SPLIT_MODES else 1
     if split > 1:
@@ -139,8 +141,16 @@ def gemm_time(prof_dict, key, M, N, K, batch=1, conv=False, overlapped=False):
         if split > 1 and conv != "im2col":
             return float("inf")
         t_slab = max(t_slab, prof_dict.get(("conv_slab_swap" if swap else "conv_slab", bn), t_slab))
+        t_fixed = max(t_fixed, prof_dict.get(("conv_fixed_swap" if swap else "conv_fixed", bn), t_fixed))
     sms = _param(prof_dict, "sm_count", DEFAULT_SMS)
     pm, pn = (N, M) if swap else (M, N)
+    # the library's own rules, which the slab figures cannot express: a tile twice as wide as the problem does the
+    # narrower tile's work at a wider tile's price, and swapping operands only pays when the row count is the skinny
+    # dimension (a convolution's swapped tile is covered above)
+    if bn > 16 and bn // 2 >= pn:
+        return float("inf")
+    if swap and not conv and M > 64:
+        return float("inf")
     if group == 2:
         if conv or swap or mode or pm <= tm or K < 8 * TILE_K:   # short K is epilogue bound: pairs gain nothing
             return float("inf")
@@ -188,7 +198,7 @@ def gemm_time(prof_dict, key, M, N, K, batch=1, conv=False, overlapped=False):
     if group == 2:
         active *= 2
     t = t_fixed + slabs * t_slab + extra
-    bytes_ = 2.0 * batch * (M * K + N * K + M * N)
+    bytes_ = operand_bytes if operand_bytes is not None else 2.0 * batch * (M * K + N * K + M * N)
     if (overlapped and not conv and mode == 0 and split == 1 and not swap and min(M, N) > TILE_M and tiles < sms
             and 2.0 * batch * M * N * K / bytes_ <= ROTATE_INTENSITY):
         # A chain of independent launches over distinct operand sets: a launch that leaves SMs free and
@@ -201,7 +211,6 @@ def gemm_time(prof_dict, key, M, N, K, batch=1, conv=False, overlapped=False):
     # HBM floor: operand bytes at the streaming rate of the SMs that take part
     per_sm = _param(prof_dict, "dram_gbs_per_sm", 40.0) * 1e9
     hbm = _param(prof_dict, "hbm_gbs", 6000.0) * 1e9
-    bytes_ = 2.0 * batch * (M * K + N * K + M * N)
     t_mem = t_fixed + bytes_ / min(hbm, active * per_sm)
     return max(t, t_mem)
 
@@ -222,7 +231,7 @@ def gemv_time(prof_dict, key, rows, K, m):
     return t_fixed + bytes_ * s_per_byte * growth
 
 
-def cost_model(prof_dict, M, N, K, batch=1, conv=False, overlapped=False):
+def cost_model(prof_dict, M, N, K, batch=1, conv=False, overlapped=False, operand_bytes=None):
     """Best configuration key for C[M,N] = A[M,K] * B[N,K]^T; first element 0 means GEMV.
 
     Same call shape as the reference's cost_model(prof_dict, M, N, K)
@@ -238,17 +247,17 @@ def cost_model(prof_dict, M, N, K, batch=1, conv=False, overlapped=False):
             rows, m = (N, M) if M <= N else (M, N)
             t = gemv_time(prof_dict, key, rows, K, m)
         else:
-            t = gemm_time(prof_dict, key, M, N, K, batch, conv, overlapped)
+            t = gemm_time(prof_dict, key, M, N, K, batch, conv, overlapped, operand_bytes)
         if t < best:
             best, best_key = t, key
     return best_key
 
 
-def predicted_time(prof_dict, key, M, N, K, batch=1, conv=False, overlapped=False):
+def predicted_time(prof_dict, key, M, N, K, batch=1, conv=False, overlapped=False, operand_bytes=None):
     if key[0] == 0:
         rows, m = (N, M) if M <= N else (M, N)
         return gemv_time(prof_dict, key, rows, K, m)
-    return gemm_time(prof_dict, key, M, N, K, batch, conv, overlapped)
+    return gemm_time(prof_dict, key, M, N, K, batch, conv, overlapped, operand_bytes)
 
 
 def sgemm_cost_model(prof_dict, M, N, K):

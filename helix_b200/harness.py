@@ -220,9 +220,12 @@ def profile_fp16(fast=False, progress=None):
         waves = -(-196 * max(1, 1) // sms)
         t1 = time_conv_f16(32, 64, 28, 28, bn, 3, 3, 1, 1, ccfg); tick()
         t2 = time_conv_f16(32, 256, 28, 28, bn, 3, 3, 1, 1, ccfg); tick()
-        d[("conv_slab", bn)] = _two_point(t1, waves * 9, t2, waves * 36)[1]
+        fx, sl = _two_point(t1, waves * 9, t2, waves * 36)
+        d[("conv_slab", bn)] = sl
+        d[("conv_fixed", bn)] = float(fx)      # launch, im2col set-up and epilogue of a convolution launch
     if fast:
         d[("conv_slab", 128)] = 0.5 * (d[("conv_slab", 64)] + d[("conv_slab", 256)])
+        d[("conv_fixed", 128)] = 0.5 * (d[("conv_fixed", 64)] + d[("conv_fixed", 256)])
     # swapped convolution tiles (output channels on the 128 rows, bn pixels per im2col box): slope per slab on
     # 128 output channels, 28 x 28, batch 32 (25088 pixels)
     for bn in ((256,) if fast else (256, 128)):
@@ -230,7 +233,9 @@ def profile_fp16(fast=False, progress=None):
         waves = -(-(-(-25088 // bn)) // sms)
         t1 = time_conv_f16(32, 64, 28, 28, 128, 3, 3, 1, 1, ccfg); tick()
         t2 = time_conv_f16(32, 256, 28, 28, 128, 3, 3, 1, 1, ccfg); tick()
-        d[("conv_slab_swap", bn)] = _two_point(t1, waves * 9, t2, waves * 36)[1]
+        fx, sl = _two_point(t1, waves * 9, t2, waves * 36)
+        d[("conv_slab_swap", bn)] = sl
+        d[("conv_fixed_swap", bn)] = float(fx)
     # split-K: what the slot round trip and the last arriver's sum add, from two slice counts on a quarter-wave
     # problem: t - (fixed + slabs * slab) = a + b * S
     for bn in wide:
@@ -368,8 +373,9 @@ def conv_f16_result(prof_dict, batch, IC, H, W, OC, kH, kW, stride, pad):
     C = (IC + 7) // 8 * 8
     im2col = C % 64 == 0 and batch * H * W * C * 2 >= 131072 and stride <= 8      # the library's tensor-map rule
     # the convolution harness times one buffer set with ordered launches: a lone launch
+    real_bytes = 2.0 * (batch * H * W * C + OC * kH * kW * C + M * N)        # x, w and y once each
     key = costmodel.cost_model(prof_dict, M, N, (K + 7) // 8 * 8, 1,
-                               conv=False if as_gemm else ("im2col" if im2col else True))
+                               conv=False if as_gemm else ("im2col" if im2col else True), operand_bytes=real_bytes)
     if key is None or key[0] == 0:
         key = (costmodel.max_stages(128), 128, 128, 1, 0, 0)
     t = time_conv_f16(batch, IC, H, W, OC, kH, kW, stride, pad, key_to_cfg(key, conv=True, prof_dict=prof_dict))
