@@ -169,7 +169,10 @@ def gemm_time(prof_dict, key, M, N, K, batch=1, conv=False, overlapped=False, op
         bytes_ = 2.0 * batch * (M * K + N * K + M * N)
         slab_bytes = (min(M, tm) + bn) * TILE_K * 2.0
         # the HBM rate grows a little with the number of streaming CTAs (measured 4.6 TB/s with 16..43, 5.6 with 148)
-        hbm = _param(prof_dict, "hbm_wide_gbs", 5300.0) * 1e9 * (0.8 + 0.2 * min(tiles, sms) / sms)
+        wide = _param(prof_dict, "hbm_wide_gbs", 5300.0)
+        if bn < 256:     # narrower boxes: their own measured rate where the profile has it
+            wide = prof_dict.get(("hbm_wide_gbs", bn), 0.85 * wide)
+        hbm = wide * 1e9 * (0.8 + 0.2 * min(tiles, sms) / sms)
         t_hbm = bytes_ / hbm
         t_cta = -(-tiles // sms) * nkb * slab_bytes / (_param(prof_dict, "wide_gbs_per_sm", 400.0) * 1e9)
         # every CTA pulls the same A rows: those lines are a hot spot in L2, which then delivers

@@ -188,6 +188,10 @@ def profile_fp16(fast=False, progress=None):
     t = time_gemm_f16(16, 256 * sms, 4096, cfg(256)); tick()
     d[("hbm_wide_gbs",)] = float(2.0 * (16 * 4096 + 256 * sms * 4096 + 16 * 256 * sms) /
                                   max(t - d[("skinny_fixed",)], 1e-9) / 1e9)
+    # the same stream through 128-row boxes (twice the tensor copies per byte): measurably slower
+    t = time_gemm_f16(16, 256 * sms, 4096, cfg(128)); tick()
+    d[("hbm_wide_gbs", 128)] = float(2.0 * (16 * 4096 + 256 * sms * 4096 + 16 * 256 * sms) /
+                                      max(t - d[("skinny_fixed",)], 1e-9) / 1e9)
     skinny = {}
     for bn in ((16,) if fast else (32, 16)):          # skinny M on the UMMA N axis: everything streams from DRAM
         N = 128 * sms
