@@ -1165,6 +1165,24 @@ static void default_config_impl(int M, int N, int K, int batch, int sm_count, bo
   // lone launches: 16 x 11008 x 4096 31 -> 24 us, 128 x 4096 x 11008 73 -> 29 us, 64 x 4096 x 4096 25 -> 16 us.
   // (Launches on distinct buffers that overlap on idle SMs do best with the widest tile and no split: 16-18 us.)
   if (!conv && M <= kBM && N >= 1024 && num_kb >= 8) {
+    // Measured lone launches (one buffer set, ordered), best configuration of a survey of tile widths, operand swap,
+    // split-K and stream-K: up to 32 rows -- the rows on the UMMA N axis (16 or 32 wide), weights on the 128-row axis,
+    // every CTA streaming an equal share of all K slabs (stream-K): 16 x 11008 x 4096 18.5 us (24.4 unswapped at
+    // 128 wide), 8 x 11008 x 4096 19.0 (35.7), 32 x 8192 x 8192 32.2 (45.8); above 64 rows -- 128-wide tiles with
+    // stream-K: 128 x 4096 x 11008 28.6 us (29.3 with split-K over 4, 57 whole tiles).  In between, the model below.
+    if (M <= 32 && batch == 1) {
+      out->swap_ab = 1;
+      out->tile_n = M <= 16 ? 16 : 32;
+      out->stream_k = 1;
+      out->stages = max_stages(out->tile_n, false);
+      return;
+    }
+    if (M > 64 && batch == 1 && num_kb >= 64 && (N + 127) / 128 >= 16 && (int64_t)((N + 127) / 128) < sm_count) {
+      out->tile_n = 128;
+      out->stream_k = 1;
+      out->stages = max_stages(128, false);
+      return;
+    }
     const double b_bytes = 2.0 * batch * (double)N * K, a_bytes = 2.0 * batch * (double)M * K;
     const double live = std::min(4, (std::min(M, kBM) + 31) / 32) / 4.0;
     double best_t = 1e30;
