@@ -1424,10 +1424,12 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
   const int smax = max_stages(bn, conv);
   p.stages = cfg.stages > 0 ? std::min(cfg.stages, smax) : smax;
   if (p.stages < (conv ? 3 : 2)) return HELIX_ERR_UNSUPPORTED;
-  // stages per "full" barrier: four for narrow tiles (eight stages fit), two otherwise; at least two groups
+  // stages per "full" barrier: four for narrow tiles (eight stages fit), two at 128 wide, one at 256; at least two groups
   p.group = 1;
   if (!conv) {
-    p.group = (bn <= 64 && p.stages >= 8) ? 4 : (p.stages >= 6 ? 3 : (p.stages >= 4 ? 2 : 1));
+    // measured with the forwarded arrivals (8192 x 2048 x 4096, microseconds): 64 wide 215.7 / 212.5 at 2 / 4 stages
+    // per group; 128 wide 132.9 / 132.7 / 136.5 at 1 / 2 / 3; 256 wide 112.0 / 115.2 at 1 / 2
+    p.group = (bn <= 64 && p.stages >= 8) ? 4 : (bn <= 128 && p.stages >= 4 ? 2 : 1);
     if ((cfg.probe >> 4) & 7) p.group = (cfg.probe >> 4) & 7;   // tuning override
     while (p.group > 1 && p.stages / p.group < 2) --p.group;
     p.stages = p.stages / p.group * p.group;
