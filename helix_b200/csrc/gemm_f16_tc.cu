@@ -86,6 +86,8 @@ struct GemmParams {
   int tma_store;   // whole tiles leave through shared memory and a TMA store (tmap_c is valid)
   int independent; // nothing read or written here is written by the kernel queued just before
   int probe;       // tuning instrument (helix_cfg_t.probe): 1 = issue no MMA, 2 = no A loads, 4 = no B loads
+  int m64;         // 1: the 128-row axis holds at most 64 rows in all (swapped operands, direct output): the MMAs run with
+                   //    M = 64 -- half the pipe time -- and row r of the tile sits in TMEM lane (r / 16) * 32 + r % 16
   int dual;        // 1: two warps issue the MMAs of alternate K slabs (warp 3 joins the MMA warp; needs load_warps <= 2)
   int eshift;      // 1: two consecutive ring stages share one "empty" barrier and one commit of the MMA issuer (0: one each)
   int group;       // ring stages that share one "full" barrier (see the MMA issuer); stages is a multiple of it
@@ -203,7 +205,7 @@ __device__ __forceinline__ void mma_issue_loop(const GemmParams& p, const int ct
                                                const int stages, uint8_t* sA, uint8_t* sB, uint64_t* full_bar,
                                                uint64_t* empty_bar, uint64_t* tmem_full, uint64_t* tmem_empty,
                                                volatile int* abort_flag, const uint32_t tmem_base) {
-  constexpr uint32_t kIdesc = umma_idesc_f16(kBM, BN);
+  const uint32_t kIdesc = p.m64 ? umma_idesc_f16(64, BN) : umma_idesc_f16(kBM, BN);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -616,7 +618,9 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       tc_fence_after_sync();
       if (quarter == 0 && lane == 0) trace_mark(p, idx, 4);
       const int trow = quarter * 32 + lane;      // row inside the tile
-      const int row = w.m_blk * kBM + trow;      // index on the 128-row (A side) axis
+      // index on the 128-row (A side) axis; an M = 64 accumulator keeps row r in lane (r / 16) * 32 + r % 16, i.e. the
+      // lower 16 lanes of each warp's quarter hold rows 16 * quarter ... (measured layout), the upper 16 nothing
+      const int row = p.m64 ? (lane < 16 ? quarter * 16 + lane : p.PM) : w.m_blk * kBM + trow;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
       // 64 columns of this warp's 32 rows, rounded once to fp16, through the warp's swizzled 32 x 128-byte
       // staging box and one TMA store (full 128-byte lines, edges clipped by the tensor map); two boxes per
@@ -1449,6 +1453,8 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
   p.dual = (!conv && (cfg.probe & 0x80) && p.load_warps <= 2) ? 1 : 0;
   if (p.dual) p.eshift = 0;
   p.swap = cfg.swap_ab ? 1 : 0;
+  // at most 64 rows on the 128-row axis, swapped operands, whole tiles written directly: M = 64 MMAs (probe bit 8: off)
+  p.m64 = (p.swap && p.PM <= 64 && bn >= 32 && !cfg.stream_k && cfg.split_k <= 1 && !(cfg.probe & 0x100)) ? 1 : 0;
   p.C = static_cast<__half*>(C);
   p.ldc = ldc;
   p.stride_c = sc;

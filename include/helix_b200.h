@@ -106,7 +106,8 @@ typedef struct helix_cfg {
                     stage is released on its own (no pairing of stages per commit); bits 4-6, when not zero,
                     fix how many ring stages share one arrival barrier; bit 7 = two warps issue the MMAs
                     of alternate K slabs (one-CTA kernel with at most two loading warps; measured 4-8 %
-                    faster on tiles up to 128 wide, not a default); results are not affected by these   */
+                    faster on tiles up to 128 wide, not a default); bit 8 = swapped tiles with at most 64
+                    rows keep M = 128 MMAs instead of M = 64; results are not affected by these         */
 } helix_cfg_t;
 
 /* A fully described launch; the tagged union the timing entry point iterates. */
