@@ -28,7 +28,10 @@ METRIC = "fp16_gemm_conv_sweep_tflops"
 UNIT = "TFLOP/s"
 INSTANCES = 8        # copies of the model-level sweep in the work list
 PASSES = 6           # passes over the list per step
-WORKLOAD = ("model-level sweep: BERT-base b16 s512 (72 GEMMs incl. batched QK^T/PV) + ResNet-50 b32 224x224 "
+
+
+def workload_text():
+    return ("model-level sweep: BERT-base b16 s512 (72 GEMMs incl. batched QK^T/PV) + ResNet-50 b32 224x224 "
             "(53 convs), work list = %d seeded copies (%d units)" % (INSTANCES, INSTANCES * 125))
 
 
@@ -124,7 +127,7 @@ def bench_reference(args, rank, world):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": avg * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "step": "one pass over one copy of the sweep (1/%d of the list, every "
+        "config": {"workload": workload_text(), "step": "one pass over one copy of the sweep (1/%d of the list, every "
                                                   "distinct unit in its real count)" % INSTANCES},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
                          "gflops_per_core": value * 1e3 / cores, "sample": cpu.sample_text(avg)},
@@ -379,9 +382,9 @@ SWEEP_DRAM_BYTES_PER_LAUNCH = {
 
 
 def kernel_breakdown(sw, ops, limit_units=125):
-    """Time the launches of one copy of the sweep grouped by the kernel they resolve to (CUDA-graph replay,
-    events on the launching stream, each group alone on the whole machine): launches, seconds and algorithmic
-    flop / bytes per group."""
+    """Time the launches of one copy of the sweep grouped by the kernel they resolve to in the sweep (CUDA-graph
+    replay, events on the launching stream, each group alone on the whole machine with the sweep's own tile
+    choice): launches, seconds and algorithmic flop / bytes per group."""
     from helix_b200 import workloads
     import ctypes
     import torch
@@ -390,6 +393,12 @@ def kernel_breakdown(sw, ops, limit_units=125):
     for u, l0 in list(zip(sw.units, sw.launches))[:limit_units]:
         l = Launch()
         ctypes.memmove(ctypes.byref(l), ctypes.byref(l0), ctypes.sizeof(Launch))
+        # the kernel and tile the sweep really launches for this unit (chosen for its share of the SMs), made
+        # explicit, then given the whole machine: the groups carry the names a profiler sees in the sweep
+        if not (l.cfg.tile_m or l.cfg.tile_n):
+            chosen = ops.default_config(l)
+            chosen.max_ctas = l.cfg.max_ctas
+            l.cfg = chosen
         ops.limit_ctas(l, 0)
         g = groups.setdefault(ops.kernel_name(l), {"launches": [], "flop": 0.0, "bytes": 0.0})
         g["launches"].append(l)
@@ -594,7 +603,7 @@ def bench_helix(args, rank, world, local_rank):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16 in / f32 accumulate", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "step": "%d passes over the work list (%.2f TFLOP per pass)" % (args.passes, total_flops / 1e12),
+        "config": {"workload": workload_text(), "step": "%d passes over the work list (%.2f TFLOP per pass)" % (args.passes, total_flops / 1e12),
                    "units_this_rank": len(mine), "cache": "operands of one pass on rank 0 total %.1f GB (> L2), one buffer set per unit" % (sw.bytes / 1e9),
                    "cuda_graph": graph is not None,
                    "parallelism": "fixed work list partitioned over %d GPU(s) by LPT on a roofline estimate; no collective" % world,
@@ -647,6 +656,7 @@ def bench_helix(args, rank, world, local_rank):
 
 
 def main():
+    global INSTANCES
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -655,8 +665,11 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the per-configuration table and the CPU pass")
     ap.add_argument("--lanes", type=int, default=2, help="independent units run in this many concurrent chains per GPU")
     ap.add_argument("--passes", type=int, default=PASSES, help="passes over the work list per step")
+    ap.add_argument("--instances", type=int, default=INSTANCES,
+                    help="seeded copies of the sweep in the work list (default 8; 1 keeps a profiler run small)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
+    INSTANCES = max(1, args.instances)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
