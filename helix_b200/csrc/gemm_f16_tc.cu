@@ -19,8 +19,8 @@
 //     evenly to all CTAs, so that every SM stays busy whatever the tile count (one SM cannot
 //     pull more than about 1/148 of the HBM bandwidth, so memory-bound shapes need all of them);
 //   * epilogue warps read TMEM with tcgen05.ld, round once to fp16 and store to global memory;
-//     partial K ranges are stored as fp32 slots; split-K slices and stream-K ranges are summed, in slice or CTA
-//     order (deterministic), by the CTA that brings a tile's last contribution;
+//     partial K ranges are stored as fp32 slots; split-K slices are summed in slice order by the CTA that
+//     completes a tile last, stream-K ranges by a small second kernel (both deterministic);
 //   * swap_ab puts the large N extent on the 128-row UMMA axis when M is skinny.
 // For convolution the A-side tile is gathered by 8 producer warps with 16-byte zero-filling
 // cp.async (8 lanes per output pixel, K axis ordered (r, s, c)), written in the same swizzled
@@ -183,7 +183,6 @@ __device__ __forceinline__ bool get_item(const GemmParams& p, int cta, int grid,
   const bool whole = (w.kb0 == 0 && w.kb1 == p.num_kb);
   w.mode = whole ? kOutDirect : kOutStreamSlot;
   w.aux = 2 * cta + s;
-  w.tile = j;        // dealt-out tile index: names the tile's arrival counter
   return true;
 }
 
@@ -772,27 +771,9 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         // by side -- so every store and every load of a warp covers 512 contiguous bytes.
         const int64_t slot_idx = w.mode == kOutStreamSlot ? (int64_t)w.aux : (int64_t)w.tile * p.split_k + w.aux;
         float* slot = p.partial + slot_idx * (kBM * BN) + ((size_t)quarter * (BN / 4) * 32 + lane) * 4;
-        // A warp whose 32 rows all lie beyond the matrix (M = 16: three of the four) has nothing to add to the
-        // sum: it neither stores nor sums its part of the slots.
-        const bool live = w.m_blk * kBM + quarter * 32 < p.PM;
-        // Who contributes to this tile, and where their slots are.  Split-K: the tile's split_k slices, slot
-        // tile * split_k + slice.  Stream-K: the CTAs c_lo..c_hi whose slab ranges meet the tile's; a CTA's range
-        // touches at most two tiles (slots 2c and 2c + 1), and only the first contributor can have started in the
-        // previous tile.
-        int n_contrib, first_slot, next_slot, slot_step;
-        if (w.mode == kOutSplitSlice) {
-          n_contrib = p.split_k;
-          first_slot = w.tile * p.split_k;
-          next_slot = first_slot + 1;
-          slot_step = 1;
-        } else {
-          const int u_lo = w.tile * p.num_kb, u_hi = u_lo + p.num_kb;
-          const int c_lo = u_lo / p.sk_upc, c_hi = (u_hi - 1) / p.sk_upc;
-          n_contrib = c_hi - c_lo + 1;
-          first_slot = 2 * c_lo + (c_lo * p.sk_upc < u_lo ? 1 : 0);
-          next_slot = 2 * (c_lo + 1);
-          slot_step = 2;
-        }
+        // A warp whose 32 rows all lie beyond the matrix (M = 16: three of the four) has nothing to add to a
+        // split-K sum: it neither stores nor sums its part of the slots.
+        const bool live = w.mode != kOutSplitSlice || w.m_blk * kBM + quarter * 32 < p.PM;
 #pragma unroll 1
         for (int c0 = 0; live && c0 < BN; c0 += kChunk) {
           uint32_t r[kChunk];
@@ -808,9 +789,9 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-        {
-          // The CTA that brings a tile's last contribution adds the contributors' slots in slice (or CTA) order
-          // (a fixed order whoever comes last, so the result is deterministic), rounds once and writes C.
+        if (w.mode == kOutSplitSlice) {
+          // The CTA that completes a tile's last K slice adds the slices' slots in slice order (a fixed
+          // order whoever comes last, so the result is deterministic), rounds once and writes C.
           // The counter needs no clearing: its upper half names the launch that last used it, a stale one
           // restarts at one arrival, and the CTA that completes a tile leaves the count at zero so that a
           // replay of the same launch (a CUDA graph) starts afresh.
@@ -821,29 +802,27 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(ctr), want;
             while (true) {
               const unsigned int arrivals = (unsigned int)(seen >> 32) == p.epoch ? (unsigned int)seen + 1u : 1u;
-              want = ((unsigned long long)p.epoch << 32) | (arrivals == (unsigned int)n_contrib ? 0u : arrivals);
+              want = ((unsigned long long)p.epoch << 32) | (arrivals == (unsigned int)p.split_k ? 0u : arrivals);
               const unsigned long long old = atomicCAS(ctr, seen, want);
               if (old == seen) { *red_flag = (int)arrivals; break; }
               seen = old;
             }
           }
           named_bar_sync(kEpiBarrier, 128);
-          if (*red_flag == n_contrib && live) {
+          if (*red_flag == p.split_k && live) {
             __threadfence();
-            const float* lane_base = p.partial + ((size_t)quarter * (BN / 4) * 32 + lane) * 4;
-            auto slot_of = [&](int i) {   // slot of the i-th contributor
-              return lane_base + (int64_t)(i == 0 ? first_slot : next_slot + (i - 1) * slot_step) * (kBM * BN);
-            };
+            const float* slot0 = p.partial + (int64_t)w.tile * p.split_k * (kBM * BN) +
+                                 ((size_t)quarter * (BN / 4) * 32 + lane) * 4;
             auto sum_chunk = [&](uint32_t (&r)[kChunk], int c0) {
               float a[kChunk];
 #pragma unroll
               for (int jj = 0; jj < kChunk; ++jj) a[jj] = 0.0f;
               // two slices per step, their loads in flight together (the slots sit in L2: latency, not
               // bandwidth, is what the sum waits for); the adds stay in slice order
-              for (int ks = 0; ks < n_contrib; ks += 2) {
-                const float* s0 = slot_of(ks);
-                const bool two = ks + 1 < n_contrib;
-                const float* s1 = two ? slot_of(ks + 1) : s0;
+              for (int ks = 0; ks < p.split_k; ks += 2) {
+                const float* s0 = slot0 + (size_t)ks * (kBM * BN);
+                const bool two = ks + 1 < p.split_k;
+                const float* s1 = two ? s0 + kBM * BN : s0;
                 float4 v0[kChunk / 4], v1[kChunk / 4];
 #pragma unroll
                 for (int jj = 0; jj < kChunk; jj += 4) {
@@ -923,6 +902,53 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     __syncwarp();
     tc_fence_after_sync();
     tmem_dealloc<kTmemCols>(tmem_base);
+  }
+}
+
+// Stream-K fix-up: one block per dealt-out tile.  A tile whose K slabs were shared by several
+// CTAs is the sum of their fp32 slots, added in CTA order (deterministic) and rounded once.
+// Grid: (blocks per tile, dealt-out tiles); one thread per 4 consecutive columns of a tile row, so
+// the whole fix-up is one wide wave of independent 16-byte loads.
+__global__ void gemm_streamk_fixup_kernel(const GemmParams p, int bn, int grid) {
+  const int j = blockIdx.y;  // dealt-out tile index
+  const int u_lo = j * p.num_kb, u_hi = (j + 1) * p.num_kb;
+  const int c_lo = u_lo / p.sk_upc, c_hi = (u_hi - 1) / p.sk_upc;
+  if (c_lo == c_hi) return;  // computed whole by one CTA and already stored
+  const int quad = blockIdx.x * blockDim.x + threadIdx.x;  // index of a float4 inside the tile
+  const int quads_per_row = bn >> 2;
+  if (quad >= kBM * quads_per_row) return;
+  const int trow = quad / quads_per_row, tcol = (quad - trow * quads_per_row) << 2;
+  WorkItem w;
+  decode_tile(p, p.dp_rounds * grid + j, w);
+  const int row = w.m_blk * kBM + trow, col = w.n_blk * bn + tcol;
+  if (row >= p.PM || col >= p.PN) return;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c = c_lo; c <= c_hi; ++c) {
+    const int first_tile = (c * p.sk_upc) / p.num_kb;
+    const int slot = 2 * c + (j == first_tile ? 0 : 1);
+    // slots are lane-major: the float4 (row, 4j..4j+3) sits at ((row / 32 * (bn / 4) + j) * 32 + row % 32) * 4
+    const float4 v = *reinterpret_cast<const float4*>(
+        p.partial + (int64_t)slot * kBM * bn + ((size_t)((trow >> 5) * (bn >> 2) + (tcol >> 2)) * 32 + (trow & 31)) * 4);
+    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+  }
+  const float vals[4] = {s.x, s.y, s.z, s.w};
+  __half* cbase = p.C + (int64_t)w.b * p.stride_c;
+  if (!p.swap && col + 3 < p.PN && (p.ldc & 3) == 0 && (p.stride_c & 3) == 0 &&
+      (reinterpret_cast<uintptr_t>(p.C) & 7) == 0) {
+    __half2 h0 = __floats2half2_rn(vals[0], vals[1]);
+    __half2 h1 = __floats2half2_rn(vals[2], vals[3]);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&h0);
+    pk.y = *reinterpret_cast<uint32_t*>(&h1);
+    *reinterpret_cast<uint2*>(cbase + (int64_t)row * p.ldc + col) = pk;
+  } else {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if (col + q < p.PN) {
+        const int64_t o = p.swap ? (int64_t)(col + q) * p.ldc + row : (int64_t)row * p.ldc + col + q;
+        cbase[o] = __float2half_rn(vals[q]);
+      }
+    }
   }
 }
 
@@ -1231,7 +1257,7 @@ static void default_config_impl(int M, int N, int K, int batch, int sm_count, bo
       }
     }
     if (tail != 0 && num_kb >= 8) {
-      // dealt-out slabs, the fp32 slots' round trip and the last-arriving CTAs' sums
+      // dealt-out slabs, the fp32 slots' round trip through HBM, and the fix-up launch
       // (measured on 4096^3: about 6 us plus three times the slots' HBM transfer time)
       const double slot_bytes = 2.0 * std::min<int64_t>(tiles * num_kb, sm_count) * kBM * bn * 4.0;
       const double sk = ((double)rounds * num_kb + std::ceil((double)tail * num_kb / sm_count)) * slab_us(bn) +
@@ -1308,13 +1334,6 @@ static void streamk_plan(int64_t tiles, int num_kb, int grid, int* dp_rounds, in
   *sk_upc = std::max(1, upc);
 }
 
-// a fresh tag per launch: whatever the counter words of a workspace hold from other launches (or from no launch at
-// all) reads as stale, so the workspace needs no clearing
-static unsigned int next_launch_epoch() {
-  static std::atomic<unsigned int> next_epoch{0x5eed0001u};
-  return next_epoch.fetch_add(1u);
-}
-
 static size_t splitk_counter_bytes(int64_t tiles) { return ((size_t)tiles * sizeof(unsigned long long) + 1023) / 1024 * 1024; }
 
 size_t gemm_f16_workspace_bytes(const helix_cfg_t* cfg, int M, int N, int K, int batch, int sm_count) {
@@ -1326,8 +1345,7 @@ size_t gemm_f16_workspace_bytes(const helix_cfg_t* cfg, int M, int N, int K, int
     const int64_t tiles = (int64_t)((pm + kBM - 1) / kBM) * ((pn + bn - 1) / bn) * std::max(batch, 1);
     const int grid = (int)std::min<int64_t>(tiles * std::max(1, (K + kBK - 1) / kBK), sm_count);
     if (tiles % grid == 0) return 0;
-    // arrival counters of the dealt-out tiles (fewer than grid), then two slots per CTA
-    return splitk_counter_bytes(grid) + (size_t)2 * grid * kBM * bn * sizeof(float);
+    return (size_t)2 * grid * kBM * bn * sizeof(float);
   }
   if (cfg->split_k <= 1) return 0;
   // split-K: arrival counters (one per tile, rounded up to 1 KiB), then one kBM x BN fp32 slot per tile and slice
@@ -1441,7 +1459,7 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
   p.ldc = ldc;
   p.stride_c = sc;
   int grid;
-  bool fixup = false, reduce = false;   // stream-K / split-K with partial tiles in the workspace
+  bool fixup = false, reduce = false;
   if (cfg.stream_k) {
     grid = (int)std::min<int64_t>(tiles * p.num_kb, sm_count);
     p.stream_k = 1;
@@ -1450,13 +1468,10 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
     if (p.sk_tiles == 0) {
       p.stream_k = 0;  // whole waves only: plain tile list
     } else {
-      const size_t cbytes = splitk_counter_bytes(grid);
-      const size_t need = cbytes + (size_t)2 * grid * kBM * bn * sizeof(float);
-      if (!ws || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 15)) return HELIX_ERR_WORKSPACE;
-      p.counters = static_cast<unsigned long long*>(ws);
-      p.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + cbytes);
-      p.epoch = next_launch_epoch();
-      fixup = true;   // the launch sums its own partial tiles (last-arriving CTA): it only shares its workspace
+      const size_t need = (size_t)2 * grid * kBM * bn * sizeof(float);
+      if (!ws || ws_bytes < need) return HELIX_ERR_WORKSPACE;
+      p.partial = static_cast<float*>(ws);
+      fixup = true;
     }
   }
   if (!p.stream_k) {
@@ -1473,7 +1488,10 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
       if (!ws || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 15)) return HELIX_ERR_WORKSPACE;
       p.counters = static_cast<unsigned long long*>(ws);
       p.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + cbytes);
-      p.epoch = next_launch_epoch();
+      // a fresh tag per launch: whatever the counter words hold from other launches (or from no launch at
+      // all) reads as stale, so the workspace needs no clearing
+      static std::atomic<unsigned int> next_epoch{0x5eed0001u};
+      p.epoch = next_epoch.fetch_add(1u);
       reduce = true;
     }
   }
@@ -1516,6 +1534,12 @@ static int launch_common(const helix_cfg_t& cfg, bool conv, const CUtensorMap& t
 #undef HELIX_BN_CASE
   if (e != cudaSuccess) return HELIX_ERR_CUDA;
   ++*launches;
+  if (fixup) {
+    const dim3 fgrid((kBM * (bn >> 2) + 255) / 256, p.sk_tiles);
+    gemm_streamk_fixup_kernel<<<fgrid, 256, 0, stream>>>(p, bn, grid);
+    if (cudaGetLastError() != cudaSuccess) return HELIX_ERR_CUDA;
+    ++*launches;
+  }
   return HELIX_OK;
 }
 

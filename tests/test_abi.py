@@ -66,8 +66,7 @@ def test_default_config_and_workspace_are_consistent(lib):
             pm, pn = (N, M) if c.swap_ab else (M, N)
             tiles = -(-pm // 128) * -(-pn // c.tile_n) * b
             grid = min(tiles * -(-K // 64), 148)   # no device here: the library assumes 148 SMs
-            # arrival counters of the dealt-out tiles (8 bytes each, rounded up to 1 KiB), then two slots per CTA
-            assert ws == (0 if tiles % grid == 0 else -(-grid * 8 // 1024) * 1024 + 2 * grid * 128 * c.tile_n * 4)
+            assert ws == (0 if tiles % grid == 0 else 2 * grid * 128 * c.tile_n * 4)
         elif c.split_k == 1:
             assert ws == 0
         else:

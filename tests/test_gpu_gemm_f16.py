@@ -230,7 +230,7 @@ def test_gemm_stream_k(oracle, bn, swap, shape):
     cfg = _sk(bn, swap)
     got = _run(a, b, cfg)
     again = _run(a, b, cfg)
-    assert np.array_equal(got.view(np.uint16), again.view(np.uint16)), "the stream-K sum must be deterministic"
+    assert np.array_equal(got.view(np.uint16), again.view(np.uint16)), "stream-K fix-up must be deterministic"
     _, ref32 = oracle.hgemm_fast(a, b)
     util.assert_f16_close(got, ref32, f"stream-K {shape} bn={bn} swap={swap}")
 
