@@ -36,6 +36,7 @@ constexpr int kPairProducerWarps = 3;   // warp 0 and warps 6, 7 issue TMA loads
 constexpr int kThreads = 32 + 32 + 128 + 64;
 constexpr int kStagingBytes = 2 * 128 * 128;     // two 128-row x 128-byte boxes shared by the four epilogue warps
 constexpr int kEpiBarrier = 1;                   // named barrier of the 128 epilogue threads
+constexpr int kTokBarrier2 = 10;                 // named barriers 10, 11: issue order of two MMA warps that alternate K slabs
 constexpr int kFwdBarrier2 = 2;                  // named barriers 2..9: arrival of a group of ring stages, forwarded to the MMA warp
 
 struct Gemm2Params {
@@ -47,6 +48,7 @@ struct Gemm2Params {
   int load_warps;   // issuing warps per CTA, <= stages (see the one-CTA kernel's producer)
   int tma_store, independent;
   int probe;        // tuning instrument (helix_cfg_t.probe): 1 = issue no MMA, 2 = no A loads, 4 = no B loads
+  int dual;         // 1: warps 1 and 7 of the even CTA issue the MMAs of alternate K slabs (needs load_warps <= 2, group 1)
   int group;        // ring stages that share one "full" barrier (one wait of the MMA issuer per group)
   FastDiv fd_grp;
   int* status;
@@ -210,6 +212,63 @@ __device__ __forceinline__ void umma_commit_pair_elect(uint64_t* bar) {
       : "memory");
 }
 
+// Dual issue (the default; probe bit 9 turns it off): two warps of the even CTA walk this loop and issue the MMAs of alternate K slabs
+// (slab n belongs to warp n & 1 = ME).  Each waits for its own slabs' arrival barrier itself (one barrier per stage):
+// the ~200 cycles a shared-memory read spends behind the warp's own queued MMAs, its descriptors and its commit all
+// run while the other warp's four MMAs of 128 pipe cycles each are being issued.  The order of the MMAs is fixed by
+// a token: the owner of slab n - 1 arrives at a named barrier after issuing, fenced, and the owner of slab n meets
+// it there before issuing, so the accumulation order -- every bit of the result -- is that of one issuer.  Both
+// warps walk the whole sequence whatever happens (after a failed wait nothing is issued, the rendezvous are kept).
+template <int BN, int ME>
+__device__ __forceinline__ void pair_dual_issue_loop(const Gemm2Params& p, const int pair, const int num_pairs,
+                                                     const int lane, const int stages, uint8_t* sA, uint8_t* sB,
+                                                     uint64_t* full_bar, uint64_t* empty_bar, uint64_t* tmem_full,
+                                                     uint64_t* tmem_empty, volatile int* abort_flag,
+                                                     const uint32_t tmem_base) {
+  constexpr int kBHalfBytes = (BN / 2) * kBK * 2;
+  constexpr uint32_t kIdesc = umma_idesc_f16(2 * kBM, BN);
+  int stage = 0;
+  uint32_t phase = 0;
+  bool ok = true;
+  int nslab = 0;
+  Item2 it;
+  for (int idx = 0; get_item2(p, pair, num_pairs, idx, it); ++idx) {
+    const int acc = idx & 1;
+    const uint32_t acc_phase = (idx >> 1) & 1;
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status));
+    tc_fence_after_sync();
+    if (lane == 0 && ME == 0) trace2_tile(p, idx, 2);
+    const uint32_t d_tmem = tmem_base + acc * BN;
+    for (int kb = it.kb0; kb < it.kb1; ++kb) {
+      const int n = nslab++;
+      if ((n & 1) == ME) {
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase, abort_flag, p.status));
+        if (lane == 0) trace2_slab(p, 1, n);
+        tc_fence_after_sync();
+        const uint64_t da = umma_desc_sw128(smem_u32(sA + (size_t)stage * kATileBytes));
+        const uint64_t db = umma_desc_sw128(smem_u32(sB + (size_t)stage * kBHalfBytes));
+        if (n > 0) {
+          named_bar_sync(kTokBarrier2 + ((n - 1) & 1), 64);
+          tc_fence_after_sync();
+        }
+        if (ok && !(p.probe & 1)) {
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k)
+            umma_f16_ss_pair_elect(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kb > it.kb0) || (k > 0));
+        }
+        tc_fence_before_sync();
+        asm volatile("bar.arrive %0, 64;" ::"r"(kTokBarrier2 + (n & 1)) : "memory");
+        if (ok) umma_commit_pair_elect(&empty_bar[stage]);
+      }
+      if (++stage == stages) { stage = 0; phase ^= 1; }
+    }
+    if (ok) umma_commit_pair_elect(&tmem_full[acc]);   // both warps, each for its own MMAs (barrier count 2)
+    if (lane == 0 && ME == 0) trace2_tile(p, idx, 3);
+  }
+  // the token of the last slab is met by the warp that did not issue it, so that no arrival is left over
+  if (nslab > 0 && ((nslab - 1) & 1) != ME) named_bar_sync(kTokBarrier2 + ((nslab - 1) & 1), 64);
+}
+
 template <int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -251,7 +310,7 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_full[a], p.dual ? 2 : 1);
       mbar_init(&tmem_empty[a], 8);
     }
     *abort_flag = 0;
@@ -280,7 +339,11 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // and meets it at a named barrier per group of stages: a shared-memory read by the MMA warp itself would queue
     // behind the MMAs it has just issued.  Both warps walk the same sequence of groups to its end whatever
     // happens (after a failed wait only the rendezvous are kept), in lockstep per group.
-    if (warp == 7 && rank == 0 && p.load_warps < kPairProducerWarps) {
+    if (p.dual) {
+      if (warp == 7 && rank == 0)   // second MMA-issuing warp (it issues no loads: load_warps <= 2)
+        pair_dual_issue_loop<BN, 1>(p, pair, num_pairs, lane, stages, sA, sB, full_bar, empty_bar, tmem_full, tmem_empty,
+                                    abort_flag, tmem_base);
+    } else if (warp == 7 && rank == 0 && p.load_warps < kPairProducerWarps) {
       bool ok = true;
       int stage = 0, gpos = 0, gidx = 0;
       uint32_t phase = 0;
@@ -349,7 +412,10 @@ gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // The whole warp walks the loop convergently (warp-uniform state, waits end in a vote) and one elected lane
     // issues.  With a watcher warp (forward) the arrival of a group of stages comes through a named barrier and the
     // sequence is walked to its end even after a failed wait (ok = false: only the rendezvous are kept).
-    if (rank == 0) {
+    if (rank == 0 && p.dual) {
+      pair_dual_issue_loop<BN, 0>(p, pair, num_pairs, lane, stages, sA, sB, full_bar, empty_bar, tmem_full, tmem_empty,
+                                  abort_flag, tmem_base);
+    } else if (rank == 0) {
       const bool forward = p.load_warps < kPairProducerWarps;
       int stage = 0;
       uint32_t phase = 0;
@@ -690,7 +756,13 @@ int gemm_f16_pair_launch(const helix_cfg_t& cfg, const void* A, int64_t lda, con
   // measured with the forwarded arrivals (microseconds at 1 / 2 / 3 stages per group): 4096^3 104.6 / 102.0 / 108.5,
   // 8192 x 768 x 3072 36.7 / 35.3 / 38.1, 8192 x 2304 x 768 23.8 / 23.6 / 24.1
   p.group = p.stages >= 4 ? 2 : 1;
+  // Two issuing warps, each waiting for its own slabs (one arrival barrier per stage), unless probe bit 9 asks for
+  // the single issuer or a third loading warp needs warp 7.  Measured against the single issuer with two stages per
+  // group (microseconds): 4096^3 101.7 -> 101.0, 8192 x 2304 x 768 23.9 -> 23.0, 8192 x 3072 x 768 32.3 -> 31.0,
+  // 8192^3 and 2048 x 14336 x 4096 within 1 %; on 128-wide pair tiles 12-20 % (4096^3 137.7 -> 122.6).
+  p.dual = (!(cfg.probe & 0x200) && (cfg.load_group > 0 ? cfg.load_group : 2) <= 2) ? 1 : 0;
   if ((cfg.probe >> 4) & 7) p.group = (cfg.probe >> 4) & 7;   // tuning override
+  if (p.dual) p.group = 1;
   while (p.group > 1 && p.stages / p.group < 2) --p.group;
   p.stages = p.stages / p.group * p.group;
   p.fd_grp = make_fastdiv(p.group);

@@ -107,7 +107,9 @@ typedef struct helix_cfg {
                     fix how many ring stages share one arrival barrier; bit 7 = two warps issue the MMAs
                     of alternate K slabs (one-CTA kernel with at most two loading warps; measured 4-8 %
                     faster on tiles up to 128 wide, not a default); bit 8 = swapped tiles with at most 64
-                    rows keep M = 128 MMAs instead of M = 64; results are not affected by these         */
+                    rows keep M = 128 MMAs instead of M = 64; bit 9 = the pair kernel (cta_group 2) issues its
+                    MMAs from one warp (two warps alternating K slabs are its default with at most two
+                    loading warps); results are not affected by these                                     */
 } helix_cfg_t;
 
 /* A fully described launch; the tagged union the timing entry point iterates. */

@@ -390,3 +390,10 @@ def test_two_issuing_warps_give_the_same_bits(shape, bn):
     assert torch.equal(one, two)
     ref = a.float() @ b.float().T
     assert float((two.float() - ref).norm() / ref.norm()) < 2e-3
+    # the pair kernel: two issuing warps are its default, probe bit 9 selects the single issuer
+    pair_two = ops.gemm_f16(a, b, cfg=ops.make_cfg(OP_GEMM_F16, 256, max(bn, 128), 64, cta_group=2))
+    pair_one = ops.gemm_f16(a, b, cfg=ops.make_cfg(OP_GEMM_F16, 256, max(bn, 128), 64, cta_group=2, probe=0x200))
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(pair_one, pair_two)
+    assert float((pair_two.float() - ref).norm() / ref.norm()) < 2e-3
