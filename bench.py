@@ -296,8 +296,10 @@ def per_config_table(peaks):
     # C4: ResNet-style convolutions at batch 32, each rated against its own floor max(flops/peak, bytes/hbm);
     # fourth figure: microseconds per launch when four launches on distinct buffers overlap
     c4 = {}
-    for layer in datagen.C4_LAYERS:
-        B, C, H, W, OC, kh, kw, s, p = layer
+    # plus the first layer of the model-level CNN (3 channels stored as 4: the raw-row kernel), flops counted on 3
+    for layer in list(datagen.C4_LAYERS) + [(32, 3, 224, 224, 64, 7, 7, 2, 3)]:
+        B, IC, H, W, OC, kh, kw, s, p = layer
+        C = ops.conv_stored_channels(IC, H, W, OC, kh, kw, s, p)
         Ho, Wo = ops.conv_out_hw(H, W, kh, kw, s, p)
         ls = []
         for _ in range(4):
@@ -309,7 +311,7 @@ def per_config_table(peaks):
         for l in ls:
             l.flags = LAUNCH_INDEPENDENT
         over, _, _ = timed(ls, warmup=3, iters=20)
-        fl = 2.0 * B * Ho * Wo * OC * C * kh * kw
+        fl = 2.0 * B * Ho * Wo * OC * IC * kh * kw
         by = 2.0 * (xx.numel() + ww.numel() + yy.numel())
         floor = max(fl / (peaks["tflops"] * 1e12), by / (peaks["hbm_gbs"] * 1e9))
         c4["x".join(map(str, layer))] = r3(avg * 1e6, fl / avg / 1e12, floor / avg) + [round(over * 1e6, 2)]

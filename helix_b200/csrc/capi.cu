@@ -302,6 +302,7 @@ size_t helix_workspace_bytes(const helix_launch_t* l) {
       const helix::ConvGeom g = conv_geom(l->conv);
       const int64_t M = (int64_t)g.NB * g.Ho * g.Wo, K = (int64_t)g.R * g.S * g.C;
       if (M <= 0 || M > 0x7fffffff || K > 0x7fffffff) return 0;
+      if (g.C == 4) return 0;   // the four-channel first-layer kernel keeps everything on chip
       helix_cfg_t cfg = l->cfg;
       if (!have_cfg) helix::conv_f16_default_config(g, sms, &cfg);
       return helix::gemm_f16_workspace_bytes(&cfg, (int)M, g.KO, (int)K, 1, sms);

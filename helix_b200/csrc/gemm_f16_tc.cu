@@ -1595,6 +1595,12 @@ int conv_f16_launch(const helix_cfg_t* cfg_in, const void* x, const void* w, voi
   if (!x || !w || !y || g.NB <= 0 || g.H <= 0 || g.W <= 0 || g.C <= 0 || g.KO <= 0 || g.R <= 0 || g.S <= 0 ||
       g.stride <= 0 || g.pad < 0 || g.Ho <= 0 || g.Wo <= 0)
     return HELIX_ERR_INVALID;
+  // four stored channels (an RGB first layer): its own kernel, which needs no 16-byte pixels
+  if (g.C == 4) {
+    // no tunable configuration: of an explicit one only the probe bits are read
+    return conv_f16_stem_launch(x, w, y, g, (cfg_in && cfg_in->tile_m != 0) ? cfg_in->probe : 0, status_dev, sm_count,
+                                independent, stream, launches);
+  }
   if ((g.C & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return HELIX_ERR_ALIGN;
   const int64_t M64 = (int64_t)g.NB * g.Ho * g.Wo;
   const int64_t K64 = (int64_t)g.R * g.S * g.C;

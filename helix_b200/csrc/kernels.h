@@ -73,6 +73,10 @@ bool conv_f16_halo_eligible(const ConvGeom& g, const helix_cfg_t* cfg);
 double conv_f16_halo_estimate_us(const ConvGeom& g, int sm_count);   // < 0: geometry not covered
 int conv_f16_halo_launch(const helix_cfg_t* cfg, const void* x, const void* w, void* y, const ConvGeom& g,
                          int* status_dev, int sm_count, bool independent, cudaStream_t stream, int64_t* launches);
+// ---- conv_f16_stem.cu (stride-2 convolution over 4 stored channels, input rows resident in shared memory)
+bool conv_f16_stem_eligible(const ConvGeom& g);
+int conv_f16_stem_launch(const void* x, const void* w, void* y, const ConvGeom& g, int probe, int* status_dev,
+                         int sm_count, bool independent, cudaStream_t stream, int64_t* launches);
 int conv_f16_launch(const helix_cfg_t* cfg, const void* x, const void* w, void* y, const ConvGeom& g, void* ws,
                     size_t ws_bytes, int* status_dev, int sm_count, bool independent, cudaStream_t stream,
                     int64_t* launches);

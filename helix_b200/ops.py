@@ -109,7 +109,9 @@ def kernel_name(launch):
         return "gemm_f16_tc2_kernel<%d>" % c.tile_n
     gathers = False
     if launch.op == OP_CONV_F16:
-        n, h, w, ch, _, r, s, stride, pad = list(launch.conv)
+        n, h, w, ch, ko, r, s, stride, pad = list(launch.conv)
+        if ch == 4:
+            return "conv_f16_stem_kernel<%d>" % (4 if ko <= 64 else 2)
         as_gemm = r == 1 and s == 1 and stride == 1 and pad == 0
         im2col = ch % 64 == 0 and n * h * w * ch * 2 >= 131072 and stride <= 8 and not c.conv_gather
         gathers = not as_gemm and not im2col
@@ -221,6 +223,20 @@ def gemv_f32(w, x, out=None, cfg=None):
 
 def conv_out_hw(H, W, R, S, stride, pad):
     return (H + 2 * pad - R) // stride + 1, (W + 2 * pad - S) // stride + 1
+
+
+def conv_stored_channels(IC, H, W, OC, kh, kw, stride, pad):
+    """Channels an NHWC fp16 activation of IC logical channels is stored with (the rest are zeros).  Pixels are
+    16 bytes or more (C a multiple of 8) for the tensor-map kernels; an input of up to 4 channels is stored as 4
+    where the first-layer kernel covers the geometry (stride 2, filter up to 8 x 7, output rows of up to 128 pixels,
+    64 or 128 output channels -- the conditions of conv_f16_stem_eligible in csrc/conv_f16_stem.cu)."""
+    if IC <= 4 and stride == 2 and 2 <= kh <= 8 and pad < kh and W % 2 == 0 and OC in (64, 128):
+        P = (pad + 1) & ~1
+        Wo = (W + 2 * pad - kw) // 2 + 1
+        Ho = (H + 2 * pad - kh) // 2 + 1
+        if P - pad + kw <= 8 and 1 <= Wo <= 128 and Ho >= 1 and (P + W) * 8 <= 2176:
+            return 4
+    return (IC + 7) // 8 * 8
 
 
 def launch_conv2d_f16(x, w, out, stride, pad, cfg=None, ws=None):

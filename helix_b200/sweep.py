@@ -14,13 +14,6 @@ import torch
 from . import ops, workloads
 from ._lib import LAUNCH_INDEPENDENT
 
-STEM_CHANNEL_PAD = 8  # NHWC activations need C % 8 == 0 (16-byte rule); C = 3 is stored as 8
-
-
-def _padded_channels(c):
-    return (c + STEM_CHANNEL_PAD - 1) // STEM_CHANNEL_PAD * STEM_CHANNEL_PAD
-
-
 def unit_operand_shapes(unit):
     """Shapes (a, b, out) of a unit's device tensors in the layouts the kernels take."""
     s = unit["shape"]
@@ -30,7 +23,7 @@ def unit_operand_shapes(unit):
             return (s[3], M, K), (s[3], N, K), (s[3], M, N)
         return (M, K), (N, K), (M, N)
     B, IC, H, W, OC, kh, kw, stride, pad = s
-    C = _padded_channels(IC)
+    C = ops.conv_stored_channels(IC, H, W, OC, kh, kw, stride, pad)   # C = 3 is stored as 4 (first layer) or 8
     Ho, Wo = ops.conv_out_hw(H, W, kh, kw, stride, pad)
     return (B, H, W, C), (OC, kh, kw, C), (B, Ho, Wo, OC)
 

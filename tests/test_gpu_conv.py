@@ -150,6 +150,64 @@ def test_conv_window_resident_kernel(oracle, geom):
     util.assert_f16_close(got, y32, f"window-resident conv {geom}")
 
 
+@pytest.mark.parametrize("geom", [
+    (1, 4, 16, 16, 64, 7, 7, 2, 3),        # one item per CTA
+    (2, 4, 224, 224, 64, 7, 7, 2, 3),      # the first layer of an RGB network, two images
+    (4, 4, 1200, 16, 64, 7, 7, 2, 3),      # 2400 output rows: eight items per CTA, the 16-slot row ring wraps, strips cross images
+    (300, 4, 20, 24, 64, 7, 7, 2, 3),      # ten output rows per image: every strip crosses images, clipped rows top and bottom
+    (3, 4, 30, 50, 64, 7, 7, 2, 3),        # all four channels non-zero
+    (2, 4, 64, 64, 64, 3, 3, 2, 1),        # 3 x 3: taps at window positions 1..3
+    (2, 4, 64, 64, 128, 5, 5, 2, 2),       # 128 output channels: two accumulators, two staging boxes per item
+    (5, 4, 40, 256, 128, 8, 6, 2, 2),      # widest row (128 output pixels), eight filter rows, even pad
+    (2, 4, 33, 32, 64, 4, 2, 2, 0),        # no padding, odd height
+])
+def test_conv_four_channel_first_layer_kernel(oracle, geom):
+    """Stride-2 convolution over 4 stored channels: the matrix descriptor reads the overlapping windows straight
+    from raw image rows in shared memory (no im2col anywhere)."""
+    B, C, H, W, OC, kh, kw, stride, pad = geom
+    x, w = datagen.c4_conv(*geom, seed=31)
+    assert ops.conv_stored_channels(3, H, W, OC, kh, kw, stride, pad) == 4
+    got = _run(x, w, stride, pad)
+    _, y32 = oracle.conv2d_nhwc_f16(x, w, stride, pad)
+    assert got.shape == y32.shape
+    util.assert_f16_close(got, y32, f"first-layer conv {geom}")
+    if kh == 7 and B == 2:
+        # the same layer with the fourth channel zero and 8 stored channels goes through the gather kernel
+        x[..., 3:] = 0
+        x8 = np.zeros((B, H, W, 8), np.float16)
+        w8 = np.zeros((OC, kh, kw, 8), np.float16)
+        x8[..., :4], w8[..., :4] = x, w
+        util.assert_f16_close(_run(x, w, stride, pad), oracle.conv2d_nhwc_f16(x8, w8, stride, pad)[1], "3 + 1 channels")
+
+
+def test_conv_first_layer_full_batch_against_the_gather_kernel(oracle):
+    """32 x 224 x 224 x 3 -> 64, 7 x 7 / 2: twelve items per CTA.  First and last image against the oracle, every
+    image against the implicit-GEMM kernel on the same data stored with 8 channels (different summation order)."""
+    geom = (32, 4, 224, 224, 64, 7, 7, 2, 3)
+    x, w = datagen.c4_conv(*geom, seed=32)
+    x[..., 3:] = 0
+    w[..., 3:] = 0
+    refs = {img: oracle.conv2d_nhwc_f16(x[img:img + 1], w, 2, 3)[1] for img in (0, 31)}
+    for rep in range(3):   # rows are handed between warps through barriers: repeat
+        got = _run(x, w, 2, 3)
+        for img, y32 in refs.items():
+            util.assert_f16_close(got[img:img + 1], y32, f"first layer image {img} run {rep}")
+    x8 = np.zeros((32, 224, 224, 8), np.float16)
+    w8 = np.zeros((64, 7, 7, 8), np.float16)
+    x8[..., :4], w8[..., :4] = x, w
+    other = _run(x8, w8, 2, 3)
+    diff = np.abs(got.astype(np.float32) - other.astype(np.float32))
+    assert float(diff.max()) <= 4e-3, float(diff.max())     # two fp16 roundings of sums of magnitude ~1
+
+
+def test_conv_four_channels_outside_the_first_layer_kernel_are_refused():
+    x = torch.zeros((1, 16, 16, 4), dtype=torch.float16, device="cuda")
+    w = torch.zeros((64, 3, 3, 4), dtype=torch.float16, device="cuda")
+    with pytest.raises(Exception):
+        ops.conv2d_f16_nhwc(x, w, 1, 1)      # stride 1: pixels must be 16 bytes
+    assert ops.conv_stored_channels(3, 16, 16, 64, 3, 3, 1, 1) == 8
+
+
 @pytest.mark.parametrize("geom,bn", [
     ((2, 64, 32, 32, 64, 3, 3, 1, 1), 256),     # 64 output channels on half of the 128 rows
     ((3, 64, 30, 30, 72, 3, 3, 1, 1), 256),     # ragged channels (72) and pixels (2700)

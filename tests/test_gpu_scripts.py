@@ -218,7 +218,7 @@ def test_conv_op_level_list_sampled_parity_with_the_models_pick(workdir):
     assert all(l in layers for l in speech)
     for idx, (B, IC, H, W, OC, kH, kW, stride, pad) in enumerate(layers[::53] + speech):
         rng = np.random.default_rng(2000 + idx)
-        C = (IC + 7) // 8 * 8
+        C = ops.conv_stored_channels(IC, H, W, OC, kH, kW, stride, pad)
         x = np.zeros((B, H, W, C), np.float16)
         w = np.zeros((OC, kH, kW, C), np.float16)
         x[..., :IC] = rng.uniform(-1, 1, (B, H, W, IC)).astype(np.float16)
