@@ -189,7 +189,11 @@ int helix_gemv_f16(const helix_cfg_t* cfg, const void* W, int64_t ldw, const voi
 /* y[N,Ho,Wo,KO] = conv2d(x[N,H,W,C], w[KO,R,S,C]), zero padding, fp32 accumulate, fp16 in/out,
  * as one implicit GEMM with M = N*Ho*Wo, N = KO, K = R*S*C.  Replaces the im2col executable plus
  * GEMM executable pair of get_Ampere_FP16_conv_Helix_result (scripts/Ampere_FP16/
- * Ampere_FP16_conv.py:431-446, src_template/Ampere_FP16/im2col.cu:37-97).  C multiple of 8. */
+ * Ampere_FP16_conv.py:431-446, src_template/Ampere_FP16/im2col.cu:37-97).  C a multiple of 8 (16-byte pixels), or
+ * C = 4 (an RGB image stored with one zero channel) for the first-layer geometry: stride 2, 2 <= R <= 8, pad < R,
+ * S + (pad odd) <= 8, W even and at most 128 output pixels per row, KO = 64 or 128; that case runs its own kernel,
+ * needs no workspace, and reads of an explicit cfg only the probe bits (bit 0 no MMAs, bit 1 no row copies, bit 2
+ * no output stores).  Any other C = 4 call returns HELIX_ERR_UNSUPPORTED. */
 int helix_conv2d_f16_nhwc(const helix_cfg_t* cfg, const void* x, const void* w, void* y,
                           int N, int H, int W, int C, int KO, int R, int S, int stride, int pad,
                           void* ws, size_t ws_bytes, void* status_dev, void* stream);
