@@ -236,3 +236,31 @@ def test_conv_op_level_list_sampled_parity_with_the_models_pick(workdir):
         for img in sorted({0, B - 1}):
             _, y32 = oracle.conv2d_nhwc_f16(x[img:img + 1], w, stride, pad)
             util.assert_f16_close(y[img:img + 1].cpu().numpy(), y32, f"conv {(B, IC, H, W, OC, kH, kW, stride, pad)} image {img} with {key}")
+
+
+def test_conv_op_level_first_layers_parity():
+    """Every layer of the op-level convolution list that is stored with 4 channels (the 7 x 7 / 2 first layer at
+    batch 1 ... 64 and a 3 x 3 / 2 one) through the first-layer kernel: first and last image against the oracle."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, SCRIPTS)
+    import numpy as np
+    import torch
+    from helix_b200 import ops
+    from oracle import api as oracle
+    from tests import util
+    from utils.get_benchmark_shape_list import get_conv_op_shape_list
+    oracle.build()
+    layers = sorted({l for l in get_conv_op_shape_list() if ops.conv_stored_channels(*l[1:]) == 4})
+    assert len(layers) >= 19
+    for idx, (B, IC, H, W, OC, kH, kW, stride, pad) in enumerate(layers):
+        rng = np.random.default_rng(3000 + idx)
+        x = np.zeros((B, H, W, 4), np.float16)
+        w = np.zeros((OC, kH, kW, 4), np.float16)
+        x[..., :IC] = rng.uniform(-1, 1, (B, H, W, IC)).astype(np.float16)
+        w[..., :IC] = (rng.standard_normal((OC, kH, kW, IC), dtype=np.float32) * np.float32((2.0 / (IC * kH * kW)) ** 0.5)).astype(np.float16)
+        y = ops.conv2d_f16_nhwc(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), stride, pad)
+        torch.cuda.synchronize()
+        ops.check_status()
+        for img in sorted({0, B - 1}):
+            _, y32 = oracle.conv2d_nhwc_f16(x[img:img + 1], w, stride, pad)
+            util.assert_f16_close(y[img:img + 1].cpu().numpy(), y32, f"first layer {(B, IC, H, W, OC, kH, kW, stride, pad)} image {img}")

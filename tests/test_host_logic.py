@@ -429,3 +429,23 @@ def test_cost_model_split_k_modes_and_launch_protocol():
     c = harness.key_to_cfg(k128[:5] + (1,))
     assert (c.split_k, c.stream_k) == (1, 1)
     assert harness.overlaps(16, 11008, 4096) and not harness.overlaps(4096, 4096, 4096)
+
+
+def test_stored_channels_of_convolution_inputs():
+    """An input of up to four channels is stored with 4 (8-byte pixels) only where the first-layer kernel covers the
+    geometry; everything else pads to a multiple of 8.  The sweep's operand shapes follow."""
+    from helix_b200 import ops, sweep
+    sc = ops.conv_stored_channels
+    assert sc(3, 224, 224, 64, 7, 7, 2, 3) == 4          # the ResNet / GoogLeNet first layer
+    assert sc(3, 108, 108, 64, 3, 3, 2, 1) == 4
+    assert sc(4, 64, 64, 128, 5, 5, 2, 2) == 4
+    assert sc(3, 224, 224, 64, 7, 7, 1, 3) == 8          # stride 1
+    assert sc(3, 224, 224, 96, 11, 11, 4, 0) == 8        # stride 4 (AlexNet)
+    assert sc(3, 224, 224, 32, 7, 7, 2, 3) == 8          # 32 output channels
+    assert sc(3, 600, 600, 64, 7, 7, 2, 3) == 8          # output rows longer than 128 pixels
+    assert sc(3, 225, 225, 64, 7, 7, 2, 3) == 8          # odd width: rows are not multiples of 16 bytes
+    assert sc(3, 224, 224, 64, 7, 8, 2, 3) == 8          # eight taps do not fit beside the alignment shift of an odd pad
+    assert sc(1, 161, 700, 32, 5, 20, 2, 0) == 8
+    assert sc(5, 224, 224, 64, 7, 7, 2, 3) == 8 and sc(64, 56, 56, 64, 3, 3, 1, 1) == 64 and sc(24, 9, 9, 8, 1, 1, 1, 0) == 24
+    a, b, o = sweep.unit_operand_shapes({"kind": "conv", "shape": [32, 3, 224, 224, 64, 7, 7, 2, 3]})
+    assert a == (32, 224, 224, 4) and b == (64, 7, 7, 4) and o == (32, 112, 112, 64)
