@@ -666,7 +666,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["helix", "reference"], default="helix")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-configuration table and the CPU pass")
-    ap.add_argument("--lanes", type=int, default=2, help="independent units run in this many concurrent chains per GPU")
+    ap.add_argument("--lanes", type=int, default=4, help="independent units run in this many concurrent chains per GPU")
     ap.add_argument("--passes", type=int, default=PASSES, help="passes over the work list per step")
     ap.add_argument("--instances", type=int, default=INSTANCES,
                     help="seeded copies of the sweep in the work list (default 8; 1 keeps a profiler run small)")

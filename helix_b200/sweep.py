@@ -86,11 +86,18 @@ class Sweep:
             # units of a sweep share no buffers, so a launch need not wait for its predecessor
             l.flags = LAUNCH_INDEPENDENT
             if self.lanes > 1:
-                sms = ops.device_info().sm_count
-                ops.limit_ctas(l, (sms // self.lanes) & ~1, lane=self.lane_of[i])
+                ops.limit_ctas(l, self.lane_sms()[self.lane_of[i]], lane=self.lane_of[i])
             self.launches.append(l)
         self.flops = sum(workloads.unit_flops(u) for u in self.units)
         self.bytes = sum(workloads.unit_bytes(u) for u in self.units)
+
+    def lane_sms(self):
+        """SMs each lane's launches may spread over: even shares (CTA pairs), the SMs left over handed out two at a
+        time to the first lanes (148 SMs on four lanes: 38, 38, 36, 36)."""
+        sms = ops.device_info().sm_count
+        base = (sms // self.lanes) & ~1
+        extra = (sms - base * self.lanes) // 2
+        return [base + (2 if lane < extra else 0) for lane in range(self.lanes)]
 
     @staticmethod
     def _prepare(u, a, b, out, cfg):

@@ -19,11 +19,15 @@ def _reduced_units():
     return picked
 
 
-def test_two_lanes_match_the_serial_sweep():
+@pytest.mark.parametrize("nlanes", [2, 4])
+def test_lanes_match_the_serial_sweep(nlanes):
     units = _reduced_units()
     serial = sweep.Sweep(units, seed=7, lanes=1)
-    lanes = sweep.Sweep(units, seed=7, lanes=2)
-    assert all(l.cfg.max_ctas == (ops.device_info().sm_count // 2) & ~1 for l in lanes.launches)
+    lanes = sweep.Sweep(units, seed=7, lanes=nlanes)
+    share = lanes.lane_sms()
+    sms = ops.device_info().sm_count
+    assert len(share) == nlanes and all(v % 2 == 0 for v in share) and sms - 1 <= sum(share) <= sms
+    assert all(l.cfg.max_ctas == share[lane] for l, lane in zip(lanes.launches, lanes.lane_of))
     n1 = serial.step()
     n2 = lanes.step()
     torch.cuda.synchronize()
