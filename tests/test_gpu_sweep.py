@@ -112,13 +112,13 @@ def _check_unit_against_oracle(oracle, u, a, b, out, what):
     return 1
 
 
-@pytest.mark.parametrize("lanes", [2, 1])
+@pytest.mark.parametrize("lanes", [4, 2, 1])
 def test_model_level_sweep_at_full_size_against_the_oracle(oracle, lanes):
     """The benchmark's own workload and launch configuration: every GEMM of BERT-base at batch 16 / seq 512 and
     the 53 ResNet-50 convolutions at batch 32, dealt to `lanes` concurrent chains with each launch limited to
     1 / lanes of the SMs (the library re-chooses its tile for the smaller machine), independent-launch flag set.
     Every distinct shape (4 linear GEMMs, the two batched attention GEMMs, 23 convolutions, among them the 7x7
-    stem with 3 channels stored as 8, the 7x7-pixel layers and the strided 1x1 projections) is compared with
+    first layer with 3 channels stored as 4, the 7x7-pixel layers and the strided 1x1 projections) is compared with
     the oracle; then the same step replayed from a CUDA graph, as the benchmark times it, must reproduce the
     eager outputs bit for bit."""
     units = workloads.model_level_sweep()
