@@ -77,6 +77,10 @@ int conv_f16_halo_launch(const helix_cfg_t* cfg, const void* x, const void* w, v
 bool conv_f16_stem_eligible(const ConvGeom& g);
 int conv_f16_stem_launch(const void* x, const void* w, void* y, const ConvGeom& g, int probe, int* status_dev,
                          int sm_count, bool independent, cudaStream_t stream, int64_t* launches);
+// ---- conv_f16_rows.cu (3 x 3 / 1, 64 -> 64 channels: pixels on the accumulator rows, window and weights resident)
+bool conv_f16_rows_eligible(const ConvGeom& g, int sm_count, bool worth_it);
+int conv_f16_rows_launch(const void* x, const void* w, void* y, const ConvGeom& g, int probe, int* status_dev,
+                         int sm_count, bool independent, cudaStream_t stream, int64_t* launches);
 int conv_f16_launch(const helix_cfg_t* cfg, const void* x, const void* w, void* y, const ConvGeom& g, void* ws,
                     size_t ws_bytes, int* status_dev, int sm_count, bool independent, cudaStream_t stream,
                     int64_t* launches);

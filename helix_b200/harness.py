@@ -375,7 +375,7 @@ def conv_f16_result(prof_dict, batch, IC, H, W, OC, kH, kW, stride, pad):
     M, N, K = batch * Ho * Wo, OC, IC * kH * kW
     as_gemm = kH == 1 and kW == 1 and stride == 1 and pad == 0
     C = ops.conv_stored_channels(IC, H, W, OC, kH, kW, stride, pad)
-    if C == 4:   # the first-layer kernel has no tunable configuration: nothing for the cost model to pick
+    if ops.conv_has_fixed_kernel(batch, C, H, W, OC, kH, kW, stride, pad):   # nothing for the cost model to pick
         cost_ms = time_conv_f16(batch, IC, H, W, OC, kH, kW, stride, pad) * 1e3
         return cost_ms, 2.0 * M * N * K / 1e9 / cost_ms
     im2col = C % 64 == 0 and batch * H * W * C * 2 >= 131072 and stride <= 8      # the library's tensor-map rule

@@ -112,6 +112,9 @@ def kernel_name(launch):
         n, h, w, ch, ko, r, s, stride, pad = list(launch.conv)
         if ch == 4:
             return "conv_f16_stem_kernel<%d>" % (4 if ko <= 64 else 2)
+        rows_geom = ch == 64 and ko == 64 and r == 3 and s == 3 and stride == 1 and pad == 1 and w + 2 <= 64
+        if rows_geom and c.conv_gather == 4:    # explicit, or the library's default for this geometry
+            return "conv_f16_rows_kernel"
         as_gemm = r == 1 and s == 1 and stride == 1 and pad == 0
         im2col = ch % 64 == 0 and n * h * w * ch * 2 >= 131072 and stride <= 8 and not c.conv_gather
         gathers = not as_gemm and not im2col
@@ -237,6 +240,18 @@ def conv_stored_channels(IC, H, W, OC, kh, kw, stride, pad):
         if P - pad + kw <= 8 and 1 <= Wo <= 128 and Ho >= 1 and (P + W) * 8 <= 2176:
             return 4
     return (IC + 7) // 8 * 8
+
+
+def conv_has_fixed_kernel(N, C, H, W, KO, R, S, stride, pad):
+    """True where the library runs a convolution through a kernel without a tunable configuration (the 4-channel
+    first-layer kernel, the 64 -> 64 channel row-pair kernel): nothing for a cost model to pick there."""
+    if C == 4:
+        return True
+    l = Launch()
+    l.op = OP_CONV_F16
+    for i, v in enumerate((N, H, W, C, KO, R, S, stride, pad)):
+        l.conv[i] = v
+    return default_config(l).conv_gather == 4
 
 
 def launch_conv2d_f16(x, w, out, stride, pad, cfg=None, ws=None):

@@ -93,7 +93,10 @@ typedef struct helix_cfg {
   int conv_gather; /* CONV_F16: 0 = activations arrive through an im2col tensor map wherever the
                       geometry allows it (C a multiple of 64, tensor of 128 KiB or more), else
                       through gathering producer warps; 1 = always gather (cp.async);
-                      3 = window-resident kernel (stride 1, C a multiple of 64, W + 2*pad <= 256).
+                      3 = window-resident kernel (stride 1, C a multiple of 64, W + 2*pad <= 256);
+                      4 = row-pair kernel (3 x 3, stride 1, pad 1, 64 -> 64 channels, W <= 62: pixels on
+                      the accumulator rows, window and all weights resident; the library's own choice
+                      for that geometry when W >= 46 and there are at least three row pairs per SM).
                       With swap_ab = 1 (im2col geometries only) the output channels take the
                       128-row axis and tile_n pixels the other one                          */
   int max_ctas;  /* > 0: the launch spreads over at most this many SMs (also honoured when the rest of

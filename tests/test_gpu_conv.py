@@ -151,6 +151,36 @@ def test_conv_window_resident_kernel(oracle, geom):
 
 
 @pytest.mark.parametrize("geom", [
+    (1, 64, 8, 8, 64, 3, 3, 1, 1),         # one item per CTA, most accumulator rows junk
+    (2, 64, 56, 56, 64, 3, 3, 1, 1),       # the ResNet stage-1 layer: 116 of 128 rows live
+    (3, 64, 7, 13, 64, 3, 3, 1, 1),        # odd height: the last row pair of an image has one row
+    (2, 64, 33, 62, 64, 3, 3, 1, 1),       # widest row (Wp = 64): the last tap's junk rows reach past the window
+    (40, 64, 56, 48, 64, 3, 3, 1, 1),      # 1120 items: seven or eight per CTA, window and accumulator rings wrap
+    (300, 64, 5, 50, 64, 3, 3, 1, 1),      # three row pairs per image: strips cross images every few items
+])
+def test_conv_row_pair_kernel(oracle, geom):
+    """3 x 3 / 1, 64 -> 64 channels with the pixels on the accumulator rows (conv_gather = 4): every tap reads the
+    resident window through a shifted matrix descriptor; same summation order as the implicit GEMM, so the same bits."""
+    B, C, H, W, OC, kh, kw, stride, pad = geom
+    x, w = datagen.c4_conv(*geom, seed=41)
+    got = _run(x, w, stride, pad, ops.make_cfg(OP_CONV_F16, tile_m=128, tile_n=64, tile_k=64, conv_gather=4))
+    other = _run(x, w, stride, pad, ops.make_cfg(OP_CONV_F16, tile_m=128, tile_n=64, tile_k=64))
+    assert np.array_equal(got, other)
+    for img in sorted({0, B - 1}):
+        _, y32 = oracle.conv2d_nhwc_f16(x[img:img + 1], w, stride, pad)
+        util.assert_f16_close(got[img:img + 1], y32, f"row-pair conv {geom} image {img}")
+    auto = _run(x, w, stride, pad)       # the library's own choice (this kernel where its tile fits)
+    assert np.allclose(auto.astype(np.float32), other.astype(np.float32), rtol=1e-2, atol=2e-3)
+
+
+def test_conv_row_pair_kernel_refuses_other_geometries():
+    x = torch.zeros((1, 16, 16, 128), dtype=torch.float16, device="cuda")
+    w = torch.zeros((64, 3, 3, 128), dtype=torch.float16, device="cuda")
+    with pytest.raises(Exception):
+        ops.conv2d_f16_nhwc(x, w, 1, 1, cfg=ops.make_cfg(OP_CONV_F16, tile_m=128, tile_n=64, tile_k=64, conv_gather=4))
+
+
+@pytest.mark.parametrize("geom", [
     (1, 4, 16, 16, 64, 7, 7, 2, 3),        # one item per CTA
     (2, 4, 224, 224, 64, 7, 7, 2, 3),      # the first layer of an RGB network, two images
     (4, 4, 1200, 16, 64, 7, 7, 2, 3),      # 2400 output rows: eight items per CTA, the 16-slot row ring wraps, strips cross images
