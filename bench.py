@@ -381,6 +381,7 @@ SWEEP_DRAM_BYTES_PER_LAUNCH = {
     "gemm_f16_tc_kernel<256,0>": 30764491, "gemm_f16_tc_kernel<64,0>": 68126530,
     "gemm_f16_tc_kernel<128,0>": 14688633, "gemm_f16_tc_kernel<64,1>": 26433792,
     "conv_f16_stem_kernel<4>": 13823700,   # profiles/conv_f16_stem_kernel_7x7_c3_224x224.md
+    "conv_f16_rows_kernel": 12970000,      # profiles/conv_f16_rows_kernel_3x3_c64_56x56.md
 }
 
 
