@@ -173,6 +173,35 @@ def test_conv_row_pair_kernel(oracle, geom):
     assert np.allclose(auto.astype(np.float32), other.astype(np.float32), rtol=1e-2, atol=2e-3)
 
 
+def test_convolutions_with_a_fixed_kernel_say_so_in_the_default_config():
+    """3 x 3 / 1 at 64 -> 64 channels gets the row-pair kernel (conv_gather = 4) where its tile fits and there are a
+    few row pairs per SM; the 4-channel first layer needs no workspace; everything else keeps a tunable tile."""
+    import ctypes
+    from helix_b200 import _lib
+    from helix_b200._lib import Cfg, Launch
+    lib = _lib.load()
+
+    def default(geom, max_ctas=0):
+        l = Launch()
+        l.op = _lib.OP_CONV_F16
+        for i, v in enumerate(geom):
+            l.conv[i] = v
+        l.cfg.max_ctas = max_ctas
+        c = Cfg()
+        assert lib.helix_default_config(ctypes.byref(l), ctypes.byref(c)) == 0
+        return c, lib.helix_workspace_bytes(ctypes.byref(l))
+    # (N, H, W, C, KO, R, S, stride, pad)
+    c, ws = default((32, 56, 56, 64, 64, 3, 3, 1, 1))
+    assert c.conv_gather == 4 and (c.tile_m, c.tile_n, c.split_k, c.stream_k, c.swap_ab) == (128, 64, 1, 0, 0) and ws == 0
+    assert default((32, 56, 56, 64, 64, 3, 3, 1, 1), max_ctas=36)[0].conv_gather == 4      # one of four launch chains
+    assert default((2, 56, 56, 64, 64, 3, 3, 1, 1))[0].conv_gather == 0                     # 56 row pairs on 148 SMs
+    assert default((32, 28, 28, 64, 64, 3, 3, 1, 1))[0].conv_gather == 0                    # 30 of 64 pixel slots per row
+    assert default((32, 56, 56, 64, 128, 3, 3, 1, 1))[0].conv_gather == 0
+    assert default((32, 56, 56, 128, 64, 3, 3, 1, 1))[0].conv_gather == 0
+    assert default((32, 56, 56, 64, 64, 3, 3, 2, 1))[0].conv_gather == 0
+    assert default((32, 224, 224, 4, 64, 7, 7, 2, 3))[1] == 0
+
+
 def test_conv_row_pair_kernel_refuses_other_geometries():
     x = torch.zeros((1, 16, 16, 128), dtype=torch.float16, device="cuda")
     w = torch.zeros((64, 3, 3, 128), dtype=torch.float16, device="cuda")
