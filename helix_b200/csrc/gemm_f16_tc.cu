@@ -1307,9 +1307,10 @@ void conv_f16_default_config(const ConvGeom& g, int sm_count, helix_cfg_t* out) 
     default_config_impl(M, g.KO, K, 1, sm_count, false, true, out);
   else if (conv_im2col_eligible(g)) {
     default_config_impl(M, g.KO, K, 1, sm_count, false, false, out);
-    // A tcgen05.mma step of 128 x N x 16 takes about 130 cycles whatever N <= 256 (measured on
-    // 64-, 128- and 256-wide tiles), so 65..128 output channels are better spent as the 128 rows
-    // with 256 pixels per step: measured 17.1 -> 13.9 us on 3x3, 128 -> 128 channels, 28 x 28 x 32.
+    // A 128 x N x 16 step costs max(N / 2 cycles of pipe time, (128 + N) / 4 cycles of operand fetch from shared
+    // memory): the wide tile does twice the work of a 128-wide one in 1.5x the fetch time, so 65..128 output channels
+    // are better spent as the 128 rows with 256 pixels per step: measured 17.1 -> 13.9 us on 3x3, 128 -> 128
+    // channels, 28 x 28 x 32.
     // With more channels the pixel tiles become too few for the machine, with 64 or fewer half of
     // every step is padding.
     if (g.KO > 64 && g.KO <= kBM && M >= 64 * 256) {
