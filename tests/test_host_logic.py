@@ -449,3 +449,59 @@ def test_stored_channels_of_convolution_inputs():
     assert sc(5, 224, 224, 64, 7, 7, 2, 3) == 8 and sc(64, 56, 56, 64, 3, 3, 1, 1) == 64 and sc(24, 9, 9, 8, 1, 1, 1, 0) == 24
     a, b, o = sweep.unit_operand_shapes({"kind": "conv", "shape": [32, 3, 224, 224, 64, 7, 7, 2, 3]})
     assert a == (32, 224, 224, 4) and b == (64, 7, 7, 4) and o == (32, 112, 112, 64)
+
+
+def test_first_layer_kernel_row_ring_never_overwrites_a_row_that_is_still_needed():
+    """Restates the row bookkeeping of csrc/conv_f16_stem.cu (RowWalk, the 16-slot ring, the per-slot "last reader"
+    and the completion wait the copying warp derives from it) and checks, for many geometries and strips, that every
+    item finds its rows in the slots the issuing warps compute, and that a slot is only rewritten after the last item
+    that reads its old row is among the items the copying warp has waited for."""
+    SLOTS, RING = 16, 16
+
+    def walk(H, Ho, R, pad, t0, t1):
+        seg_base = seg_first = count = 0
+        prev_hi = -1
+        content = [None] * SLOTS          # (image, row) held by each slot
+        last_use = [-1] * SLOTS           # item that reads it last
+        true_last = {}                    # (image, row) -> last item of the strip that reads it
+        for t in range(t0, t1):
+            b, oy = divmod(t, Ho)
+            for iy in range(max(0, 2 * oy - pad), min(H - 1, 2 * oy - pad + R - 1) + 1):
+                true_last[(b, iy)] = t - t0
+        for t in range(t0, t1):
+            i = t - t0
+            b, oy = divmod(t, Ho)
+            lo, hi = max(0, 2 * oy - pad), min(H - 1, 2 * oy - pad + R - 1)
+            assert lo <= hi
+            if i == 0 or oy == 0:
+                seg_base, seg_first, new_lo = count, lo, lo
+            else:
+                new_lo = prev_hi + 1
+            if hi >= new_lo:
+                count += hi - new_lo + 1
+            prev_hi = hi
+            index_of = lambda iy: seg_base + iy - seg_first
+            need = i - RING // 2
+            for iy in range(new_lo, hi + 1):
+                need = max(need, last_use[index_of(iy) % SLOTS])
+            assert need <= i - 1
+            for iy in range(new_lo, hi + 1):
+                slot = index_of(iy) % SLOTS
+                if content[slot] is not None:
+                    assert true_last[content[slot]] <= need, (H, R, pad, t0, t, content[slot])
+                content[slot] = (b, iy)
+                last_use[slot] = i + min((iy + pad) // 2, Ho - 1) - oy
+                assert last_use[slot] >= true_last[(b, iy)]
+            slot0 = index_of(lo) % SLOTS
+            for k, iy in enumerate(range(lo, hi + 1)):       # what the issuing warp reads: consecutive slots from slot0
+                assert content[(slot0 + k) % SLOTS] == (b, iy)
+
+    rng = __import__("random").Random(5)
+    for (H, R, pad) in [(224, 7, 3), (20, 7, 3), (64, 3, 1), (64, 5, 2), (40, 8, 2), (33, 4, 0), (9, 2, 0), (11, 8, 7), (7, 7, 3)]:
+        Ho = (H + 2 * pad - R) // 2 + 1
+        for NB in (1, 3, 40):
+            items = NB * Ho
+            walk(H, Ho, R, pad, 0, items)
+            for _ in range(20):
+                a = rng.randrange(items)
+                walk(H, Ho, R, pad, a, min(items, a + rng.randrange(1, 60)))
