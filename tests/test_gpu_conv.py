@@ -56,10 +56,14 @@ def test_conv_split_k(oracle):
 
 def test_conv_golden_vectors_from_reference_composition():
     g = np.load(os.path.join(GOLD, "conv_ref.npz"))
-    for i in range(4):
+    for i in range(5):
         B, C, H, W, OC, kh, kw, stride, pad = (int(v) for v in g[f"c{i}_geom"])
         x = np.ascontiguousarray(g[f"c{i}_x_nchw"].transpose(0, 2, 3, 1))
         w = np.ascontiguousarray(g[f"c{i}_w_oihw"].transpose(0, 2, 3, 1))
+        Cs = ops.conv_stored_channels(C, H, W, OC, kh, kw, stride, pad)
+        if Cs != C:      # the 3-channel first layer is stored with a zero fourth channel
+            x = np.concatenate([x, np.zeros(x.shape[:3] + (Cs - C,), np.float16)], axis=3)
+            w = np.concatenate([w, np.zeros(w.shape[:3] + (Cs - C,), np.float16)], axis=3)
         got = _run(x, w, stride, pad)
         util.assert_f16_close(got, g[f"c{i}_y_nhwc"].astype(np.float32), f"golden conv {i}")
 
