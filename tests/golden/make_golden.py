@@ -78,7 +78,9 @@ def conv_cases():
     for i, (B, C, H, W, OC, k, stride, pad) in enumerate([(2, 8, 9, 9, 16, 3, 1, 1), (1, 16, 12, 10, 8, 3, 2, 1),
                                                           (2, 8, 6, 6, 8, 1, 1, 0), (1, 8, 11, 11, 8, 5, 2, 2),
                                                           # an RGB network's first layer: 3 channels, 7 x 7 / 2, pad 3
-                                                          (2, 3, 20, 24, 64, 7, 2, 3)]):
+                                                          (2, 3, 20, 24, 64, 7, 2, 3),
+                                                          # 3 x 3 at 64 -> 64 channels, rows of 50 pixels
+                                                          (1, 64, 6, 50, 64, 3, 1, 1)]):
         x = rng.uniform(-1, 1, (B, C, H, W)).astype(np.float32).astype(np.float16)        # NCHW as the reference
         w = (rng.standard_normal((OC, C, k, k)) * np.sqrt(2.0 / (C * k * k))).astype(np.float32).astype(np.float16)
         col = im2col_nchw(x, k, stride, pad)                                              # [B, K, Ho, Wo]

@@ -56,7 +56,7 @@ def test_conv_split_k(oracle):
 
 def test_conv_golden_vectors_from_reference_composition():
     g = np.load(os.path.join(GOLD, "conv_ref.npz"))
-    for i in range(5):
+    for i in range(6):
         B, C, H, W, OC, kh, kw, stride, pad = (int(v) for v in g[f"c{i}_geom"])
         x = np.ascontiguousarray(g[f"c{i}_x_nchw"].transpose(0, 2, 3, 1))
         w = np.ascontiguousarray(g[f"c{i}_w_oihw"].transpose(0, 2, 3, 1))
@@ -66,6 +66,9 @@ def test_conv_golden_vectors_from_reference_composition():
             w = np.concatenate([w, np.zeros(w.shape[:3] + (Cs - C,), np.float16)], axis=3)
         got = _run(x, w, stride, pad)
         util.assert_f16_close(got, g[f"c{i}_y_nhwc"].astype(np.float32), f"golden conv {i}")
+        if (C, OC, kh, kw, stride, pad) == (64, 64, 3, 3, 1, 1):      # also through the row-pair kernel
+            got = _run(x, w, stride, pad, ops.make_cfg(OP_CONV_F16, tile_m=128, tile_n=64, tile_k=64, conv_gather=4))
+            util.assert_f16_close(got, g[f"c{i}_y_nhwc"].astype(np.float32), f"golden conv {i}, row-pair kernel")
 
 
 def test_conv_delta_kernel_is_a_shift():

@@ -50,7 +50,7 @@ def test_hgemm_one_hot_is_exact(oracle):
 def test_conv_matches_reference_composition(oracle):
     """NHWC oracle vs reference im2col(NCHW)+cpuF16F16Gemm: same sums in another order."""
     g = _load("conv_ref.npz")
-    for i in range(5):       # the last one is the 3-channel 7 x 7 / 2 first-layer geometry
+    for i in range(6):       # the last two: the 3-channel 7 x 7 / 2 first layer, and 3 x 3 at 64 -> 64 channels
         B, C, H, W, OC, kh, kw, stride, pad = (int(v) for v in g[f"c{i}_geom"])
         x = np.ascontiguousarray(g[f"c{i}_x_nchw"].transpose(0, 2, 3, 1))
         w = np.ascontiguousarray(g[f"c{i}_w_oihw"].transpose(0, 2, 3, 1))
