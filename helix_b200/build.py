@@ -18,7 +18,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 OBJ_DIR = os.path.join(CSRC, "_obj")
 LIB_PATH = os.path.join(PKG_DIR, "libhelix_b200.so")
 SOURCES = ["capi.cu", "gemv_f16.cu", "sgemm_f32.cu", "gemm_f16_tc.cu", "gemm_f16_tc2.cu", "conv_f16_halo.cu", "conv_f16_stem.cu", "conv_f16_rows.cu", "conv_f32.cu", "gemv_f32.cu"]
-HEADERS = ["common.cuh", "kernels.h", os.path.join("..", "..", "include", "helix_b200.h")]
+HEADERS = ["common.cuh", "conv_common.cuh", "kernels.h", os.path.join("..", "..", "include", "helix_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

@@ -33,6 +33,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "conv_common.cuh"
 #include "kernels.h"
 
 namespace helix {
@@ -104,17 +105,6 @@ __device__ __forceinline__ bool win_item(const WinParams& p, int t, WinItem& it)
 __device__ __forceinline__ int issuer_first_tap(int first, int nissue, int issuer) {
   const int r = first % nissue;
   return issuer >= r ? issuer - r : issuer - r + nissue;
-}
-
-// 4-D tiled load (C, W, H, N); coordinates may be negative or beyond the tensor: those elements
-// arrive as zeros.  c * 2 bytes must be a multiple of 16.
-__device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* desc, uint64_t* bar, int c, int w, int h,
-                                            int n) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], "
-      "[%2];" ::"r"(smem_u32(smem_dst)),
-      "l"(reinterpret_cast<uint64_t>(desc)), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n)
-      : "memory");
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -371,23 +361,6 @@ conv_f16_win_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
   }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-  });
-  return fn;
-}
-
 struct WinPlan {
   int Wp, TH, HR, RB, npos, buf_bytes, box_bytes, w_stages;
   size_t smem;
@@ -418,10 +391,23 @@ bool plan(const ConvGeom& g, WinPlan* out) {
 
 }  // namespace
 
+EncodeTiledFn conv_tensor_map_encoder() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
 bool conv_f16_halo_eligible(const ConvGeom& g, const helix_cfg_t* cfg) {
   (void)cfg;
   WinPlan pl;
-  return encode_fn() != nullptr && plan(g, &pl);
+  return conv_tensor_map_encoder() != nullptr && plan(g, &pl);
 }
 
 // Microseconds the window kernel is expected to take, or a negative value when the geometry is not covered:
@@ -441,7 +427,7 @@ int conv_f16_halo_launch(const helix_cfg_t* cfg, const void* x, const void* w, v
                          int* status_dev, int sm_count, bool independent, cudaStream_t stream, int64_t* launches) {
   WinPlan pl;
   if (!plan(g, &pl)) return HELIX_ERR_UNSUPPORTED;
-  EncodeTiledFn fn = encode_fn();
+  EncodeTiledFn fn = conv_tensor_map_encoder();
   if (!fn) return HELIX_ERR_CUDA;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return HELIX_ERR_ALIGN;
   WinParams p{};

@@ -26,6 +26,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "conv_common.cuh"
 #include "kernels.h"
 
 namespace helix {
@@ -58,20 +59,6 @@ struct RowsParams {
   int* status;
   FastDiv fd_pairs;
 };
-
-__device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* desc, uint64_t* bar, int c, int w, int h,
-                                            int n) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], "
-      "[%2];" ::"r"(smem_u32(smem_dst)),
-      "l"(reinterpret_cast<uint64_t>(desc)), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n)
-      : "memory");
-}
-
-__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
-  const __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<const uint32_t*>(&h);
-}
 
 __global__ void __launch_bounds__(kThreads, 1)
 conv_f16_rows_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
@@ -252,23 +239,6 @@ conv_f16_rows_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
   }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn rows_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-  });
-  return fn;
-}
-
 constexpr size_t kSmemBytes = 1024 + (size_t)kTaps * kWSlabBytes + (size_t)kWinStages * kWinBytes + kStagingBytes +
                               (1 + 2 * kWinStages + 2 * kAcc) * 8 + 16;
 
@@ -281,7 +251,7 @@ bool conv_f16_rows_eligible(const ConvGeom& g, int sm_count, bool worth_it) {
   if (g.W < 1 || g.W + 2 > 64 || g.H < 1 || g.Ho != g.H || g.Wo != g.W) return false;
   if ((int64_t)g.NB * ((g.Ho + 1) / 2) > 0x3fffffff) return false;
   if (worth_it && (g.W + 2 < 48 || (int64_t)g.NB * ((g.Ho + 1) / 2) < 3 * (int64_t)sm_count)) return false;
-  return rows_encode_fn() != nullptr;
+  return conv_tensor_map_encoder() != nullptr;
 }
 
 int conv_f16_rows_launch(const void* x, const void* w, void* y, const ConvGeom& g, int probe, int* status_dev,
@@ -290,7 +260,7 @@ int conv_f16_rows_launch(const void* x, const void* w, void* y, const ConvGeom& 
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
       (reinterpret_cast<uintptr_t>(y) & 15))
     return HELIX_ERR_ALIGN;
-  EncodeTiledFn fn = rows_encode_fn();
+  EncodeTiledFn fn = conv_tensor_map_encoder();
   if (!fn) return HELIX_ERR_CUDA;
   RowsParams p{};
   p.NB = g.NB; p.H = g.H; p.W = g.W; p.Wp = g.W + 2; p.Ho = g.Ho;

@@ -29,6 +29,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "conv_common.cuh"
 #include "kernels.h"
 
 namespace helix {
@@ -71,11 +72,6 @@ __device__ __forceinline__ uint64_t umma_desc_plain(uint32_t smem_addr, uint32_t
   d |= static_cast<uint64_t>(sbo >> 4) << 32;
   d |= static_cast<uint64_t>(1) << 46;
   return d;
-}
-
-__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
-  const __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<const uint32_t*>(&h);
 }
 
 // Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completion on an mbarrier.
@@ -376,23 +372,6 @@ conv_f16_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const StemParam
   }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn stem_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-  });
-  return fn;
-}
-
 size_t stem_smem_bytes(const ConvGeom& g) {
   return 1024 + kStagingBytes + (size_t)kSlots * kPitch + (size_t)g.R * kChunksPerRow * (g.KO / 8) * 128 + (2 * kRing + 8) * 8 + 16 + kRing * 4;
 }
@@ -428,7 +407,7 @@ int conv_f16_stem_launch(const void* x, const void* w, void* y, const ConvGeom& 
   p.status = status_dev;
   p.fd_ho = make_fastdiv(g.Ho);
   // y[NB][Ho][Wo][KO] as (KO, Wo, NB * Ho); one box = 64 channels x 32 pixels of one output row
-  EncodeTiledFn fn = stem_encode_fn();
+  EncodeTiledFn fn = conv_tensor_map_encoder();
   if (!fn) return HELIX_ERR_CUDA;
   CUtensorMap ty;
   {
